@@ -1,0 +1,113 @@
+/*
+ * slayer_b200 — C ABI of the Blackwell (sm_100a) SLAYER spiking-neuron operators.
+ *
+ * Every entry point takes plain device pointers and sizes; no framework types cross this
+ * boundary.  All tensors are float32, row-major [rows, T] with time last and contiguous,
+ * resident on the CUDA device that is current on the calling thread.  `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  Calls are asynchronous
+ * with respect to the host: they enqueue work on `stream` and return.
+ *
+ * Return value: 0 on success, a negative SLAYER_B200_E* code on failure.  After a failure,
+ * slayer_b200_last_error() returns a human-readable message for the calling thread.
+ * Nothing here falls back to the CPU: without a usable GPU the calls fail.
+ *
+ * The Python extension modules `slayerCuda` and `slayerLoihiCuda` built from this library
+ * export the reference's operator names and signatures on top of these functions.
+ */
+#ifndef SLAYER_B200_H_INCLUDED
+#define SLAYER_B200_H_INCLUDED
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SLAYER_B200_OK          0
+#define SLAYER_B200_EINVAL     -1   /* bad argument (null pointer, negative size, ...)      */
+#define SLAYER_B200_ECUDA      -2   /* a CUDA runtime call or kernel launch failed          */
+#define SLAYER_B200_EUNSUPPORTED -3 /* argument outside what the kernels implement          */
+#define SLAYER_B200_EDEVICE    -4   /* a kernel reported a device-side error status         */
+
+/* ABI version of this header (bumped when a signature changes). */
+int slayer_b200_abi_version(void);
+
+/* Message describing the last failure on the calling thread ("" if none). */
+const char *slayer_b200_last_error(void);
+
+/*
+ * Causal temporal FIR (psp filter):  out[r,t] = Ts * sum_{i<K, i<=t} in[r,t-i] * filter[i].
+ * fp32 fused multiply-add chain in ascending tap order, one multiply by Ts at the end.
+ * Replaces conv<float>() / convKernel, src/cuda/convKernels.h:10-35, :64-96, reached from
+ * convCuda, src/cuda/slayerKernels.cu:41-57.  `out` must not alias `in`.
+ */
+int slayer_b200_conv(float *out, const float *in, const float *filter,
+                     int64_t rows, int64_t T, int64_t K, float Ts, void *stream);
+
+/*
+ * Adjoint of the above:  out[r,t] = Ts * sum_{i<K, t+i<T} in[r,t+i] * filter[i].
+ * Replaces corr<float>() / corrKernel, src/cuda/convKernels.h:37-62, :98-129, reached from
+ * corrCuda, src/cuda/slayerKernels.cu:59-75.  `out` must not alias `in`.
+ */
+int slayer_b200_corr(float *out, const float *in, const float *filter,
+                     int64_t rows, int64_t T, int64_t K, float Ts, void *stream);
+
+/*
+ * Time shift by one amount for all rows:  out[r,t] = in[r,t-d] if 0 <= t-d < T else 0,
+ * d = trunc(shift / Ts) (toward zero; negative shifts advance the signal).
+ * Replaces shift<float>() scalar form / shiftKernel, src/cuda/shiftKernels.h:9-34, :63-98,
+ * reached from shiftCuda (1-element branch) and shiftFlCuda, slayerKernels.cu:87-95, :115-129.
+ */
+int slayer_b200_shift_scalar(float *out, const float *in, float shift,
+                             int64_t rows, int64_t T, float Ts, void *stream);
+
+/*
+ * Per-neuron time shift: rows = nBatch * nNeurons, row r uses lut[r % nNeurons] (device
+ * pointer to nNeurons floats).  One launch covers the whole batch.
+ * Replaces shift<float>() LUT form / shiftKernel, src/cuda/shiftKernels.h:36-61, :100-136,
+ * reached from shiftCuda, src/cuda/slayerKernels.cu:96-105.
+ */
+int slayer_b200_shift_lut(float *out, const float *in, const float *lut,
+                          int64_t nBatch, int64_t nNeurons, int64_t T, float Ts, void *stream);
+
+/*
+ * SRM spike generation with refractory response.  For each row, in time order:
+ * if u[t] >= theta then s[t] = 1/Ts and nu[0..nuSize) is added into u[t..t+nuSize) (clipped
+ * at T, one fp32 add per sample, in spike order); else s[t] = 0.  `u` is updated in place.
+ * Spike positions and the updated u are bit-identical to the sequential definition.
+ * Replaces getSpikes<float>() / getSpikesKernel, src/cuda/spikeKernels.h:9-38, :54-60,
+ * reached from getSpikesCuda, src/cuda/slayerKernels.cu:14-39.
+ */
+int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
+                               int64_t rows, int64_t nuSize, int64_t T,
+                               float theta, float Ts, void *stream);
+
+/*
+ * Loihi CUBA neuron (fixed-point current and voltage decay, threshold, refractory delay).
+ * Input w[r,t] holds integer-valued weighted spikes; outputs are the spike train s (0/1),
+ * the voltage v and the current u as float32 images of the int32 state.  Integer
+ * arithmetic follows the reference's C++ promotion rules exactly (uint32 products with
+ * wrap-around, logical >> 12).  refDelay must be >= 1.
+ * Replaces getSpikes<float>() / getSpikesKernel, src/cuda/spikeLoihiKernels.h:9-72, :75-96,
+ * reached from getSpikesCuda, src/cuda/slayerLoihiKernels.cu:12-46.
+ */
+int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const float *w,
+                                 int64_t rows, int64_t T,
+                                 uint32_t wgtExp, uint32_t theta, uint32_t iDecay,
+                                 uint32_t vDecay, uint32_t refDelay, void *stream);
+
+/*
+ * Surrogate gradient of the spike function, fused into one pass:
+ *   out[i] = g[i] * ( scale / tau * exp(-|u[i] - theta| / tau) ),   i < n.
+ * `out` may alias `g`.  Replaces the chain of elementwise tensor operations in
+ * _spikeFunction.backward, src/slayer.py:858-865, and _spike.backward,
+ * src/slayerLoihi.py:279-283 (tau = tauRho * theta, scale = scaleRho); the reference's
+ * never-bound native twin is evalRhoKernel, src/cuda/spikeKernels.h:41-52.
+ */
+int slayer_b200_spike_grad(float *out, const float *g, const float *u, int64_t n,
+                           float theta, float tau, float scale, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLAYER_B200_H_INCLUDED */

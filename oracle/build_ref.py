@@ -53,6 +53,7 @@ def build_cuda_ops(root, verbose=False):
              extra_include_paths=[os.path.join(root, "src", "cuda")],
              is_python_module=False, verbose=verbose)
         shutil.copy2(os.path.join(bdir, name + ".so"), target)
+        shutil.rmtree(bdir)          # keep only the binary
         built.append(target)
     return built
 

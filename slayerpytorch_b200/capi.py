@@ -1,0 +1,64 @@
+"""ctypes view of the C ABI in ``include/slayer_b200.h``.
+
+For callers that hold raw device pointers (``tensor.data_ptr()``, CuPy, cuda-python ...).
+Every function of the header is declared here with its argument types; ``SYMBOLS`` is the
+list the tests check against the header.  Loading fails loudly when the library is not built.
+"""
+import ctypes
+import os
+
+from . import LIB_DIR
+
+LIB_PATH = os.path.join(LIB_DIR, "libslayer_b200.so")
+
+_p = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_u32 = ctypes.c_uint32
+_f = ctypes.c_float
+_int = ctypes.c_int
+
+SYMBOLS = {
+    "slayer_b200_abi_version": (_int, []),
+    "slayer_b200_last_error": (ctypes.c_char_p, []),
+    "slayer_b200_conv": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
+    "slayer_b200_corr": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
+    "slayer_b200_shift_scalar": (_int, [_p, _p, _f, _i64, _i64, _f, _p]),
+    "slayer_b200_shift_lut": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
+    "slayer_b200_srm_get_spikes": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _f, _p]),
+    "slayer_b200_loihi_get_spikes": (_int, [_p, _p, _p, _p, _i64, _i64, _u32, _u32, _u32, _u32, _u32, _p]),
+    "slayer_b200_spike_grad": (_int, [_p, _p, _p, _i64, _f, _f, _f, _p]),
+}
+
+_lib = None
+
+
+class SlayerB200Error(RuntimeError):
+    pass
+
+
+def load():
+    """dlopen the library and declare every entry point."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise OSError("slayer_b200: %s is not built (run `python -m slayerpytorch_b200.build`); "
+                          "there is no CPU fallback" % LIB_PATH)
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)         # AttributeError if the symbol is missing
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        msg = load().slayer_b200_last_error()
+        raise SlayerB200Error("%s failed (%d): %s" % (what, rc, (msg or b"").decode()))
+
+
+def call(name, *args):
+    """Call an entry point by name and raise SlayerB200Error on a non-zero return code."""
+    rc = getattr(load(), name)(*args)
+    check(rc, name)

@@ -1,0 +1,141 @@
+// Python module `slayerCuda`: the reference's operator names and signatures
+// (src/cuda/slayerKernels.cu:136-145) on top of the slayer_b200 C ABI.
+//
+// Differences from the reference shim, all deliberate:
+//   - work is enqueued on PyTorch's current stream under a device guard (the reference uses
+//     the legacy default stream and leaves the device switched);
+//   - a one-element shift tensor is read on the device (no host synchronisation);
+//   - the per-neuron shift covers the whole batch in one launch;
+//   - dtype is checked explicitly;
+//   - two additional operators are exported: spikeGrad and spikeGrad_ (in place).
+#include "bindings_common.h"
+
+using namespace sb200py;
+
+static torch::Tensor getSpikesCuda(torch::Tensor d_u, const torch::Tensor &d_nu, const float theta, const float Ts)
+{
+    check_input(d_u, "d_u");
+    check_input(d_nu, "d_nu");
+    check_device(d_u, d_nu, "d_u", "d_nu");
+    TORCH_CHECK_INDEX(d_u.dim() >= 4, "getSpikes expects a tensor with at least 4 dimensions (NCHWT), got ", d_u.dim());
+    c10::cuda::CUDAGuard guard(d_u.device());
+    auto d_s = torch::empty_like(d_u);
+    const int64_t Ns = d_u.size(-1);
+    const int64_t rows = Ns ? d_u.numel() / Ns : 0;
+    const int64_t nuSize = d_nu.dim() ? d_nu.size(-1) : 1;
+    check_rc(slayer_b200_srm_get_spikes(d_s.data_ptr<float>(), d_u.data_ptr<float>(), d_nu.data_ptr<float>(),
+                                        rows, nuSize, Ns, theta, Ts, current_stream()),
+             "getSpikes");
+    return d_s;
+}
+
+static torch::Tensor convCuda(torch::Tensor input, torch::Tensor filter, float Ts)
+{
+    check_input(input, "input");
+    check_input(filter, "filter");
+    check_device(input, filter, "input", "filter");
+    c10::cuda::CUDAGuard guard(input.device());
+    auto output = torch::empty_like(input);
+    const int64_t T = input.size(-1);
+    const int64_t rows = T ? input.numel() / T : 0;
+    check_rc(slayer_b200_conv(output.data_ptr<float>(), input.data_ptr<float>(), filter.data_ptr<float>(),
+                              rows, T, filter.numel(), Ts, current_stream()),
+             "conv");
+    return output;
+}
+
+static torch::Tensor corrCuda(torch::Tensor input, torch::Tensor filter, float Ts)
+{
+    check_input(input, "input");
+    check_input(filter, "filter");
+    check_device(input, filter, "input", "filter");
+    c10::cuda::CUDAGuard guard(input.device());
+    auto output = torch::empty_like(input);
+    const int64_t T = input.size(-1);
+    const int64_t rows = T ? input.numel() / T : 0;
+    check_rc(slayer_b200_corr(output.data_ptr<float>(), input.data_ptr<float>(), filter.data_ptr<float>(),
+                              rows, T, filter.numel(), Ts, current_stream()),
+             "corr");
+    return output;
+}
+
+static torch::Tensor shiftCuda(torch::Tensor input, torch::Tensor shiftLUT, float Ts)
+{
+    check_input(input, "input");
+    check_input(shiftLUT, "shiftLUT");
+    check_device(input, shiftLUT, "input", "shiftLUT");
+    c10::cuda::CUDAGuard guard(input.device());
+    auto output = torch::empty_like(input);
+    const int64_t T = input.size(-1);
+    const int64_t rows = T ? input.numel() / T : 0;
+    if (shiftLUT.numel() == 1) {
+        // same amount for every row; the value stays on the device
+        check_rc(slayer_b200_shift_lut(output.data_ptr<float>(), input.data_ptr<float>(),
+                                       shiftLUT.data_ptr<float>(), rows, 1, T, Ts, current_stream()),
+                 "shift");
+    } else {
+        const int64_t nBatch = input.size(0);
+        const int64_t nNeurons = nBatch ? rows / nBatch : 0;
+        TORCH_CHECK(shiftLUT.numel() == nNeurons, "shift and number of neurons must be same");
+        check_rc(slayer_b200_shift_lut(output.data_ptr<float>(), input.data_ptr<float>(),
+                                       shiftLUT.data_ptr<float>(), nBatch, nNeurons, T, Ts, current_stream()),
+                 "shift");
+    }
+    return output;
+}
+
+static torch::Tensor shift1Cuda(torch::Tensor input, torch::Tensor shiftLUT) { return shiftCuda(input, shiftLUT, 1.0f); }
+
+static torch::Tensor shiftFlCuda(torch::Tensor input, float shiftValue, float Ts)
+{
+    check_input(input, "input");
+    c10::cuda::CUDAGuard guard(input.device());
+    auto output = torch::empty_like(input);
+    const int64_t T = input.size(-1);
+    const int64_t rows = T ? input.numel() / T : 0;
+    check_rc(slayer_b200_shift_scalar(output.data_ptr<float>(), input.data_ptr<float>(), shiftValue,
+                                      rows, T, Ts, current_stream()),
+             "shift");
+    return output;
+}
+
+static torch::Tensor shiftFl1Cuda(torch::Tensor input, float shiftValue) { return shiftFlCuda(input, shiftValue, 1.0f); }
+
+static torch::Tensor spikeGradImpl(torch::Tensor out, const torch::Tensor &gradOut, const torch::Tensor &u,
+                                   float theta, float tau, float scale)
+{
+    check_input(gradOut, "gradOutput");
+    check_input(u, "membranePotential");
+    check_device(gradOut, u, "gradOutput", "membranePotential");
+    TORCH_CHECK(gradOut.numel() == u.numel(), "gradOutput and membranePotential must have the same number of elements");
+    c10::cuda::CUDAGuard guard(gradOut.device());
+    check_rc(slayer_b200_spike_grad(out.data_ptr<float>(), gradOut.data_ptr<float>(), u.data_ptr<float>(),
+                                    gradOut.numel(), theta, tau, scale, current_stream()),
+             "spikeGrad");
+    return out;
+}
+
+static torch::Tensor spikeGradCuda(torch::Tensor gradOut, torch::Tensor u, float theta, float tau, float scale)
+{
+    return spikeGradImpl(torch::empty_like(gradOut), gradOut, u, theta, tau, scale);
+}
+
+static torch::Tensor spikeGradInplaceCuda(torch::Tensor gradOut, torch::Tensor u, float theta, float tau, float scale)
+{
+    return spikeGradImpl(gradOut, gradOut, u, theta, tau, scale);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
+{
+    m.def("getSpikes", &getSpikesCuda, "Get spikes (CUDA)");
+    m.def("conv", &convCuda, "Convolution in time (CUDA)");
+    m.def("corr", &corrCuda, "Correlation in time (CUDA)");
+    m.def("shift", &shiftCuda, "Element shift in time (CUDA)");
+    m.def("shift", &shift1Cuda, "Element shift in time (CUDA)");
+    m.def("shift", &shiftFlCuda, "Element shift in time (CUDA)");
+    m.def("shift", &shiftFl1Cuda, "Element shift in time (CUDA)");
+    m.def("spikeGrad", &spikeGradCuda,
+          "gradOutput * scale/tau * exp(-|u - theta| / tau) in one pass (CUDA)");
+    m.def("spikeGrad_", &spikeGradInplaceCuda, "In-place variant of spikeGrad (overwrites gradOutput)");
+    m.attr("backend") = "slayer_b200";
+}

@@ -1,0 +1,126 @@
+// Loihi CUBA neuron: fixed-point current / voltage decay, threshold and refractory delay.
+//
+// Per row, with integer state uOld = vOld = 0 and the neuron not refractory:
+//   t = 0:  s = v = u = 0 (the input sample is ignored)
+//   t >= 1: uT = sgn(uOld) * ((|uOld| * (4096 - iDecay)) >> 12) + (64 << wgtExp) * int(w[t])
+//           vT = sgn(vOld) * ((|vOld| * (4096 - vDecay)) >> 12) + uT
+//           the refractory state set by a spike at t' is cleared at the top of step t'+refDelay
+//           spike = vT > theta and not refractory
+//           vOld  = vT if neither refractory nor spiking, else 0;   uOld = uT
+//           outputs: s = spike, u = uT, v = vDecay at a spike else vOld
+// All products and the >> 12 are evaluated modulo 2^32 with a logical shift (the reference's
+// expressions mix int and unsigned operands), sgn(0) = +1, and outputs are float images of
+// the int32 values.  The reference re-reads its own spike output from refDelay steps back to
+// clear the refractory state; because a neuron cannot spike while refractory, that is
+// equivalent to the countdown kept in a register here.
+//
+// Memory: 16 algorithmic bytes per element (read w; write s, v, u), bound by HBM.  Same
+// warp-owned 32x32 tile scheme as the SRM kernel: the input tile is overwritten with the
+// current u, a second tile collects v, spikes leave as a bit mask.
+#include "common.cuh"
+#include "tile.cuh"
+
+namespace sb200 {
+
+__global__ void __launch_bounds__(256)
+loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
+                        int64_t rows, int T, unsigned weightScale, int theta,
+                        unsigned iKeep, unsigned vKeep, int vDecayMark, unsigned refDelay)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int warps_per_block = blockDim.x >> 5;
+    float *tile_u = smem + warp * (2 * kTileWords);
+    float *tile_v = tile_u + kTileWords;
+    const float vMarkF = (float)vDecayMark;
+
+    const int64_t nblocks = (rows + kTile - 1) / kTile;
+    const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
+    for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
+        const int64_t row0 = rb * kTile;
+        int uOld = 0, vOld = 0;
+        unsigned refLeft = 0;                // steps until the refractory state clears
+
+        for (int t0 = 0; t0 < T; t0 += kTile) {
+            tile_load(tile_u, w, row0, rows, t0, T, lane);
+            __syncwarp();
+
+            unsigned smask = 0u;
+#pragma unroll 1
+            for (int c4 = 0; c4 < kTile / 4; ++c4) {
+                float4 *cu = reinterpret_cast<float4 *>(tile_u + tile_chunk(lane, c4));
+                float4 *cv = reinterpret_cast<float4 *>(tile_v + tile_chunk(lane, c4));
+                const float4 in4 = *cu;
+                const float wv[4] = {in4.x, in4.y, in4.z, in4.w};
+                float uo[4], vo[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (t0 == 0 && c4 == 0 && j == 0) {   // t = 0
+                        uo[j] = 0.0f;
+                        vo[j] = 0.0f;
+                        continue;
+                    }
+                    const unsigned uSign = uOld >= 0 ? 1u : 0xffffffffu;
+                    const unsigned vSign = vOld >= 0 ? 1u : 0xffffffffu;
+                    const unsigned uT = uSign * ((uSign * (unsigned)uOld * iKeep) >> 12)
+                                      + weightScale * (unsigned)__float2int_rz(wv[j]);
+                    const unsigned vT = vSign * ((vSign * (unsigned)vOld * vKeep) >> 12) + uT;
+                    const int vTemp = (int)vT;
+
+                    if (refLeft != 0) --refLeft;
+                    const bool refractory = refLeft != 0;
+                    const bool spk = (vTemp > theta) && !refractory;
+                    vOld = (refractory || spk) ? 0 : vTemp;
+                    if (spk) refLeft = refDelay;
+                    uOld = (int)uT;
+
+                    smask |= (spk ? 1u : 0u) << (c4 * 4 + j);
+                    uo[j] = (float)uOld;
+                    vo[j] = spk ? vMarkF : (float)vOld;
+                }
+                *cu = make_float4(uo[0], uo[1], uo[2], uo[3]);
+                *cv = make_float4(vo[0], vo[1], vo[2], vo[3]);
+            }
+            __syncwarp();
+
+            tile_store(tile_u, u, row0, rows, t0, T, lane);
+            tile_store(tile_v, v, row0, rows, t0, T, lane);
+            mask_store(smask, 1.0f, s, row0, rows, t0, T, lane);
+            __syncwarp();
+        }
+    }
+}
+
+}  // namespace sb200
+
+extern "C" int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const float *w,
+                                            int64_t rows, int64_t T,
+                                            uint32_t wgtExp, uint32_t theta, uint32_t iDecay,
+                                            uint32_t vDecay, uint32_t refDelay, void *stream_)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(rows >= 0 && T >= 0, "loihi_get_spikes: negative size");
+    SB200_REQUIRE(T < (1LL << 31) - 64, "loihi_get_spikes: T=%lld too large", (long long)T);
+    SB200_REQUIRE(refDelay >= 1, "loihi_get_spikes: refDelay must be >= 1");
+    SB200_REQUIRE(wgtExp <= 25, "loihi_get_spikes: wgtExp=%u out of range", wgtExp);
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    SB200_REQUIRE(s && v && u && w, "loihi_get_spikes: null pointer");
+    SB200_REQUIRE(s != v && s != u && v != u && s != w && v != w,
+                  "loihi_get_spikes: output buffers must be distinct");
+    cudaStream_t stream = (cudaStream_t)stream_;
+
+    const int64_t nblocks = ceil_div(rows, kTile);
+    const int sms = sm_count();
+    int warps = 8;
+    while (warps > 1 && ceil_div(nblocks, warps) < 2 * (int64_t)sms) warps >>= 1;
+    int64_t grid = ceil_div(nblocks, warps);
+    const int64_t cap = (int64_t)sms * 16;
+    if (grid > cap) grid = cap;
+    const size_t smem = (size_t)warps * 2 * kTileWords * sizeof(float);
+    loihi_get_spikes_kernel<<<(unsigned)grid, warps * 32, smem, stream>>>(
+        s, v, u, w, rows, (int)T, 1u << (6 + wgtExp), (int)theta,
+        4096u - iDecay, 4096u - vDecay, (int)vDecay, refDelay);
+    return check_launch("loihi_get_spikes kernel launch");
+}

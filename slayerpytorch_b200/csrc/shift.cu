@@ -1,0 +1,141 @@
+// Axonal-delay time shift: out[r,t] = in[r,t-d_r], zero filled, d_r = trunc(shift_r / Ts).
+//
+// Pure data movement, bound by HBM bandwidth (8 algorithmic bytes per element).  One launch
+// covers every row of the batch; the per-neuron table is indexed by row % nNeurons.
+//
+// Work split: a group of LPR lanes (a power of two, up to a full warp) owns one row and
+// strides along time, so every global access of a group is contiguous.  When the row length
+// is a multiple of four and both buffers are 16-byte aligned, every access is a 128-bit
+// vector: the store is aligned, and the shifted source vector is assembled from the two
+// aligned source vectors that straddle it.  Because T % 4 == 0, an aligned source vector is
+// either wholly inside its row or wholly outside, so zero fill stays exact.
+#include "common.cuh"
+
+namespace sb200 {
+
+template <bool LUT>
+__global__ void __launch_bounds__(256)
+shift_vec4_kernel(float4 *__restrict__ out, const float4 *__restrict__ in,
+                  const float *__restrict__ lut, float shift, float Ts,
+                  int64_t rows, int T4, int64_t nNeurons, int lpr_log2)
+{
+    const int lpr = 1 << lpr_log2;
+    const int lane_in_row = threadIdx.x & (lpr - 1);
+    const int64_t groups_per_block = blockDim.x >> lpr_log2;
+    const int64_t group0 = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> lpr_log2);
+    const int64_t group_stride = (int64_t)gridDim.x * groups_per_block;
+    const int T = T4 * 4;
+
+    for (int64_t row = group0; row < rows; row += group_stride) {
+        const float sv = LUT ? __ldg(lut + (row % nNeurons)) : shift;
+        const int d = shift_steps(sv, Ts);
+        const float4 *src = in + row * T4;
+        float4 *dst = out + row * T4;
+        if (d >= T || d <= -T) {
+            for (int q = lane_in_row; q < T4; q += lpr) dst[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            continue;
+        }
+        // source element index of output element 4q is 4q - d = 4*(q + a) + o, o in [0,3]
+        const int a = (-d) >> 2;          // arithmetic shift = floor division
+        const int o = (-d) & 3;
+#pragma unroll 2
+        for (int q = lane_in_row; q < T4; q += lpr) {
+            const int q0 = q + a;
+            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+            if (q0 >= 0 && q0 < T4) v0 = __ldg(src + q0);
+            if (o != 0 && q0 + 1 >= 0 && q0 + 1 < T4) v1 = __ldg(src + q0 + 1);
+            float4 r;
+            switch (o) {
+                case 0:  r = v0; break;
+                case 1:  r = make_float4(v0.y, v0.z, v0.w, v1.x); break;
+                case 2:  r = make_float4(v0.z, v0.w, v1.x, v1.y); break;
+                default: r = make_float4(v0.w, v1.x, v1.y, v1.z); break;
+            }
+            dst[q] = r;
+        }
+    }
+}
+
+template <bool LUT>
+__global__ void __launch_bounds__(256)
+shift_scalar_kernel(float *__restrict__ out, const float *__restrict__ in,
+                    const float *__restrict__ lut, float shift, float Ts,
+                    int64_t rows, int T, int64_t nNeurons, int lpr_log2)
+{
+    const int lpr = 1 << lpr_log2;
+    const int lane_in_row = threadIdx.x & (lpr - 1);
+    const int64_t groups_per_block = blockDim.x >> lpr_log2;
+    const int64_t group0 = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> lpr_log2);
+    const int64_t group_stride = (int64_t)gridDim.x * groups_per_block;
+
+    for (int64_t row = group0; row < rows; row += group_stride) {
+        const float sv = LUT ? __ldg(lut + (row % nNeurons)) : shift;
+        const int d = shift_steps(sv, Ts);
+        const float *src = in + row * T;
+        float *dst = out + row * T;
+#pragma unroll 4
+        for (int t = lane_in_row; t < T; t += lpr) {
+            const int64_t id = (int64_t)t - d;
+            dst[t] = (id >= 0 && id < T) ? __ldg(src + id) : 0.0f;
+        }
+    }
+}
+
+static int launch_shift(float *out, const float *in, const float *lut, float shift, float Ts,
+                        int64_t rows, int64_t T, int64_t nNeurons, cudaStream_t stream)
+{
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    const bool vec = (T % 4 == 0) && aligned16(out) && aligned16(in);
+    const int64_t units = vec ? T / 4 : T;       // accesses per row
+    int lpr_log2 = 0;
+    while ((1 << lpr_log2) < units && lpr_log2 < 5) ++lpr_log2;
+    const int threads = 256;
+    const int64_t groups_per_block = threads >> lpr_log2;
+    int64_t blocks = ceil_div(rows, groups_per_block);
+    const int64_t cap = (int64_t)sm_count() * 8 * 4;   // a few waves of resident CTAs
+    if (blocks > cap) blocks = cap;
+    if (vec) {
+        if (lut)
+            shift_vec4_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(
+                (float4 *)out, (const float4 *)in, lut, 0.f, Ts, rows, (int)(T / 4), nNeurons, lpr_log2);
+        else
+            shift_vec4_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>(
+                (float4 *)out, (const float4 *)in, nullptr, shift, Ts, rows, (int)(T / 4), 1, lpr_log2);
+    } else {
+        if (lut)
+            shift_scalar_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(
+                out, in, lut, 0.f, Ts, rows, (int)T, nNeurons, lpr_log2);
+        else
+            shift_scalar_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>(
+                out, in, nullptr, shift, Ts, rows, (int)T, 1, lpr_log2);
+    }
+    return check_launch("shift kernel launch");
+}
+
+}  // namespace sb200
+
+extern "C" int slayer_b200_shift_scalar(float *out, const float *in, float shift,
+                                        int64_t rows, int64_t T, float Ts, void *stream)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(rows >= 0 && T >= 0, "shift: negative size (rows=%lld, T=%lld)", (long long)rows, (long long)T);
+    SB200_REQUIRE(T < (1LL << 31) - 8, "shift: T=%lld too large", (long long)T);
+    SB200_REQUIRE(rows == 0 || T == 0 || (out && in), "shift: null pointer");
+    SB200_REQUIRE(out != in || rows == 0 || T == 0, "shift: out must not alias in");
+    return launch_shift(out, in, nullptr, shift, Ts, rows, T, 1, (cudaStream_t)stream);
+}
+
+extern "C" int slayer_b200_shift_lut(float *out, const float *in, const float *lut,
+                                     int64_t nBatch, int64_t nNeurons, int64_t T, float Ts, void *stream)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(nBatch >= 0 && nNeurons >= 0 && T >= 0, "shift: negative size");
+    SB200_REQUIRE(T < (1LL << 31) - 8, "shift: T=%lld too large", (long long)T);
+    const int64_t rows = nBatch * nNeurons;
+    SB200_REQUIRE(rows == 0 || T == 0 || (out && in && lut), "shift: null pointer");
+    SB200_REQUIRE(out != in || rows == 0 || T == 0, "shift: out must not alias in");
+    if (rows == 0) return SLAYER_B200_OK;
+    return launch_shift(out, in, lut, 0.f, Ts, rows, T, nNeurons, (cudaStream_t)stream);
+}

@@ -1,0 +1,76 @@
+"""Helpers for the GPU parity tests: device buffers through torch, calls through the C ABI."""
+import ctypes
+
+import numpy as np
+import torch
+
+from slayerpytorch_b200 import capi
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.detach().cpu().numpy()
+
+
+def ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def rows_T(t):
+    T = t.shape[-1]
+    return (t.numel() // T if T else 0), T
+
+
+def c_conv(x, f, Ts, corr=False):
+    out = torch.empty_like(x)
+    rows, T = rows_T(x)
+    capi.call("slayer_b200_corr" if corr else "slayer_b200_conv",
+              ptr(out), ptr(x), ptr(f), rows, T, f.numel(), float(Ts), stream())
+    return out
+
+
+def c_shift_scalar(x, d, Ts):
+    out = torch.empty_like(x)
+    rows, T = rows_T(x)
+    capi.call("slayer_b200_shift_scalar", ptr(out), ptr(x), float(d), rows, T, float(Ts), stream())
+    return out
+
+
+def c_shift_lut(x, lut, Ts):
+    out = torch.empty_like(x)
+    rows, T = rows_T(x)
+    nb = x.shape[0]
+    capi.call("slayer_b200_shift_lut", ptr(out), ptr(x), ptr(lut), nb, rows // nb, T, float(Ts), stream())
+    return out
+
+
+def c_srm(u, nu, theta, Ts):
+    """In place on u; returns s."""
+    s = torch.empty_like(u)
+    rows, T = rows_T(u)
+    capi.call("slayer_b200_srm_get_spikes", ptr(s), ptr(u), ptr(nu), rows, nu.numel(), T,
+              float(theta), float(Ts), stream())
+    return s
+
+
+def c_loihi(w, wgtExp, theta, iDecay, vDecay, refDelay):
+    s, v, u = torch.empty_like(w), torch.empty_like(w), torch.empty_like(w)
+    rows, T = rows_T(w)
+    capi.call("slayer_b200_loihi_get_spikes", ptr(s), ptr(v), ptr(u), ptr(w), rows, T,
+              int(wgtExp), int(theta), int(iDecay), int(vDecay), int(refDelay), stream())
+    return s, v, u
+
+
+def c_spike_grad(g, u, theta, tau, scale):
+    out = torch.empty_like(g)
+    capi.call("slayer_b200_spike_grad", ptr(out), ptr(g), ptr(u), g.numel(),
+              float(theta), float(tau), float(scale), stream())
+    return out

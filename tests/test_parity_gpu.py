@@ -1,0 +1,329 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle.
+
+Integer / index / copy work (shift, spike positions, the updated SRM potential, all Loihi
+outputs) must be bit-exact.  conv / corr reproduce the oracle's fused-multiply-add chain and
+are also compared bit for bit; the stated tolerance of the task (1e-5 relative) is the
+fallback assertion should a platform differ.  spike_grad is held to 1e-5 relative.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_oracle as co
+from tests import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-5   # tolerance for floating-point values (conv, corr, shift values, gradients)
+
+
+def setup_module(module):
+    co.set_ftz(True)       # the FIR and SRM kernels flush denormals like the reference build
+
+
+def teardown_module(module):
+    co.set_ftz(False)
+
+
+def assert_close_or_equal(got, want):
+    if np.array_equal(got, want):
+        return
+    scale = np.maximum(np.abs(want), 1e-30)
+    worst = np.max(np.abs(got - want) / scale)
+    np.testing.assert_allclose(got, want, rtol=REL, atol=1e-30)
+    pytest.fail("within %g relative but not bit-exact (worst %.3g)" % (REL, worst))
+
+
+# ------------------------------------------------------------------------------- shift
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1, 1), (2, 3, 1, 1, 7), (3, 5, 2, 1, 300),
+                                   (2, 7, 1, 3, 1450), (1, 33, 1, 1, 2000), (4, 9, 1, 1, 64)])
+def test_shift_scalar(shape):
+    rng = np.random.RandomState(sum(shape))
+    x = rng.randn(*shape).astype(np.float32)
+    xd = G.dev(x)
+    T = shape[-1]
+    for d in sorted({0, 1, -1, 2, 3, -3, 4, 5, T - 1, -(T - 1), T, -T, 3 * T, -3 * T, 2.7, -2.7}):
+        for Ts in (1.0, 0.1):
+            got = G.host(G.c_shift_scalar(xd, d, Ts))
+            np.testing.assert_array_equal(got, co.shift(x, d, Ts), err_msg="d=%s Ts=%s" % (d, Ts))
+
+
+@pytest.mark.parametrize("shape,Ts", [((5, 10, 4, 3, 500), 0.1), ((3, 16, 1, 1, 300), 1.0),
+                                      ((2, 6, 2, 2, 1450), 1.0), ((4, 130, 1, 1, 30), 1.0),
+                                      ((2, 3, 1, 1, 5), 0.5)])
+def test_shift_per_neuron(shape, Ts):
+    """Recipe of test/test_slayer009.py: delays in (-1, 1) at Ts = 0.1, plus wider ranges."""
+    rng = np.random.RandomState(42 + shape[-1])
+    x = rng.randn(*shape).astype(np.float32)
+    for span in (1.0, 5.0, 2.0 * shape[-1] * Ts):
+        lut = ((rng.rand(*shape[1:4]) * 2 - 1) * span).astype(np.float32)
+        got = G.host(G.c_shift_lut(G.dev(x), G.dev(lut), Ts))
+        np.testing.assert_array_equal(got, co.shift(x, lut, Ts))
+
+
+def test_shift_unaligned_buffers_take_the_scalar_path():
+    rng = np.random.RandomState(7)
+    flat = rng.randn(4 * 300 + 3).astype(np.float32)
+    base = G.dev(flat)
+    for off in (1, 2, 3):
+        xd = base[off:off + 1200].view(1, 4, 1, 1, 300)
+        x = flat[off:off + 1200].reshape(1, 4, 1, 1, 300)
+        np.testing.assert_array_equal(G.host(G.c_shift_scalar(xd, 3, 1.0)), co.shift(x, 3, 1.0))
+
+
+# --------------------------------------------------------------------------- conv / corr
+@pytest.mark.parametrize("T", [1, 5, 64, 300, 301, 500, 1450, 2000])
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 11, 12, 13, 77, 110, 160])
+def test_conv_corr_bit_exact(T, K):
+    rng = np.random.RandomState(1000 * T + K)
+    rows = 37 if T < 1000 else 33
+    x = (rng.rand(rows, T) < 0.2).astype(np.float32) * rng.randn(rows, T).astype(np.float32)
+    f = rng.randn(K).astype(np.float32)
+    xd, fd = G.dev(x), G.dev(f)
+    for Ts in (1.0, 0.1):
+        assert_close_or_equal(G.host(G.c_conv(xd, fd, Ts)), co.conv(x, f, Ts))
+        assert_close_or_equal(G.host(G.c_conv(xd, fd, Ts, corr=True)), co.corr(x, f, Ts))
+
+
+def test_conv_delay_gradient_filter():
+    """K = 2 difference filter of the delay gradient (src/slayer.py:950-953): (x[t-1]-x[t])/Ts."""
+    rng = np.random.RandomState(3)
+    x = rng.randn(2, 5, 1, 1, 300).astype(np.float32)
+    f = (np.array([-1, 1], np.float32) / np.float32(0.1))
+    got = G.host(G.c_conv(G.dev(x), G.dev(f), 1))
+    assert_close_or_equal(got, co.conv(x, f, 1))
+    want = np.zeros_like(x)
+    want[..., 0] = -x[..., 0] * 10
+    want[..., 1:] = (x[..., :-1] - x[..., 1:]) * 10
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)
+
+
+def test_conv_spike_input_and_psp_kernel(golden_dir):
+    g = np.load(golden_dir + "/ref_python.npz")
+    for tag, kern in (("psp_Ts1", "srm_Ts1_srmKernel"), ("psp_kat", "srm_kat_srmKernel")):
+        x, y, Ts = g[tag + "_in"], g[tag + "_out"], float(g[tag + "_Ts"])
+        got = G.host(G.c_conv(G.dev(x), G.dev(g[kern]), Ts))
+        assert np.linalg.norm(got - y) / y.size < 1e-6      # test/test_slayer011.py:39-43
+        assert_close_or_equal(got, co.conv(x, g[kern], Ts))
+
+
+def test_conv_many_rows_and_row_remainders():
+    rng = np.random.RandomState(5)
+    f = rng.randn(77).astype(np.float32)
+    fd = G.dev(f)
+    for rows in (1, 31, 32, 33, 1000):
+        x = rng.randn(rows, 300).astype(np.float32)
+        assert_close_or_equal(G.host(G.c_conv(G.dev(x), fd, 1.0)), co.conv(x, f, 1.0))
+        assert_close_or_equal(G.host(G.c_conv(G.dev(x), fd, 1.0, corr=True)), co.corr(x, f, 1.0))
+
+
+def test_conv_unaligned_buffer():
+    rng = np.random.RandomState(8)
+    flat = rng.randn(9 * 300 + 1).astype(np.float32)
+    f = rng.randn(11).astype(np.float32)
+    xd = G.dev(flat)[1:].view(9, 300)
+    assert_close_or_equal(G.host(G.c_conv(xd, G.dev(f), 1.0)), co.conv(flat[1:].reshape(9, 300), f, 1.0))
+
+
+def test_conv_very_long_filter_fallback():
+    rng = np.random.RandomState(9)
+    x = rng.randn(3, 2500).astype(np.float32)
+    f = (rng.randn(2300) * 0.05).astype(np.float32)
+    assert_close_or_equal(G.host(G.c_conv(G.dev(x), G.dev(f), 1.0)), co.conv(x, f, 1.0))
+    assert_close_or_equal(G.host(G.c_conv(G.dev(x), G.dev(f), 1.0, corr=True)), co.corr(x, f, 1.0))
+
+
+# ------------------------------------------------------------------------- SRM getSpikes
+def srm_case(rng, shape, nus, scale=8.0):
+    u = (rng.randn(*shape) * scale).astype(np.float32)
+    nu = (-np.abs(rng.randn(nus)) * 6).astype(np.float32)
+    return u, nu
+
+
+@pytest.mark.parametrize("T", [1, 2, 31, 32, 33, 300, 500, 2000])
+@pytest.mark.parametrize("nus", [1, 2, 11, 33, 34, 65, 110, 160, 257])
+def test_srm_get_spikes_bit_exact(T, nus):
+    rng = np.random.RandomState(T * 1000 + nus)
+    u, nu = srm_case(rng, (2, 3, 1, 7, T), nus)
+    ud = G.dev(u)
+    s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
+    s_want, u_want = co.srm_get_spikes(u, nu, 10.0, 1.0)
+    np.testing.assert_array_equal(s, s_want)
+    np.testing.assert_array_equal(G.host(ud).view(np.uint32), u_want.view(np.uint32))
+    assert T < 4 or s.sum() > 0
+
+
+def test_srm_long_refractory_kernel_fallback():
+    rng = np.random.RandomState(77)
+    u, nu = srm_case(rng, (1, 5, 1, 1, 700), 400)
+    ud = G.dev(u)
+    s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
+    s_want, u_want = co.srm_get_spikes(u, nu, 10.0, 1.0)
+    np.testing.assert_array_equal(s, s_want)
+    np.testing.assert_array_equal(G.host(ud), u_want)
+
+
+def test_srm_edge_values():
+    """theta hit exactly, nu[0] != 0, dense bursts (positive kernel), NaN / Inf rows, Ts != 1."""
+    rng = np.random.RandomState(123)
+    T = 100
+    u = (rng.randn(1, 6, 1, 1, T) * 5).astype(np.float32)
+    u[0, 0, 0, 0, ::7] = 10.0                      # exactly theta -> spike (>=)
+    u[0, 1, 0, 0, :] = 11.0                        # spikes everywhere unless suppressed
+    u[0, 2, 0, 0, 10] = np.nan
+    u[0, 3, 0, 0, 20] = np.inf
+    u[0, 4, 0, 0, 30] = -np.inf
+    u[0, 5, 0, 0, :] = -0.0
+    for nu in (np.array([0.5, -3, -2, -1], np.float32), np.array([1.0, 2.0, 0.5], np.float32),
+               np.array([-20.0], np.float32)):
+        for Ts in (1.0, 0.1, 2.0):
+            ud = G.dev(u)
+            s = G.host(G.c_srm(ud, G.dev(nu), 10.0, Ts))
+            s_want, u_want = co.srm_get_spikes(u, nu, 10.0, Ts)
+            np.testing.assert_array_equal(s > 0, s_want > 0)
+            np.testing.assert_allclose(s, s_want, rtol=1e-6)
+            np.testing.assert_array_equal(G.host(ud).view(np.uint32), u_want.view(np.uint32))
+
+
+def test_srm_trace_of_reference_fixture(golden_dir):
+    """test/test_slayer002.py:153-167 on the MATLAB trace, now on the GPU."""
+    srm = np.load(golden_dir + "/srm_kat.npz")
+    nu = np.load(golden_dir + "/ref_python.npz")["srm_kat_refKernel"]
+    for key in ("spikeFuncHid", "spikeFuncOut"):
+        data = srm[key][:500]
+        ud = G.dev(data[:, 0].reshape(1, 1, 1, 1, -1))
+        s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 0.1)).ravel()
+        np.testing.assert_array_equal(s > 0, data[:, 2] > 0)
+        np.testing.assert_allclose(G.host(ud).ravel(), data[:, 1], atol=2e-3)
+
+
+# ----------------------------------------------------------------------- Loihi getSpikes
+@pytest.mark.parametrize("T", [1, 2, 33, 200, 1450])
+@pytest.mark.parametrize("params", [(0, 5120, 1024, 128, 1), (0, 5120, 1024, 128, 2),
+                                    (0, 5120, 1024, 128, 17), (1, 2560, 2048, 256, 3),
+                                    (0, 320, 4095, 0, 63), (2, 100, 0, 4096, 5)])
+def test_loihi_get_spikes_bit_exact(T, params):
+    rng = np.random.RandomState(T + sum(params))
+    w = (np.round((rng.rand(3, 11, 1, 2, T) - 0.5) * 60) * (rng.rand(3, 11, 1, 2, T) < 0.3)).astype(np.float32)
+    got = G.c_loihi(G.dev(w), *params)
+    want = co.loihi_get_spikes(w, *params)
+    for a, b, name in zip(got, want, ("spike", "voltage", "current")):
+        np.testing.assert_array_equal(G.host(a), b, err_msg=name)
+
+
+def test_loihi_wraparound_negative_currents_and_fractions():
+    rng = np.random.RandomState(55)
+    w = np.round(rng.randn(40, 300) * 3e5).astype(np.float32)
+    w[::3] *= -1
+    w[1] = (rng.randn(300) * 3.7).astype(np.float32)          # int() truncates toward zero
+    got = G.c_loihi(G.dev(w), 1, 5120, 10, 3, 2)
+    want = co.loihi_get_spikes(w, 1, 5120, 10, 3, 2)
+    for a, b in zip(got, want):
+        np.testing.assert_array_equal(G.host(a), b)
+
+
+def test_loihi_reference_numpy_model_fixture(golden_dir):
+    g = np.load(golden_dir + "/ref_python.npz")
+    for k in range(int(g["nrn_count"])):
+        p = [int(v) for v in g["nrn%d_params" % k]]
+        s, v, u = G.c_loihi(G.dev(g["nrn%d_w" % k]), *p)
+        np.testing.assert_array_equal(G.host(s), g["nrn%d_spike" % k])
+        np.testing.assert_array_equal(G.host(u), g["nrn%d_current" % k])
+        np.testing.assert_array_equal(G.host(v), g["nrn%d_voltage" % k])
+
+
+# ---------------------------------------------------------------------------- spike_grad
+@pytest.mark.parametrize("n", [1, 3, 4, 1023, 4096 + 5])
+def test_spike_grad(n):
+    rng = np.random.RandomState(n)
+    g = rng.randn(n).astype(np.float32)
+    u = (rng.randn(n) * 30).astype(np.float32)
+    for theta, tau, scale in ((10.0, 10.0, 1.0), (10.0, 1.0, 1.0), (5120.0, 5120.0, 1 / 195.0)):
+        got = G.host(G.c_spike_grad(G.dev(g), G.dev(u), theta, tau, scale))
+        want = co.spike_grad(g, u, theta, tau, scale)
+        np.testing.assert_allclose(got, want, rtol=REL, atol=1e-37)
+        # and against the tensor expression it replaces (src/slayer.py:862)
+        ut, gt = torch.from_numpy(u).cuda(), torch.from_numpy(g).cuda()
+        th, ta, sc = (torch.tensor(v, device="cuda", dtype=torch.float32) for v in (theta, tau, scale))
+        ref = gt * (sc / ta * torch.exp(-torch.abs(ut - th) / ta))
+        np.testing.assert_allclose(got, ref.cpu().numpy(), rtol=REL, atol=1e-37)
+
+
+# ------------------------------------------- full-size runs checked on a random row sample
+def sample_rows(rows, n, seed):
+    return np.sort(np.random.RandomState(seed).choice(rows, size=min(n, rows), replace=False))
+
+
+def test_full_size_config2_chain_rows_match_oracle(golden_dir):
+    """BASELINE config 2 layer-1 tensors (64 x 512 neurons x 300 steps): psp -> getSpikes ->
+    per-neuron shift, then shift^-1 -> surrogate -> corr, run at full size on the GPU and
+    checked exactly on 1500 random rows (rows are independent)."""
+    g = np.load(golden_dir + "/ref_python.npz")
+    srm_k, ref_k = g["srm_Ts1_srmKernel"], g["srm_Ts1_refKernel"]
+    gen = torch.Generator().manual_seed(1002)
+    N, C, T = 64, 512, 300
+    a = (torch.randn(N, C, 1, 1, T, generator=gen).abs() * 2.5 * (torch.rand(N, C, 1, 1, T, generator=gen) < 0.3)).float()
+    delay = (torch.rand(C, generator=gen) * 5).float()
+    grad = torch.randn(N, C, 1, 1, T, generator=gen).float()
+    ad, kd, rd, dd, gd = a.cuda(), G.dev(srm_k), G.dev(ref_k), delay.cuda(), grad.cuda()
+    u = G.c_conv(ad, kd, 1.0)
+    u_pre = u.clone()
+    s = G.c_srm(u, rd, 10.0, 1.0)
+    out = G.c_shift_lut(s, dd, 1.0)
+    g1 = G.c_shift_lut(gd, -dd, 1.0)
+    g2 = G.c_spike_grad(g1, u, 10.0, 10.0, 1.0)
+    g3 = G.c_conv(g2, kd, 1.0, corr=True)
+    rows = sample_rows(N * C, 1500, 1)
+    pick = lambda t: G.host(t).reshape(N * C, T)[rows]
+    an, gn = a.numpy().reshape(N * C, T)[rows], grad.numpy().reshape(N * C, T)[rows]
+    dn = delay.numpy()[rows % C]
+    u0 = co.conv(an, srm_k, 1.0)
+    assert_close_or_equal(pick(u_pre), u0)
+    s_w, u_w = co.srm_get_spikes(u0, ref_k, 10.0, 1.0)
+    np.testing.assert_array_equal(pick(s), s_w)
+    np.testing.assert_array_equal(pick(u), u_w)
+    assert 0.001 < s_w.mean() < 0.5
+    out_w = np.stack([co.shift(s_w[i:i + 1], dn[i], 1.0)[0] for i in range(len(rows))])
+    np.testing.assert_array_equal(pick(out), out_w)
+    g1_w = np.stack([co.shift(gn[i:i + 1], -dn[i], 1.0)[0] for i in range(len(rows))])
+    np.testing.assert_array_equal(pick(g1), g1_w)
+    g2_w = co.spike_grad(g1_w, u_w, 10.0, 10.0, 1.0)
+    np.testing.assert_allclose(pick(g2), g2_w, rtol=REL, atol=1e-37)
+    assert_close_or_equal(pick(g3), co.corr(pick(g2), srm_k, 1.0))
+    # size-independent properties over the whole tensors
+    assert torch.all((s == 0) | (s == 1.0))
+    back = G.c_shift_lut(out, -dd, 1.0)                         # shift then un-shift: head survives
+    dsteps = dd.floor().long().view(1, C, 1, 1, 1)
+    tt = torch.arange(T, device="cuda").view(1, 1, 1, 1, T)
+    keep = tt < (T - dsteps)
+    assert torch.equal(back * keep, s * keep)
+
+
+def test_full_size_loihi_layer_rows_match_oracle():
+    """A config-5-like Loihi layer (8 x 32 x 16 x 16 neurons x 1450 steps, T % 4 != 0)."""
+    gen = torch.Generator().manual_seed(1005)
+    shape = (8, 32, 16, 16, 1450)
+    w = (torch.randint(-128, 128, shape, generator=gen) * (torch.rand(shape, generator=gen) < 0.08)).float()
+    s, v, u = G.c_loihi(w.cuda(), 0, 5120, 1024, 128, 1)
+    rows_total = 8 * 32 * 16 * 16
+    rows = sample_rows(rows_total, 1000, 2)
+    wn = w.numpy().reshape(rows_total, 1450)[rows]
+    want = co.loihi_get_spikes(wn, 0, 5120, 1024, 128, 1)
+    for a, b in zip((s, v, u), want):
+        np.testing.assert_array_equal(G.host(a).reshape(rows_total, 1450)[rows], b)
+    assert 0.0005 < want[0].mean() < 0.5
+    sh = G.c_shift_scalar(s, 1, 1)
+    assert torch.equal(sh[..., 1:], s[..., :-1]) and not sh[..., 0].any()
+
+
+def test_linearity_and_adjointness_at_full_size():
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(4096, 2000, generator=gen).cuda()
+    y = torch.randn(4096, 2000, generator=gen).cuda()
+    f = torch.randn(77, generator=gen).cuda()
+    cx = G.c_conv(x, f, 1.0)
+    lhs = (cx.double() * y.double()).sum()
+    rhs = (x.double() * G.c_conv(y, f, 1.0, corr=True).double()).sum()
+    assert abs(lhs - rhs) < 1e-6 * max(1.0, abs(lhs))
+    two = G.c_conv(2 * x, f, 1.0)
+    assert torch.equal(two, 2 * cx)        # scaling by a power of two is exact
