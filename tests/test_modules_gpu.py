@@ -1,0 +1,140 @@
+"""GPU: the Python operator modules (call conventions of the reference) and the mirror layer."""
+import numpy as np
+import pytest
+import torch
+
+import slayerpytorch_b200
+from oracle import cpu_oracle as co
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return slayerpytorch_b200.load_ops()
+
+
+def test_modules_are_the_native_build(ops):
+    assert ops[0].backend == "slayer_b200" and ops[1].backend == "slayer_b200"
+    assert ops[0].__file__.startswith(slayerpytorch_b200.lib_dir())
+
+
+def test_shift_overloads_and_argument_conversion(ops):
+    """Call patterns of the reference: (x, tensor, float) slayer.py:939; (x, -tensor, 0-dim cuda
+    tensor) :957; (x, 4, 1) ints, test_slayer009.py:66-68; 1-element tensor -> scalar path."""
+    sc = ops[0]
+    x = torch.randn(2, 3, 2, 1, 50).cuda()
+    xn = x.cpu().numpy()
+    lut = (torch.rand(3, 2, 1) * 6 - 3).cuda()
+    Ts0 = torch.tensor(0.5).cuda()
+    np.testing.assert_array_equal(sc.shift(x, lut, 0.5).cpu().numpy(), co.shift(xn, lut.cpu().numpy(), 0.5))
+    np.testing.assert_array_equal(sc.shift(x, -lut, Ts0).cpu().numpy(), co.shift(xn, -lut.cpu().numpy(), 0.5))
+    np.testing.assert_array_equal(sc.shift(x, lut).cpu().numpy(), co.shift(xn, lut.cpu().numpy(), 1.0))
+    np.testing.assert_array_equal(sc.shift(x, 4, 1).cpu().numpy(), co.shift(xn, 4, 1))
+    np.testing.assert_array_equal(sc.shift(x, 2.0).cpu().numpy(), co.shift(xn, 2.0, 1))
+    np.testing.assert_array_equal(sc.shift(x, torch.tensor([3.0]).cuda(), Ts0).cpu().numpy(), co.shift(xn, 3.0, 0.5))
+    with pytest.raises(TypeError):
+        sc.shift(x, "a")
+    with pytest.raises(RuntimeError):
+        sc.shift(x, lut.reshape(-1)[:4].contiguous(), 1.0)
+
+
+def test_input_checks_raise_runtime_error(ops):
+    sc, lc = ops
+    x = torch.randn(1, 2, 1, 1, 16)
+    f = torch.randn(3)
+    with pytest.raises(RuntimeError):
+        sc.conv(x, f.cuda(), 1.0)                       # CPU tensor
+    with pytest.raises(RuntimeError):
+        sc.conv(x.cuda().transpose(0, 1), f.cuda(), 1.0)  # not contiguous
+    with pytest.raises(RuntimeError):
+        sc.corr(x.cuda().double(), f.cuda(), 1.0)       # not float32
+    with pytest.raises(RuntimeError):
+        lc.getSpikes(x, 0, 80, 1, 1, 1)
+    with pytest.raises(TypeError):
+        lc.getSpikes(x.cuda(), 0, 80.5, 1, 1, 1)        # float where an unsigned is expected
+    with pytest.raises(TypeError):
+        lc.getSpikes(x.cuda(), 0, -80, 1, 1, 1)
+    with pytest.raises(RuntimeError):
+        lc.getSpikes(x.cuda(), 0, 80, 1, 1, 0)          # refDelay = 0 is rejected
+
+
+def test_get_spikes_updates_membrane_potential_in_place(ops):
+    u = (torch.randn(1, 4, 1, 1, 100) * 8).cuda()
+    before = u.clone()
+    nu = torch.tensor([0.0, -20.0, -14.0, -8.0]).cuda()
+    s = ops[0].getSpikes(u, nu, 10, 1)                  # ints convert to float like the reference
+    assert s.sum() > 0 and not torch.equal(u, before)
+    sw, uw = co.srm_get_spikes(before.cpu().numpy(), nu.cpu().numpy(), 10.0, 1.0)
+    np.testing.assert_array_equal(s.cpu().numpy(), sw)
+    np.testing.assert_array_equal(u.cpu().numpy(), uw)
+
+
+def test_conv_accepts_any_rank_and_filter_shape(ops):
+    x = torch.randn(6, 40).cuda()
+    f = torch.randn(2, 3).cuda()
+    got = ops[0].conv(x, f, torch.tensor(0.5).cuda())
+    np.testing.assert_allclose(got.cpu().numpy(), co.conv(x.cpu().numpy(), f.cpu().numpy().ravel(), 0.5), rtol=1e-5, atol=1e-6)
+
+
+def test_ops_run_on_the_current_stream(ops):
+    x = torch.randn(64, 128, 1, 1, 300).cuda()
+    f = torch.randn(77).cuda()
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        y = ops[0].conv(x, f, 1.0)
+        z = ops[0].shift(y, 3.0, 1.0)
+    st.synchronize()
+    want = co.shift(co.conv(x.cpu().numpy(), f.cpu().numpy(), 1.0), 3.0, 1.0)
+    np.testing.assert_allclose(z.cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_mirror_layer_gradient_kat(golden_dir):
+    """test/test_slayer003.py through this package's own layer API."""
+    from slayerpytorch_b200 import layer as L
+    srm = np.load(golden_dir + "/srm_kat.npz")
+    dev = torch.device("cuda")
+    neuron = {"type": "SRMALPHA", "theta": 10, "tauSr": 1.0, "tauRef": 1.0, "scaleRef": 2, "tauRho": 0.1, "scaleRho": 1}
+    sim = {"Ts": 0.1, "tSample": 50}
+    net = L.spikeLayer(neuron, sim, fullRefKernel=True).to(dev)
+    fc1, fc2 = net.dense(250, 25).to(dev), net.dense(25, 1).to(dev)
+    fc1.weight = torch.nn.Parameter(torch.from_numpy(srm["w1Initial"]).reshape(25, 250, 1, 1, 1).to(dev))
+    fc2.weight = torch.nn.Parameter(torch.from_numpy(srm["w2Initial"]).reshape(1, 25, 1, 1, 1).to(dev))
+
+    def events(idx, n):
+        x = np.zeros((n, 500), np.float32)
+        for nid, tid in idx:
+            if tid < 500:
+                x[nid, tid] = 10.0
+        return torch.from_numpy(x).reshape(1, n, 1, 1, 500).to(dev)
+
+    out = net.spike(net.psp(fc2(net.spike(net.psp(fc1(events(srm["spikeIn"], 250)))))))
+    err = net.psp(out - events(srm["spikeOut"], 1))
+    loss = 0.5 * torch.sum(err ** 2) * 0.1
+    loss.backward()
+    g1 = fc1.weight.grad.reshape(25, 250).cpu().numpy()
+    g2 = fc2.weight.grad.reshape(1, 25).cpu().numpy()
+    assert np.linalg.norm(srm["gradW2Initial"] - g2) / g2.size < 1e-4
+    assert np.linalg.norm(srm["gradW1Initial"] - g1) / g1.size < 1e-4
+
+
+def test_mirror_delay_gradient_matches_hand_formula():
+    """test/test_slayer010.py:72-80: delay gradient = -sum(error * d(psp)/dt) * Ts."""
+    from slayerpytorch_b200 import layer as L
+    ops0 = slayerpytorch_b200.load_ops()[0]
+    dev = torch.device("cuda")
+    neuron = {"type": "SRMALPHA", "theta": 10, "tauSr": 1.0, "tauRef": 1.0, "scaleRef": 2, "tauRho": 1, "scaleRho": 1}
+    sim = {"Ts": 0.1, "tSample": 50}
+    Ts = 0.1
+    net = L.spikeLayer(neuron, sim).to(dev)
+    g = torch.Generator().manual_seed(10)
+    spike_in = ((torch.rand(5, 25, 1, 1, 500, generator=g) > 0.8).float() / Ts).to(dev)
+    delay = net.delay((25, 1, 1)).to(dev)
+    psp_delayed = delay(net.psp(spike_in))
+    upstream = torch.randn(5, 25, 1, 1, 500, generator=g).to(dev)
+    psp_delayed.backward(upstream)
+    diff = torch.tensor([1.0, -1.0], device=dev) / Ts
+    dpsp = ops0.conv(psp_delayed.detach(), diff, 1)
+    want = -torch.sum(upstream * dpsp, [0, -1], keepdim=True).reshape(25, 1, 1) * Ts
+    assert torch.norm(want - delay.delay.grad).item() < 1e-4 * max(1.0, torch.norm(want).item())
