@@ -353,7 +353,7 @@ def time_ours(args, rank, world, device):
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "config 2: SRM MLP 2312-512-10 hot path, batch 64 per GPU, T=300, Ts=1, "
-                               "input rate 5%, psp K=%d, refractory %d taps, delays U(0,5)"
+                               "input rate 5%%, psp K=%d, refractory %d taps, delays U(0,5)"
                                % (wl["srm"].numel(), wl["ref"].numel()),
                    "neuron_timesteps_per_step_per_gpu": units, "l2": "flushed between steps (256 MiB write)",
                    "spike_rates": wl["rates"], "parallelism": "batch sharded, no collective"},
