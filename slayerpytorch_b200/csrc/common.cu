@@ -1,6 +1,10 @@
 // Error reporting and device queries shared by all entry points.
 #include <stdarg.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "common.cuh"
 
 namespace sb200 {
@@ -29,6 +33,25 @@ int sm_count()
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+int reserve_dynamic_smem(const void *func, size_t bytes)
+{
+    if (bytes <= 48 * 1024) return SLAYER_B200_OK;
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> granted;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = granted[std::make_pair(func, dev)];
+    if (have >= bytes) return SLAYER_B200_OK;
+    cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+        set_error("cannot reserve %zu bytes of dynamic shared memory: %s", bytes, cudaGetErrorString(e));
+        return SLAYER_B200_ECUDA;
+    }
+    have = bytes;
+    return SLAYER_B200_OK;
 }
 
 }  // namespace sb200

@@ -16,6 +16,10 @@ void clear_error();
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Make sure `func` may be launched with `bytes` of dynamic shared memory on the current
+// device (raises the per-function limit above 48 KB when needed; remembered per device).
+int reserve_dynamic_smem(const void *func, size_t bytes);
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

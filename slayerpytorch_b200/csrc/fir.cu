@@ -18,6 +18,7 @@
 // warp conflict free.  Results leave through a second tile so that global stores are
 // contiguous row segments.
 #include "common.cuh"
+#include "tile.cuh"
 
 namespace sb200 {
 
@@ -56,8 +57,9 @@ __device__ __forceinline__ void fir_group_n(float (&acc)[kFirSeg], const float4 
     }
 }
 
-// DIR = -1: conv, DIR = +1: corr.  VEC: rows are 16-byte aligned and T % 4 == 0.
-template <int DIR, bool VEC>
+// DIR = -1: conv, DIR = +1: corr.  V: global access width in floats (4, 2 or 1; T % V == 0
+// and bases aligned to 4*V bytes).
+template <int DIR, int V>
 __global__ void __launch_bounds__(kFirWarps * 32)
 fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
            int64_t rows, int T, int K, float Ts, int passes, int halo, int SX, int SY, int ttiles)
@@ -82,27 +84,22 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
 
     for (int i = threadIdx.x; i < KP; i += blockDim.x) fs[i] = i < K ? filt[i] : 0.0f;
 
-    // stage the input tile: warp w fills rows w, w+8, w+16, w+24 (contiguous global reads)
+    // stage the input tile with asynchronous copies (all in flight together): warp w fills rows
+    // w, w+8, w+16, w+24 from contiguous global segments; samples outside the row become zeros
 #pragma unroll
     for (int rr = 0; rr < kFirRows / kFirWarps; ++rr) {
         const int r = warp + rr * kFirWarps;
         const bool row_ok = r < nrow;
-        const float *src = in + (row0 + r) * (int64_t)T;
+        const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
         float *dst = xs + r * SX;
-        if (VEC) {
-            for (int p = lane * 4; p < WX; p += 128) {
-                const int gt = g0 + p;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (row_ok && gt >= 0 && gt < T) v = __ldg(reinterpret_cast<const float4 *>(src + gt));
-                *reinterpret_cast<float4 *>(dst + p) = v;
-            }
-        } else {
-            for (int p = lane; p < WX; p += 32) {
-                const int gt = g0 + p;
-                dst[p] = (row_ok && gt >= 0 && gt < T) ? __ldg(src + gt) : 0.0f;
-            }
+        for (int p = lane * V; p < WX; p += 32 * V) {
+            const int gt = g0 + p;
+            const bool ok = row_ok && gt >= 0 && gt < T;
+            cp_async<4 * V>(dst + p, ok ? src + gt : in, ok);
         }
     }
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
 
     const float *xrow = xs + lane * SX + (DIR < 0 ? halo : 0);   // tile-local position 0
@@ -171,12 +168,9 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
         if (r >= nrow) continue;
         float *dst = out + (row0 + r) * (int64_t)T + t0;
         const float *src = ys + r * SY;
-        if (VEC) {
-            for (int p = lane * 4; p < tvalid; p += 128)
-                *reinterpret_cast<float4 *>(dst + p) = ld4(src + p);
-        } else {
-            for (int p = lane; p < tvalid; p += 32) dst[p] = src[p];
-        }
+        typedef typename vec_t<V>::type vec;
+        for (int p = lane * V; p < tvalid; p += 32 * V)
+            *reinterpret_cast<vec *>(dst + p) = *reinterpret_cast<const vec *>(src + p);
     }
 }
 
@@ -247,12 +241,10 @@ static int launch_fir(float *out, const float *in, const float *filt,
         fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts);
         return check_launch("fir (long filter) kernel launch");
     }
-    const bool vec = (T % 4 == 0) && aligned16(out) && aligned16(in);
-    auto kern = vec ? fir_kernel<DIR, true> : fir_kernel<DIR, false>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { set_error("fir: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return SLAYER_B200_ECUDA; }
-    }
+    const int vw = tile_vec_width(T, {out, in});
+    auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
     kern<<<(unsigned)blocks, kFirWarps * 32, smem, stream>>>(
         out, in, filt, rows, (int)T, (int)Keff, Ts, best_p, halo, SX, SY, (int)ttiles);
     return check_launch("fir kernel launch");

@@ -15,13 +15,15 @@
 // equivalent to the countdown kept in a register here.
 //
 // Memory: 16 algorithmic bytes per element (read w; write s, v, u), bound by HBM.  Same
-// warp-owned 32x32 tile scheme as the SRM kernel: the input tile is overwritten with the
-// current u, a second tile collects v, spikes leave as a bit mask.
+// warp-owned 32x32 tile scheme as the SRM kernel (next input tile prefetched with cp.async):
+// the input tile is overwritten with the current u, another tile collects v, spikes leave as a
+// bit mask.
 #include "common.cuh"
 #include "tile.cuh"
 
 namespace sb200 {
 
+template <int V>
 __global__ void __launch_bounds__(256)
 loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
                         int64_t rows, int T, unsigned weightScale, int theta,
@@ -31,10 +33,11 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
-    float *tile_u = smem + warp * (2 * kTileWords);
-    float *tile_v = tile_u + kTileWords;
+    float *tiles_u = smem + warp * (3 * kTileWords);     // two input/current tiles (prefetch ring)
+    float *tile_v = tiles_u + 2 * kTileWords;            // voltage tile
     const float vMarkF = (float)vDecayMark;
 
+    const int ntiles = (T + kTile - 1) / kTile;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
     for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
@@ -42,12 +45,19 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
         int uOld = 0, vOld = 0;
         unsigned refLeft = 0;                // steps until the refractory state clears
 
-        for (int t0 = 0; t0 < T; t0 += kTile) {
-            tile_load(tile_u, w, row0, rows, t0, T, lane);
+        tile_prefetch<V>(tiles_u, w, row0, rows, 0, T, lane);
+        cp_async_commit();
+        for (int it = 0; it < ntiles; ++it) {
+            const int t0 = it * kTile;
+            float *tile_u = tiles_u + (it & 1) * kTileWords;
+            if (it + 1 < ntiles)
+                tile_prefetch<V>(tiles_u + ((it + 1) & 1) * kTileWords, w, row0, rows, t0 + kTile, T, lane);
+            cp_async_commit();
+            cp_async_wait<1>();
             __syncwarp();
 
             unsigned smask = 0u;
-#pragma unroll 1
+#pragma unroll 2
             for (int c4 = 0; c4 < kTile / 4; ++c4) {
                 float4 *cu = reinterpret_cast<float4 *>(tile_u + tile_chunk(lane, c4));
                 float4 *cv = reinterpret_cast<float4 *>(tile_v + tile_chunk(lane, c4));
@@ -56,7 +66,7 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
                 float uo[4], vo[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    if (t0 == 0 && c4 == 0 && j == 0) {   // t = 0
+                    if (it == 0 && c4 == 0 && j == 0) {   // t = 0
                         uo[j] = 0.0f;
                         vo[j] = 0.0f;
                         continue;
@@ -84,12 +94,44 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
             }
             __syncwarp();
 
-            tile_store(tile_u, u, row0, rows, t0, T, lane);
-            tile_store(tile_v, v, row0, rows, t0, T, lane);
-            mask_store(smask, 1.0f, s, row0, rows, t0, T, lane);
+            tile_store<V>(tile_u, u, row0, rows, t0, T, lane);
+            tile_store<V>(tile_v, v, row0, rows, t0, T, lane);
+            mask_store<V>(smask, 1.0f, s, row0, rows, t0, T, lane);
             __syncwarp();
         }
     }
+}
+
+struct LoihiArgs {
+    float *s, *v, *u;
+    const float *w;
+    int64_t rows;
+    int T;
+    unsigned weightScale;
+    int theta;
+    unsigned iKeep, vKeep;
+    int vMark;
+    unsigned refDelay;
+    cudaStream_t stream;
+};
+
+template <int V>
+static int launch_loihi(const LoihiArgs &a)
+{
+    const int64_t nblocks = ceil_div(a.rows, kTile);
+    const int sms = sm_count();
+    int warps = 8;
+    while (warps > 1 && ceil_div(nblocks, warps) < 2 * (int64_t)sms) warps >>= 1;
+    int64_t grid = ceil_div(nblocks, warps);
+    const int64_t cap = (int64_t)sms * 16;
+    if (grid > cap) grid = cap;
+    const size_t smem = (size_t)warps * 3 * kTileWords * sizeof(float);
+    auto kern = loihi_get_spikes_kernel<V>;
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
+    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(a.s, a.v, a.u, a.w, a.rows, a.T, a.weightScale, a.theta,
+                                                         a.iKeep, a.vKeep, a.vMark, a.refDelay);
+    return check_launch("loihi_get_spikes kernel launch");
 }
 
 }  // namespace sb200
@@ -109,18 +151,11 @@ extern "C" int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const 
     SB200_REQUIRE(s && v && u && w, "loihi_get_spikes: null pointer");
     SB200_REQUIRE(s != v && s != u && v != u && s != w && v != w,
                   "loihi_get_spikes: output buffers must be distinct");
-    cudaStream_t stream = (cudaStream_t)stream_;
-
-    const int64_t nblocks = ceil_div(rows, kTile);
-    const int sms = sm_count();
-    int warps = 8;
-    while (warps > 1 && ceil_div(nblocks, warps) < 2 * (int64_t)sms) warps >>= 1;
-    int64_t grid = ceil_div(nblocks, warps);
-    const int64_t cap = (int64_t)sms * 16;
-    if (grid > cap) grid = cap;
-    const size_t smem = (size_t)warps * 2 * kTileWords * sizeof(float);
-    loihi_get_spikes_kernel<<<(unsigned)grid, warps * 32, smem, stream>>>(
-        s, v, u, w, rows, (int)T, 1u << (6 + wgtExp), (int)theta,
-        4096u - iDecay, 4096u - vDecay, (int)vDecay, refDelay);
-    return check_launch("loihi_get_spikes kernel launch");
+    const LoihiArgs a = {s, v, u, w, rows, (int)T, 1u << (6 + wgtExp), (int)theta,
+                         4096u - iDecay, 4096u - vDecay, (int)vDecay, refDelay, (cudaStream_t)stream_};
+    switch (tile_vec_width(T, {s, v, u, w})) {
+        case 4: return launch_loihi<4>(a);
+        case 2: return launch_loihi<2>(a);
+        default: return launch_loihi<1>(a);
+    }
 }

@@ -11,9 +11,15 @@
 // registers and never writes ahead of itself, so the recurrence reads memory strictly forward
 // and time can be tiled with no state in memory between tiles.
 //
+// Two variants of the inner step:
+//   - window of up to 32 steps (NB > 0): the taps live in registers and the step is a fully
+//     unrolled run of NB predicated adds, oldest first - no loop, no branch, no memory access;
+//   - longer windows (up to 256 steps, W history words): a loop over the set history bits with
+//     the taps in shared memory.
+//
 // Memory: 12 algorithmic bytes per element (read u, write u, write s), bound by HBM.  A warp
 // owns 32 rows and walks them in tiles of 32 time steps through the swizzled shared-memory
-// tile of tile.cuh, so every global access is a contiguous 128-byte row segment.
+// tiles of tile.cuh, prefetching the next tile with cp.async while it works on the current one.
 #include "common.cuh"
 #include "tile.cuh"
 
@@ -21,7 +27,9 @@ namespace sb200 {
 
 constexpr int kMaxHistWords = 8;     // register history covers refractory kernels up to 257 taps
 
-template <int W>
+// V: global access width in floats.  NB > 0: unrolled window of NB history bits (W must be 1).
+// NB == 0: looped window of W history words.
+template <int V, int NB, int W>
 __global__ void __launch_bounds__(256)
 srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
                       int64_t rows, int nuEff, int T, float theta, float spikeVal)
@@ -30,15 +38,20 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
-    const int nuPad = (nuEff + 3) & ~3;
+    const int nuPad = NB > 0 ? 0 : ((nuEff + 3) & ~3);
     float *nu_s = smem;
-    float *tile = smem + nuPad + warp * kTileWords;
+    float *tiles = smem + nuPad + warp * (2 * kTileWords);
 
-    for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
-    __syncthreads();
+    if (NB == 0) {
+        for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
+        __syncthreads();
+    }
 
     const bool has_nu0 = nuEff >= 1;
-    const float nu0 = has_nu0 ? nu_s[0] : 0.0f;
+    const float nu0 = has_nu0 ? __ldg(nu) : 0.0f;
+    float nu_r[NB > 0 ? NB : 1];     // nu_r[k] = tap of a spike k+1 steps ago
+#pragma unroll
+    for (int k = 0; k < NB; ++k) nu_r[k] = (k + 1 < nuEff) ? __ldg(nu + k + 1) : 0.0f;
 
     // bit b of the history (word b/32, bit b%32) = "spiked b+1 steps ago"; keep b <= nuEff-2
     unsigned wmask[W];
@@ -48,6 +61,7 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
         wmask[w] = nb >= 32 ? 0xffffffffu : (nb <= 0 ? 0u : ((1u << nb) - 1u));
     }
 
+    const int ntiles = (T + kTile - 1) / kTile;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
     for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
@@ -56,12 +70,19 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
 #pragma unroll
         for (int w = 0; w < W; ++w) hist[w] = 0u;
 
-        for (int t0 = 0; t0 < T; t0 += kTile) {
-            tile_load(tile, u, row0, rows, t0, T, lane);
+        tile_prefetch<V>(tiles, u, row0, rows, 0, T, lane);
+        cp_async_commit();
+        for (int it = 0; it < ntiles; ++it) {
+            const int t0 = it * kTile;
+            float *tile = tiles + (it & 1) * kTileWords;
+            if (it + 1 < ntiles)
+                tile_prefetch<V>(tiles + ((it + 1) & 1) * kTileWords, u, row0, rows, t0 + kTile, T, lane);
+            cp_async_commit();
+            cp_async_wait<1>();
             __syncwarp();
 
             unsigned smask = 0u;
-#pragma unroll 1
+#pragma unroll 2
             for (int c4 = 0; c4 < kTile / 4; ++c4) {
                 float4 *chunk = reinterpret_cast<float4 *>(tile + tile_chunk(lane, c4));
                 const float4 in4 = *chunk;
@@ -70,13 +91,19 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
                 for (int j = 0; j < 4; ++j) {
                     float v = vv[j];
                     // refractory taps of recent spikes, oldest spike first
+                    if (NB > 0) {
 #pragma unroll
-                    for (int w = W - 1; w >= 0; --w) {
-                        unsigned m = hist[w];
-                        while (m) {
-                            const int k = 31 - __clz(m);
-                            v += nu_s[32 * w + k + 1];
-                            m &= ~(1u << k);
+                        for (int k = NB - 1; k >= 0; --k)
+                            if (hist[0] & (1u << k)) v += nu_r[k];
+                    } else {
+#pragma unroll
+                        for (int w = W - 1; w >= 0; --w) {
+                            unsigned m = hist[w];
+                            while (m) {
+                                const int k = 31 - __clz(m);
+                                v += nu_s[32 * w + k + 1];
+                                m &= ~(1u << k);
+                            }
                         }
                     }
                     const bool spk = v >= theta;
@@ -91,8 +118,8 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
             }
             __syncwarp();
 
-            tile_store(tile, u, row0, rows, t0, T, lane);
-            mask_store(smask, spikeVal, s, row0, rows, t0, T, lane);
+            tile_store<V>(tile, u, row0, rows, t0, T, lane);
+            mask_store<V>(smask, spikeVal, s, row0, rows, t0, T, lane);
             __syncwarp();
         }
     }
@@ -119,21 +146,45 @@ srm_get_spikes_long_kernel(float *s, float *u, const float *__restrict__ nu,
     }
 }
 
-template <int W>
-static int launch_srm(float *s, float *u, const float *nu, int64_t rows, int nuEff, int T,
-                      float theta, float spikeVal, cudaStream_t stream)
+struct SrmArgs {
+    float *s, *u;
+    const float *nu;
+    int64_t rows;
+    int nuEff, T;
+    float theta, spikeVal;
+    cudaStream_t stream;
+};
+
+template <int V, int NB, int W>
+static int launch_srm(const SrmArgs &a)
 {
-    const int64_t nblocks = ceil_div(rows, kTile);
+    const int64_t nblocks = ceil_div(a.rows, kTile);
     const int sms = sm_count();
     int warps = 8;                                   // spread small problems over all SMs
     while (warps > 1 && ceil_div(nblocks, warps) < 2 * (int64_t)sms) warps >>= 1;
     int64_t grid = ceil_div(nblocks, warps);
     const int64_t cap = (int64_t)sms * 16;
     if (grid > cap) grid = cap;
-    const size_t smem = (size_t)(((nuEff + 3) & ~3) + warps * kTileWords) * sizeof(float);
-    srm_get_spikes_kernel<W><<<(unsigned)grid, warps * 32, smem, stream>>>(
-        s, u, nu, rows, nuEff, T, theta, spikeVal);
+    const size_t smem = (size_t)((NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) + warps * 2 * kTileWords) * sizeof(float);
+    auto kern = srm_get_spikes_kernel<V, NB, W>;
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
+    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta, a.spikeVal);
     return check_launch("srm_get_spikes kernel launch");
+}
+
+template <int V>
+static int dispatch_srm(const SrmArgs &a)
+{
+    const int window = a.nuEff > 1 ? a.nuEff - 1 : 0;     // history bits needed
+    if (window <= 4) return launch_srm<V, 4, 1>(a);
+    if (window <= 8) return launch_srm<V, 8, 1>(a);
+    if (window <= 12) return launch_srm<V, 12, 1>(a);
+    if (window <= 16) return launch_srm<V, 16, 1>(a);
+    if (window <= 32) return launch_srm<V, 32, 1>(a);
+    if (window <= 64) return launch_srm<V, 0, 2>(a);
+    if (window <= 128) return launch_srm<V, 0, 4>(a);
+    return launch_srm<V, 0, 8>(a);
 }
 
 }  // namespace sb200
@@ -152,14 +203,16 @@ extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
     cudaStream_t stream = (cudaStream_t)stream_;
     const float spikeVal = 1.0f / Ts;
     const int64_t nuEff = nuSize < T ? nuSize : T;    // taps beyond the row end never land
-    const int64_t words = ceil_div(nuEff > 1 ? nuEff - 1 : 1, 32);
-    if (words <= 1) return launch_srm<1>(s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream);
-    if (words <= 2) return launch_srm<2>(s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream);
-    if (words <= 4) return launch_srm<4>(s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream);
-    if (words <= kMaxHistWords)
-        return launch_srm<8>(s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream);
-    const int threads = 128;
-    srm_get_spikes_long_kernel<<<(unsigned)ceil_div(rows, threads), threads, 0, stream>>>(
-        s, u, nu, rows, nuSize, T, theta, spikeVal);
-    return check_launch("srm_get_spikes (long refractory kernel) launch");
+    if (nuEff - 1 > 32 * kMaxHistWords) {
+        const int threads = 128;
+        srm_get_spikes_long_kernel<<<(unsigned)ceil_div(rows, threads), threads, 0, stream>>>(
+            s, u, nu, rows, nuSize, T, theta, spikeVal);
+        return check_launch("srm_get_spikes (long refractory kernel) launch");
+    }
+    const SrmArgs a = {s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream};
+    switch (tile_vec_width(T, {s, u})) {
+        case 4: return dispatch_srm<4>(a);
+        case 2: return dispatch_srm<2>(a);
+        default: return dispatch_srm<1>(a);
+    }
 }

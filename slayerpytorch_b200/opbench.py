@@ -1,0 +1,101 @@
+"""Time one operator on synthetic data of a given shape (CUDA events, inputs resident in HBM).
+
+    python -m slayerpytorch_b200.opbench --op getSpikes --rows 262144 --T 300 --iters 5
+
+Operators: conv, corr, getSpikes, shift, shiftScalar, spikeGrad, loihi.  Prints one JSON line with
+the average launch time, algorithmic GB/s (8 bytes per element for conv/corr/shift, 12 for
+getSpikes/spikeGrad, 16 for loihi) and elements per second.  Small enough to run under a
+profiler: every iteration is exactly one kernel launch of the operator (getSpikes works in
+place, so its potential is restored by a device copy between launches).
+"""
+import argparse
+import json
+import sys
+
+import torch
+
+import slayerpytorch_b200
+from slayerpytorch_b200.layer import alpha_kernel, loihi_psp_kernel
+
+ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "loihi": 16}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=sorted(ALG_BYTES))
+    ap.add_argument("--rows", type=int, default=262144)
+    ap.add_argument("--T", type=int, default=300)
+    ap.add_argument("--K", type=int, default=0, help="filter taps for conv/corr (0 = SRM alpha kernel, 77 taps)")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--density", type=float, default=0.3, help="fraction of non-zero input samples")
+    ap.add_argument("--neurons", type=int, default=512, help="rows per batch sample (length of the shift table)")
+    args = ap.parse_args(argv)
+
+    sc, lc = slayerpytorch_b200.load_ops()
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(1)
+    neurons = min(args.neurons, args.rows)
+    batch = max(1, args.rows // neurons)
+    shape = (batch, neurons, 1, 1, args.T)
+    el = batch * neurons * args.T
+
+    srm = torch.tensor(alpha_kernel(10.0, 1.0, 300), dtype=torch.float32, device=dev)
+    ref = torch.tensor(alpha_kernel(1.0, 1.0, 300, mult=-20.0), dtype=torch.float32, device=dev)
+    if args.K:
+        filt = torch.randn(args.K, device=dev, generator=gen)
+    elif args.op == "corr" and args.T > 1000:
+        filt = torch.tensor(loihi_psp_kernel({"iDecay": 1024, "vDecay": 128, "wgtExp": 0}), dtype=torch.float32, device=dev)
+    else:
+        filt = srm
+    a = (torch.randn(shape, device=dev, generator=gen).abs() * 1.2
+         * (torch.rand(shape, device=dev, generator=gen) < args.density)).float()
+    extra = {}
+    restore = None
+    if args.op in ("conv", "corr"):
+        fn = (lambda: sc.conv(a, filt, 1.0)) if args.op == "conv" else (lambda: sc.corr(a, filt, 1.0))
+        extra["taps"] = int(filt.numel())
+    elif args.op == "getSpikes":
+        u0 = sc.conv(a, srm, 1.0)
+        u = torch.empty_like(u0)
+        restore = lambda: u.copy_(u0)
+        fn = lambda: sc.getSpikes(u, ref, 10.0, 1.0)
+    elif args.op == "shift":
+        d = torch.rand(neurons, device=dev, generator=gen) * 5
+        fn = lambda: sc.shift(a, d, 1.0)
+    elif args.op == "shiftScalar":
+        fn = lambda: sc.shift(a, 1.0, 1.0)
+    elif args.op == "spikeGrad":
+        g = torch.randn(shape, device=dev, generator=gen)
+        fn = lambda: sc.spikeGrad(g, a, 10.0, 10.0, 1.0)
+    else:
+        w = (torch.randint(-128, 128, shape, device=dev, generator=gen)
+             * (torch.rand(shape, device=dev, generator=gen) < 0.05)).float()
+        fn = lambda: lc.getSpikes(w, 0, 5120, 1024, 128, 1)
+
+    times = []
+    out = None
+    for it in range(args.warmup + args.iters):
+        if restore:
+            restore()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+    if args.op == "getSpikes":
+        extra["spike_rate"] = float(out.mean())
+    if args.op == "loihi":
+        extra["spike_rate"] = float(out[0].mean())
+    ms = sum(times) / len(times)
+    print(json.dumps({"op": args.op, "rows": batch * neurons, "T": args.T, "elements": el,
+                      "tensor_GiB": round(el * 4 / 2 ** 30, 3), "avg_ms": round(ms, 4), "min_ms": round(min(times), 4),
+                      "GB/s": round(ALG_BYTES[args.op] * el / ms / 1e6, 1),
+                      "Gelements/s": round(el / ms / 1e6, 2), **extra}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
