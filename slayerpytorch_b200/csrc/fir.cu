@@ -2,176 +2,246 @@
 //   conv: out[r,t] = Ts * sum_{i<K, t-i>=0} in[r,t-i] * f[i]      (psp, forward)
 //   corr: out[r,t] = Ts * sum_{i<K, t+i<T}  in[r,t+i] * f[i]      (psp, backward)
 // Each output is one fp32 fused-multiply-add chain over the taps in ascending order starting
-// from +0, scaled by Ts once at the end — the same sequence of roundings as a thread-per-
+// from +0, scaled by Ts once at the end - the same sequence of roundings as a thread-per-
 // output loop, so results are reproducible bit for bit whatever the tiling.  Samples outside
 // the row enter the chain as +0, which leaves the accumulator unchanged for finite taps.
 //
 // Cost: 8 algorithmic bytes and 2K flops per element.  For K above ~47 taps the fp32 FMA
-// pipes, not HBM, bound the kernel, so the design goal is one FMA per issue slot:
-//   - a CTA stages a [32 rows x (Tt + halo)] input tile in shared memory once;
-//   - lane l of every warp owns row l, a warp owns 8-sample time segments, and a thread
-//     keeps 8 accumulators plus a 12-sample sliding input window in registers;
-//   - per group of 4 taps a thread issues 32 FMAs, one 128-bit load of new window samples and
-//     one 128-bit broadcast load of taps; the window rotates through three register banks by
-//     unrolling, so no moves are spent on it.
+// pipes, not HBM, bound the kernel, so the design goal is to keep those pipes fed:
+//   - persistent CTAs walk [32 rows x nseg*16 samples] tiles; the input tile (plus a halo of
+//     K-1 samples) is staged in shared memory with cp.async, double buffered, so the copy of
+//     the next tile overlaps the arithmetic of the current one;
+//   - lane l of every warp owns row l, a warp owns 16-sample segments of the tile, and a
+//     thread keeps 16 accumulators plus a 20-sample sliding input window in registers;
+//   - per group of 4 taps a thread issues 64 FMAs, one 128-bit load of new window samples and
+//     one 128-bit broadcast load of taps (shared-memory bandwidth is the second scarcest
+//     resource, which is why a thread produces 16 outputs and not fewer);
+//   - the window rotates through a ring of six register quads by unrolling, and the loads for
+//     the next group target the quad that is not in use, so no moves are spent on it;
+//   - results go from registers straight to global memory (64 contiguous bytes per thread).
 // The row stride of the tile is = 4 (mod 8) words, which makes the per-row 128-bit loads of a
-// warp conflict free.  Results leave through a second tile so that global stores are
-// contiguous row segments.
+// warp conflict free.
 #include "common.cuh"
 #include "tile.cuh"
 
 namespace sb200 {
 
-constexpr int kFirRows = 32;        // rows per CTA (= lanes)
-constexpr int kFirWarps = 8;
-constexpr int kFirSeg = 8;          // outputs per thread per pass
-constexpr int kFirPassLen = kFirWarps * kFirSeg;   // 64 outputs of a row per pass
+constexpr int kFirRows = 32;        // rows per tile (= lanes)
+constexpr int kFirSeg = 16;         // outputs per thread per segment
+constexpr int kFirWin = kFirSeg + 4;           // samples one group of four taps reads
+constexpr int kFirRing = kFirWin + 4;          // register ring: the window plus the quad being loaded
+constexpr int kFirPhases = kFirRing / 4;       // 6
+constexpr int kFirMaxWarps = 16;
 
-__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
-
-// acc[m] += sum_{ii<4} win[m + base(ii)] * f[ii], ascending ii.  win = lo|mid|hi (12 samples).
-// DIR < 0 (conv): sample for (m, ii) is win[m + 4 - ii];  DIR > 0 (corr): win[m + ii].
-template <int DIR, int NT>
-__device__ __forceinline__ void fir_group(float (&acc)[kFirSeg], const float4 &lo, const float4 &mid,
-                                          const float4 &hi, const float4 &f)
+// 128-bit load from a 32-bit shared-memory address (explicit state space: the address
+// arithmetic stays 32-bit and constant offsets fold into the instruction)
+__device__ __forceinline__ float4 ld4(unsigned saddr)
 {
-    const float win[12] = {lo.x, lo.y, lo.z, lo.w, mid.x, mid.y, mid.z, mid.w, hi.x, hi.y, hi.z, hi.w};
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+    return v;
+}
+
+// acc = a * b + acc, one fused multiply-add that accumulates in place (denormals flushed, as
+// in the rest of this translation unit)
+__device__ __forceinline__ void fma_acc(float &acc, float a, float b)
+{
+    asm("fma.rn.ftz.f32 %0, %1, %2, %0;" : "+f"(acc) : "f"(a), "f"(b));
+}
+
+// The sliding input window lives in a ring of six register quads: five hold the 20 samples
+// the current group of four taps reads, the sixth receives the quad the NEXT group needs, so
+// that load never targets registers that are still being read and costs no register moves.
+// After each group the window moves by four samples; the mapping from logical window position
+// q to ring register rotates with the phase PH = group mod 6 instead of the data moving:
+//   conv (window moves toward older samples):  ring = (q - 4*PH) mod 24
+//   corr (window moves toward newer samples):  ring = (q + 4*PH) mod 24
+// The incoming quad is logical position -4 (conv) or 20 (corr) of the current phase.
+template <int DIR, int PH>
+__device__ __forceinline__ constexpr int win_reg(int q)
+{
+    return DIR < 0 ? (q + 4 * kFirRing - 4 * PH) % kFirRing : (q + 4 * PH) % kFirRing;
+}
+
+__device__ __forceinline__ void put4(float (&w)[kFirRing], int base, const float4 &v)
+{
+    w[base] = v.x; w[base + 1] = v.y; w[base + 2] = v.z; w[base + 3] = v.w;
+}
+
+// acc[m] += sum_{ii<NT} W[m + off(ii)] * f[ii], ascending ii, W = logical window of phase PH.
+// conv: sample for (m, ii) is W[m + 4 - ii];  corr: W[m + ii].
+template <int DIR, int PH, int NT>
+__device__ __forceinline__ void fir_group(float (&acc)[kFirSeg], const float (&w)[kFirRing], const float4 &f)
+{
     const float fv[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
     for (int ii = 0; ii < NT; ++ii) {
 #pragma unroll
         for (int m = 0; m < kFirSeg; ++m)
-            acc[m] = fmaf(win[DIR < 0 ? m + 4 - ii : m + ii], fv[ii], acc[m]);
+            fma_acc(acc[m], w[win_reg<DIR, PH>(DIR < 0 ? m + 4 - ii : m + ii)], fv[ii]);
     }
 }
 
-template <int DIR>
-__device__ __forceinline__ void fir_group_n(float (&acc)[kFirSeg], const float4 &lo, const float4 &mid,
-                                            const float4 &hi, const float4 &f, int ntaps)
+template <int DIR, int PH>
+__device__ __forceinline__ void fir_group_n(float (&acc)[kFirSeg], const float (&w)[kFirRing], const float4 &f, int ntaps)
 {
     switch (ntaps) {
-        case 1: fir_group<DIR, 1>(acc, lo, mid, hi, f); break;
-        case 2: fir_group<DIR, 2>(acc, lo, mid, hi, f); break;
-        case 3: fir_group<DIR, 3>(acc, lo, mid, hi, f); break;
-        default: fir_group<DIR, 4>(acc, lo, mid, hi, f); break;
+        case 1: fir_group<DIR, PH, 1>(acc, w, f); break;
+        case 2: fir_group<DIR, PH, 2>(acc, w, f); break;
+        case 3: fir_group<DIR, PH, 3>(acc, w, f); break;
+        default: fir_group<DIR, PH, 4>(acc, w, f); break;
     }
 }
+
+// One group in phase PH.  Before its arithmetic it starts the loads the group after it needs:
+// the sample quad that enters the window (into the free ring quad) and the next four taps
+// (into the tap quad the previous group has finished with).
+template <int DIR, int PH>
+__device__ __forceinline__ void fir_step(float (&acc)[kFirSeg], float (&w)[kFirRing], float4 (&f)[2],
+                                         unsigned fp_next, unsigned xp)
+{
+    put4(w, win_reg<DIR, PH>(DIR < 0 ? -4 + kFirRing : kFirWin), ld4(xp));
+    f[(PH + 1) & 1] = ld4(fp_next);
+    fir_group<DIR, PH, 4>(acc, w, f[PH & 1]);
+}
+
+// The last `left` (< 6) full groups and the partial group of `tail` taps, phases from PH on.
+// f[PH & 1] already holds the taps of the first remaining group.
+template <int DIR, int PH>
+__device__ __forceinline__ void fir_rest(float (&acc)[kFirSeg], float (&w)[kFirRing], float4 (&f)[2],
+                                         unsigned fp_next, unsigned xp, int left, int tail)
+{
+    if (left == 0) {
+        if (tail) fir_group_n<DIR, PH>(acc, w, f[PH & 1], tail);
+        return;
+    }
+    fir_step<DIR, PH>(acc, w, f, fp_next, xp);
+    if constexpr (PH + 1 < kFirPhases)
+        fir_rest<DIR, PH + 1>(acc, w, f, fp_next + 16, xp + (DIR < 0 ? 0u - 16u : 16u), left - 1, tail);
+}
+
+struct FirShape {
+    int nseg;       // 16-sample segments per tile
+    int halo;       // extra input samples staged per row (multiple of 4, >= K-1 plus slack)
+    int SX;         // row stride of the input tile in words
+    int ttiles;     // tiles along time
+    int nwarps;     // warps per CTA
+};
 
 // DIR = -1: conv, DIR = +1: corr.  V: global access width in floats (4, 2 or 1; T % V == 0
 // and bases aligned to 4*V bytes).
 template <int DIR, int V>
-__global__ void __launch_bounds__(kFirWarps * 32)
+__global__ void __launch_bounds__(kFirMaxWarps * 32)
 fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-           int64_t rows, int T, int K, float Ts, int passes, int halo, int SX, int SY, int ttiles)
+           int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles)
 {
     extern __shared__ __align__(16) float smem[];
-    const int Tt = passes * kFirPassLen;
-    const int WX = Tt + halo;
-    const int KP = (K + 3) & ~3;
-    float *fs = smem;                        // KP taps
-    float *xs = fs + KP;                     // kFirRows x SX
-    float *ys = xs + kFirRows * SX;          // kFirRows x SY
+    const int Tt = sh.nseg * kFirSeg;
+    const int WX = Tt + sh.halo;
+    const int KP = ((K + 3) & ~3) + 4;       // taps, zero padded; one spare quad for the look-ahead load
+    float *fs = smem;
+    float *xbuf = fs + KP;                   // 2 x [kFirRows x SX]
+    const int tile_words = kFirRows * sh.SX;
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int64_t rb = blockIdx.x / ttiles;
-    const int tt = blockIdx.x - (int)(rb * ttiles);
-    const int64_t row0 = rb * kFirRows;
-    const int t0 = tt * Tt;
-    const int64_t nrow = rows - row0;
-    // global time of tile-local input position 0
-    const int g0 = DIR < 0 ? t0 - halo : t0;
+    const int nwarps = blockDim.x >> 5;
 
     for (int i = threadIdx.x; i < KP; i += blockDim.x) fs[i] = i < K ? filt[i] : 0.0f;
 
-    // stage the input tile with asynchronous copies (all in flight together): warp w fills rows
-    // w, w+8, w+16, w+24 from contiguous global segments; samples outside the row become zeros
-#pragma unroll
-    for (int rr = 0; rr < kFirRows / kFirWarps; ++rr) {
-        const int r = warp + rr * kFirWarps;
-        const bool row_ok = r < nrow;
-        const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
-        float *dst = xs + r * SX;
-        for (int p = lane * V; p < WX; p += 32 * V) {
-            const int gt = g0 + p;
-            const bool ok = row_ok && gt >= 0 && gt < T;
-            cp_async<4 * V>(dst + p, ok ? src + gt : in, ok);
+    // asynchronous copy of one input tile: warp w fills rows w, w+nwarps, ... from contiguous
+    // global segments; samples outside the row (or rows outside the array) become zeros
+    auto fill = [&](float *xs, int64_t tile) {
+        const int64_t rb = tile / sh.ttiles;
+        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        const int64_t row0 = rb * kFirRows;
+        const int64_t nrow = rows - row0;
+        const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
+        for (int r = warp; r < kFirRows; r += nwarps) {
+            const bool row_ok = r < nrow;
+            const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+            float *dst = xs + r * sh.SX;
+            for (int p = lane * V; p < WX; p += 32 * V) {
+                const int gt = g0 + p;
+                const bool ok = row_ok && gt >= 0 && gt < T;
+                cp_async<4 * V>(dst + p, ok ? src + gt : in, ok);
+            }
         }
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
+        cp_async_commit();
+    };
 
-    const float *xrow = xs + lane * SX + (DIR < 0 ? halo : 0);   // tile-local position 0
-    float *yrow = ys + lane * SY;
     const int groups = K >> 2;          // full groups of 4 taps
     const int tail = K & 3;
+    constexpr unsigned step = DIR < 0 ? 0u - 16u : 16u;   // bytes the window moves per group (mod 2^32)
+    const unsigned fs_addr = (unsigned)__cvta_generic_to_shared(fs);
+    const unsigned xbuf_addr = (unsigned)__cvta_generic_to_shared(xbuf);
 
-    for (int pass = 0; pass < passes; ++pass) {
-        const int tb = (pass * kFirWarps + warp) * kFirSeg;
-        if (t0 + tb >= T) break;        // whole segment beyond the row end (warp-uniform)
-        float acc[kFirSeg];
+    int64_t tile = blockIdx.x;
+    if (tile < ntiles) fill(xbuf, tile);
+    for (int it = 0; tile < ntiles; tile += gridDim.x, ++it) {
+        cp_async_wait<0>();
+        __syncthreads();                 // this tile has landed; the other buffer is free again
+        const int64_t next = tile + gridDim.x;
+        if (next < ntiles) fill(xbuf + ((it + 1) & 1) * tile_words, next);
+
+        const int64_t rb = tile / sh.ttiles;
+        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        const int64_t row = rb * kFirRows + lane;
+        // byte address of tile position 0 of this lane's row
+        const unsigned xrow = xbuf_addr + 4u * (unsigned)((it & 1) * tile_words + lane * sh.SX + (DIR < 0 ? sh.halo : 0));
+
+        for (int seg = warp; seg < sh.nseg; seg += nwarps) {
+            const int tb = seg * kFirSeg;
+            if (t0 + tb >= T) break;    // whole segment beyond the row end (warp-uniform)
+            float acc[kFirSeg];
 #pragma unroll
-        for (int m = 0; m < kFirSeg; ++m) acc[m] = 0.0f;
+            for (int m = 0; m < kFirSeg; ++m) acc[m] = 0.0f;
 
-        // window banks; conv slides toward lower positions, corr toward higher ones
-        float4 A, B, C;
-        const float *xp;                // next sample quad to fetch
-        if (DIR < 0) {
-            A = ld4(xrow + tb - 4); B = ld4(xrow + tb); C = ld4(xrow + tb + 4);
-            xp = xrow + tb - 8;
-        } else {
-            A = ld4(xrow + tb); B = ld4(xrow + tb + 4); C = ld4(xrow + tb + 8);
-            xp = xrow + tb + 12;
-        }
-        const float *fp = fs;
-        int g = 0;
-        if (DIR < 0) {
-            for (; g + 3 <= groups; g += 3) {
-                fir_group<DIR, 4>(acc, A, B, C, ld4(fp));     C = ld4(xp);
-                fir_group<DIR, 4>(acc, C, A, B, ld4(fp + 4)); B = ld4(xp - 4);
-                fir_group<DIR, 4>(acc, B, C, A, ld4(fp + 8)); A = ld4(xp - 8);
-                xp -= 12; fp += 12;
-            }
-            for (; g < groups; ++g) {
-                fir_group<DIR, 4>(acc, A, B, C, ld4(fp));
-                C = B; B = A; A = ld4(xp);
-                xp -= 4; fp += 4;
-            }
-            if (tail) fir_group_n<DIR>(acc, A, B, C, ld4(fp), tail);
-        } else {
-            for (; g + 3 <= groups; g += 3) {
-                fir_group<DIR, 4>(acc, A, B, C, ld4(fp));     A = ld4(xp);
-                fir_group<DIR, 4>(acc, B, C, A, ld4(fp + 4)); B = ld4(xp + 4);
-                fir_group<DIR, 4>(acc, C, A, B, ld4(fp + 8)); C = ld4(xp + 8);
-                xp += 12; fp += 12;
-            }
-            for (; g < groups; ++g) {
-                fir_group<DIR, 4>(acc, A, B, C, ld4(fp));
-                A = B; B = C; C = ld4(xp);
-                xp += 4; fp += 4;
-            }
-            if (tail) fir_group_n<DIR>(acc, A, B, C, ld4(fp), tail);
-        }
-        *reinterpret_cast<float4 *>(yrow + tb) =
-            make_float4(acc[0] * Ts, acc[1] * Ts, acc[2] * Ts, acc[3] * Ts);
-        *reinterpret_cast<float4 *>(yrow + tb + 4) =
-            make_float4(acc[4] * Ts, acc[5] * Ts, acc[6] * Ts, acc[7] * Ts);
-    }
-    __syncthreads();
-
-    // drain the result tile: contiguous row segments
-    const int tvalid = min(Tt, T - t0);
+            // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
+            float w[kFirRing];
+            const unsigned x0 = xrow + 4u * (unsigned)tb - (DIR < 0 ? 16u : 0u);
 #pragma unroll
-    for (int rr = 0; rr < kFirRows / kFirWarps; ++rr) {
-        const int r = warp + rr * kFirWarps;
-        if (r >= nrow) continue;
-        float *dst = out + (row0 + r) * (int64_t)T + t0;
-        const float *src = ys + r * SY;
-        typedef typename vec_t<V>::type vec;
-        for (int p = lane * V; p < tvalid; p += 32 * V)
-            *reinterpret_cast<vec *>(dst + p) = *reinterpret_cast<const vec *>(src + p);
+            for (int q = 0; q < kFirWin / 4; ++q) put4(w, 4 * q, ld4(x0 + 16 * q));
+            unsigned xp = DIR < 0 ? x0 - 16 : x0 + 4 * kFirWin;    // next sample quad to fetch
+            unsigned fp = fs_addr;
+            float4 f[2];
+            f[0] = ld4(fp);
+            int g = 0;
+            for (; g + kFirPhases <= groups; g += kFirPhases) {
+                fir_step<DIR, 0>(acc, w, f, fp + 16, xp);
+                fir_step<DIR, 1>(acc, w, f, fp + 32, xp + step);
+                fir_step<DIR, 2>(acc, w, f, fp + 48, xp + 2 * step);
+                fir_step<DIR, 3>(acc, w, f, fp + 64, xp + 3 * step);
+                fir_step<DIR, 4>(acc, w, f, fp + 80, xp + 4 * step);
+                fir_step<DIR, 5>(acc, w, f, fp + 96, xp + 5 * step);
+                xp += kFirPhases * step;
+                fp += 16 * kFirPhases;
+            }
+            fir_rest<DIR, 0>(acc, w, f, fp + 16, xp, groups - g, tail);
+
+            if (row < rows) {
+                float *dst = out + row * (int64_t)T + t0 + tb;
+                const int left = T - (t0 + tb);          // > 0, multiple of V
+                if (V == 4) {
+#pragma unroll
+                    for (int q = 0; q < kFirSeg / 4; ++q)
+                        if (4 * q < left)
+                            *reinterpret_cast<float4 *>(dst + 4 * q) = make_float4(
+                                acc[4 * q] * Ts, acc[4 * q + 1] * Ts, acc[4 * q + 2] * Ts, acc[4 * q + 3] * Ts);
+                } else if (V == 2) {
+#pragma unroll
+                    for (int q = 0; q < kFirSeg / 2; ++q)
+                        if (2 * q < left)
+                            *reinterpret_cast<float2 *>(dst + 2 * q) = make_float2(acc[2 * q] * Ts, acc[2 * q + 1] * Ts);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < kFirSeg; ++q)
+                        if (q < left) dst[q] = acc[q] * Ts;
+                }
+            }
+        }
     }
+    cp_async_wait<0>();
 }
 
 // Thread-per-output restatement for filters too long for the shared-memory tile.
@@ -204,6 +274,34 @@ static inline int pad_stride(int w)       // smallest s >= w with s = 4 (mod 8)
     return s;
 }
 
+constexpr int kFirTileWordsPerRow = 432;  // 2 buffers x 32 rows x 432 words = 108 KB: two CTAs per SM
+
+// Tile shape for a row length T and K taps; returns false if the filter is too long to tile.
+static bool fir_shape(int64_t T, int64_t K, FirShape &sh)
+{
+    sh.halo = (int)(((K + 3) & ~3LL) + 8);     // taps rounded up plus two quads of look-ahead
+    const int room = kFirTileWordsPerRow - 4 - sh.halo;       // words left for outputs (4 = stride padding)
+    const int nseg_max = room / kFirSeg;
+    if (nseg_max < 1) return false;
+    const int64_t segs = ceil_div(T, kFirSeg);
+    sh.ttiles = (int)ceil_div(segs, nseg_max);
+    sh.nseg = (int)ceil_div(segs, sh.ttiles);
+    sh.SX = pad_stride(sh.nseg * kFirSeg + sh.halo);
+    // Warps per CTA.  Warp w runs on scheduler w % 4 and takes segments w, w+nw, ...; pick the
+    // multiple of four whose busiest scheduler has the least work, preferring 8 warps.
+    int best_load = 1 << 30;
+    sh.nwarps = 8;
+    const int candidates[4] = {8, 12, 16, 4};
+    for (int nw : candidates) {
+        int load[4] = {0, 0, 0, 0};
+        for (int w = 0; w < nw; ++w) load[w & 3] += (sh.nseg - w + nw - 1) / nw;   // segments of warp w
+        int worst = load[0];
+        for (int k = 1; k < 4; ++k) worst = load[k] > worst ? load[k] : worst;
+        if (worst < best_load) { best_load = worst; sh.nwarps = nw; }
+    }
+    return true;
+}
+
 template <int DIR>
 static int launch_fir(float *out, const float *in, const float *filt,
                       int64_t rows, int64_t T, int64_t K, float Ts, cudaStream_t stream)
@@ -215,25 +313,10 @@ static int launch_fir(float *out, const float *in, const float *filt,
         return SLAYER_B200_OK;
     }
     const int64_t Keff = K < T ? K : T;              // taps beyond the row length never contribute
-    const int halo = (int)(((Keff + 3) & ~3LL) + 4);
-    // choose the number of 64-sample passes per tile: least padding, then fewest tiles
-    int best_p = 0;
-    int64_t best_cover = 0;
-    const size_t smem_cap = 100 * 1024;              // two CTAs per SM
-    for (int p = 8; p >= 1; --p) {
-        const int Tt = p * kFirPassLen;
-        const size_t bytes = sizeof(float) * ((size_t)((Keff + 3) & ~3LL) +
-                             (size_t)kFirRows * (pad_stride(Tt + halo) + pad_stride(Tt)));
-        if (bytes > smem_cap && p > 1) continue;
-        const int64_t cover = ceil_div(T, Tt) * Tt;
-        if (best_p == 0 || cover < best_cover) { best_p = p; best_cover = cover; }
-    }
-    const int Tt = best_p * kFirPassLen;
-    const int SX = pad_stride(Tt + halo), SY = pad_stride(Tt);
-    const size_t smem = sizeof(float) * ((size_t)((Keff + 3) & ~3LL) + (size_t)kFirRows * (SX + SY));
-    const int64_t ttiles = ceil_div(T, Tt);
-    const int64_t blocks = ceil_div(rows, kFirRows) * ttiles;
-    if (smem > 220 * 1024 || blocks > 0x7fffffffLL) {
+    FirShape sh;
+    const bool tiled = fir_shape(T, Keff, sh);
+    const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
+    if (!tiled) {
         const int64_t n = rows * T;
         int64_t g = ceil_div(n, 256);
         const int64_t cap = (int64_t)sm_count() * 32;
@@ -241,12 +324,14 @@ static int launch_fir(float *out, const float *in, const float *filt,
         fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts);
         return check_launch("fir (long filter) kernel launch");
     }
+    const size_t smem = sizeof(float) * ((size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
     const int vw = tile_vec_width(T, {out, in});
     auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
-    kern<<<(unsigned)blocks, kFirWarps * 32, smem, stream>>>(
-        out, in, filt, rows, (int)T, (int)Keff, Ts, best_p, halo, SX, SY, (int)ttiles);
+    int64_t grid = 2 * (int64_t)sm_count();
+    if (grid > ntiles) grid = ntiles;
+    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles);
     return check_launch("fir kernel launch");
 }
 

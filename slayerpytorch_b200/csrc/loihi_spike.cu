@@ -16,8 +16,7 @@
 //
 // Memory: 16 algorithmic bytes per element (read w; write s, v, u), bound by HBM.  Same
 // warp-owned 32x32 tile scheme as the SRM kernel (next input tile prefetched with cp.async):
-// the input tile is overwritten with the current u, another tile collects v, spikes leave as a
-// bit mask.
+// the input tile is overwritten with the current u, two more tiles collect v and the spikes.
 #include "common.cuh"
 #include "tile.cuh"
 
@@ -33,8 +32,9 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
-    float *tiles_u = smem + warp * (3 * kTileWords);     // two input/current tiles (prefetch ring)
+    float *tiles_u = smem + warp * (4 * kTileWords);     // two input/current tiles (prefetch ring)
     float *tile_v = tiles_u + 2 * kTileWords;            // voltage tile
+    float *tile_s = tiles_u + 3 * kTileWords;            // spike tile
     const float vMarkF = (float)vDecayMark;
 
     const int ntiles = (T + kTile - 1) / kTile;
@@ -56,19 +56,20 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
             cp_async_wait<1>();
             __syncwarp();
 
-            unsigned smask = 0u;
+            // walk the 32 steps; the next chunk is fetched before the current one is processed
+            float4 cur = *reinterpret_cast<const float4 *>(tile_u + tile_chunk(lane, 0));
 #pragma unroll 2
             for (int c4 = 0; c4 < kTile / 4; ++c4) {
-                float4 *cu = reinterpret_cast<float4 *>(tile_u + tile_chunk(lane, c4));
-                float4 *cv = reinterpret_cast<float4 *>(tile_v + tile_chunk(lane, c4));
-                const float4 in4 = *cu;
-                const float wv[4] = {in4.x, in4.y, in4.z, in4.w};
-                float uo[4], vo[4];
+                float4 nxt = cur;
+                if (c4 + 1 < kTile / 4) nxt = *reinterpret_cast<const float4 *>(tile_u + tile_chunk(lane, c4 + 1));
+                const float wv[4] = {cur.x, cur.y, cur.z, cur.w};
+                float uo[4], vo[4], so[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (it == 0 && c4 == 0 && j == 0) {   // t = 0
                         uo[j] = 0.0f;
                         vo[j] = 0.0f;
+                        so[j] = 0.0f;
                         continue;
                     }
                     const unsigned uSign = uOld >= 0 ? 1u : 0xffffffffu;
@@ -85,18 +86,20 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
                     if (spk) refLeft = refDelay;
                     uOld = (int)uT;
 
-                    smask |= (spk ? 1u : 0u) << (c4 * 4 + j);
+                    so[j] = spk ? 1.0f : 0.0f;
                     uo[j] = (float)uOld;
                     vo[j] = spk ? vMarkF : (float)vOld;
                 }
-                *cu = make_float4(uo[0], uo[1], uo[2], uo[3]);
-                *cv = make_float4(vo[0], vo[1], vo[2], vo[3]);
+                *reinterpret_cast<float4 *>(tile_u + tile_chunk(lane, c4)) = make_float4(uo[0], uo[1], uo[2], uo[3]);
+                *reinterpret_cast<float4 *>(tile_v + tile_chunk(lane, c4)) = make_float4(vo[0], vo[1], vo[2], vo[3]);
+                *reinterpret_cast<float4 *>(tile_s + tile_chunk(lane, c4)) = make_float4(so[0], so[1], so[2], so[3]);
+                cur = nxt;
             }
             __syncwarp();
 
             tile_store<V>(tile_u, u, row0, rows, t0, T, lane);
             tile_store<V>(tile_v, v, row0, rows, t0, T, lane);
-            mask_store<V>(smask, 1.0f, s, row0, rows, t0, T, lane);
+            tile_store<V>(tile_s, s, row0, rows, t0, T, lane);
             __syncwarp();
         }
     }
@@ -119,13 +122,9 @@ template <int V>
 static int launch_loihi(const LoihiArgs &a)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
-    const int sms = sm_count();
-    int warps = 8;
-    while (warps > 1 && ceil_div(nblocks, warps) < 2 * (int64_t)sms) warps >>= 1;
-    int64_t grid = ceil_div(nblocks, warps);
-    const int64_t cap = (int64_t)sms * 16;
-    if (grid > cap) grid = cap;
-    const size_t smem = (size_t)warps * 3 * kTileWords * sizeof(float);
+    int warps, grid;
+    spike_launch_shape(nblocks, 4 * kTileWords * sizeof(float), warps, grid);
+    const size_t smem = (size_t)warps * 4 * kTileWords * sizeof(float);
     auto kern = loihi_get_spikes_kernel<V>;
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;

@@ -40,7 +40,8 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     const int warps_per_block = blockDim.x >> 5;
     const int nuPad = NB > 0 ? 0 : ((nuEff + 3) & ~3);
     float *nu_s = smem;
-    float *tiles = smem + nuPad + warp * (2 * kTileWords);
+    float *tiles = smem + nuPad + warp * (3 * kTileWords);   // two potential tiles (prefetch ring)
+    float *tile_s = tiles + 2 * kTileWords;                  // spike tile
 
     if (NB == 0) {
         for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
@@ -81,12 +82,14 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
             cp_async_wait<1>();
             __syncwarp();
 
-            unsigned smask = 0u;
+            // walk the 32 steps; the next chunk is fetched before the current one is processed
+            float4 cur = *reinterpret_cast<const float4 *>(tile + tile_chunk(lane, 0));
 #pragma unroll 2
             for (int c4 = 0; c4 < kTile / 4; ++c4) {
-                float4 *chunk = reinterpret_cast<float4 *>(tile + tile_chunk(lane, c4));
-                const float4 in4 = *chunk;
-                float vv[4] = {in4.x, in4.y, in4.z, in4.w};
+                float4 nxt = cur;
+                if (c4 + 1 < kTile / 4) nxt = *reinterpret_cast<const float4 *>(tile + tile_chunk(lane, c4 + 1));
+                float vv[4] = {cur.x, cur.y, cur.z, cur.w};
+                float sv[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     float v = vv[j];
@@ -108,18 +111,20 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
                     }
                     const bool spk = v >= theta;
                     vv[j] = (spk && has_nu0) ? v + nu0 : v;
-                    smask |= (spk ? 1u : 0u) << (c4 * 4 + j);
+                    sv[j] = spk ? spikeVal : 0.0f;
 #pragma unroll
                     for (int w = W - 1; w > 0; --w)
                         hist[w] = ((hist[w] << 1) | (hist[w - 1] >> 31)) & wmask[w];
                     hist[0] = ((hist[0] << 1) | (spk ? 1u : 0u)) & wmask[0];
                 }
-                *chunk = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                *reinterpret_cast<float4 *>(tile + tile_chunk(lane, c4)) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                *reinterpret_cast<float4 *>(tile_s + tile_chunk(lane, c4)) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+                cur = nxt;
             }
             __syncwarp();
 
             tile_store<V>(tile, u, row0, rows, t0, T, lane);
-            mask_store<V>(smask, spikeVal, s, row0, rows, t0, T, lane);
+            tile_store<V>(tile_s, s, row0, rows, t0, T, lane);
             __syncwarp();
         }
     }
@@ -159,13 +164,9 @@ template <int V, int NB, int W>
 static int launch_srm(const SrmArgs &a)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
-    const int sms = sm_count();
-    int warps = 8;                                   // spread small problems over all SMs
-    while (warps > 1 && ceil_div(nblocks, warps) < 2 * (int64_t)sms) warps >>= 1;
-    int64_t grid = ceil_div(nblocks, warps);
-    const int64_t cap = (int64_t)sms * 16;
-    if (grid > cap) grid = cap;
-    const size_t smem = (size_t)((NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) + warps * 2 * kTileWords) * sizeof(float);
+    int warps, grid;
+    spike_launch_shape(nblocks, 3 * kTileWords * sizeof(float), warps, grid);
+    const size_t smem = (size_t)((NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) + warps * 3 * kTileWords) * sizeof(float);
     auto kern = srm_get_spikes_kernel<V, NB, W>;
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
@@ -177,10 +178,14 @@ template <int V>
 static int dispatch_srm(const SrmArgs &a)
 {
     const int window = a.nuEff > 1 ? a.nuEff - 1 : 0;     // history bits needed
+    if (window <= 2) return launch_srm<V, 2, 1>(a);
     if (window <= 4) return launch_srm<V, 4, 1>(a);
+    if (window <= 6) return launch_srm<V, 6, 1>(a);
     if (window <= 8) return launch_srm<V, 8, 1>(a);
+    if (window <= 10) return launch_srm<V, 10, 1>(a);
     if (window <= 12) return launch_srm<V, 12, 1>(a);
     if (window <= 16) return launch_srm<V, 16, 1>(a);
+    if (window <= 24) return launch_srm<V, 24, 1>(a);
     if (window <= 32) return launch_srm<V, 32, 1>(a);
     if (window <= 64) return launch_srm<V, 0, 2>(a);
     if (window <= 128) return launch_srm<V, 0, 4>(a);

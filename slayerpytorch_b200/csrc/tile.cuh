@@ -25,6 +25,8 @@
 
 #include <initializer_list>
 
+#include "common.cuh"
+
 namespace sb200 {
 
 constexpr int kTile = 32;                 // rows per warp = time steps per tile
@@ -136,6 +138,23 @@ __device__ __forceinline__ void mask_store(unsigned mask, float value, float *g,
                 *p = bit_value(m, c, value);
         }
     }
+}
+
+// Launch shape of the warp-per-32-rows kernels: warps per CTA and a grid that gives every SM
+// the same number of resident warps (as many as shared memory allows, at most 32), each warp
+// then strides over the row blocks.  Small problems get smaller CTAs so that all SMs take part.
+inline void spike_launch_shape(int64_t nblocks, size_t smem_per_warp, int &warps, int &grid)
+{
+    const int sms = sm_count();
+    warps = 8;
+    while (warps > 1 && (nblocks + warps - 1) / warps < 2 * (int64_t)sms) warps >>= 1;
+    int64_t per_sm_warps = (int64_t)(200 * 1024 / smem_per_warp);
+    if (per_sm_warps > 32) per_sm_warps = 32;
+    int64_t ctas_per_sm = per_sm_warps / warps;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    int64_t g = (nblocks + warps - 1) / warps;
+    if (g > ctas_per_sm * sms) g = ctas_per_sm * sms;
+    grid = (int)g;
 }
 
 // Access width the host may use for a set of [rows, T] arrays.
