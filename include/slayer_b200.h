@@ -107,6 +107,24 @@ int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const float *w,
 int slayer_b200_spike_grad(float *out, const float *g, const float *u, int64_t n,
                            float theta, float tau, float scale, void *stream);
 
+/*
+ * Read and clear the device-side status word of the current device.  Kernels that wait on a
+ * hardware barrier (bulk tensor copies) poll a bounded number of times; if a wait ever runs
+ * out they record a non-zero code here and return instead of hanging.  *status_out is 0 when
+ * nothing went wrong.  This call synchronises with the device (it copies the word back), so
+ * it belongs after a batch of work, not between launches.  It has no counterpart in the
+ * reference, whose kernels neither wait on anything nor report errors.
+ */
+int slayer_b200_device_status(int *status_out);
+
+/*
+ * Enable (non-zero, the default) or disable the bulk-tensor-copy code path of the kernels
+ * that have one (SRM getSpikes when T % 4 == 0 and buffers are 16-byte aligned); returns the
+ * previous setting.  Disabled, those kernels use their cp.async path, which computes the same
+ * results.  It has no counterpart in the reference.
+ */
+int slayer_b200_set_tma(int enable);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,8 +34,9 @@ CUDA_SOURCES = {
     "srm_spike.cu": ["-ftz=true"],
     "loihi_spike.cu": [],
     "spike_grad.cu": [],
+    "tma.cu": [],
 }
-HEADERS = ["common.cuh", "tile.cuh", os.path.join(INCLUDE, "slayer_b200.h")]
+HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", os.path.join(INCLUDE, "slayer_b200.h")]
 
 MODULES = {"slayerCuda": "bindings_slayer.cpp", "slayerLoihiCuda": "bindings_loihi.cpp"}
 

@@ -27,6 +27,8 @@ SYMBOLS = {
     "slayer_b200_srm_get_spikes": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_loihi_get_spikes": (_int, [_p, _p, _p, _p, _i64, _i64, _u32, _u32, _u32, _u32, _u32, _p]),
     "slayer_b200_spike_grad": (_int, [_p, _p, _p, _i64, _f, _f, _f, _p]),
+    "slayer_b200_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
+    "slayer_b200_set_tma": (_int, [_int]),
 }
 
 _lib = None
@@ -62,3 +64,15 @@ def call(name, *args):
     """Call an entry point by name and raise SlayerB200Error on a non-zero return code."""
     rc = getattr(load(), name)(*args)
     check(rc, name)
+
+
+def device_status():
+    """Read and clear the device-side status word of the current device (synchronises)."""
+    value = ctypes.c_int(0)
+    check(load().slayer_b200_device_status(ctypes.byref(value)), "slayer_b200_device_status")
+    return value.value
+
+
+def set_tma(enable):
+    """Enable/disable the bulk-tensor-copy kernels; returns the previous setting."""
+    return bool(load().slayer_b200_set_tma(1 if enable else 0))

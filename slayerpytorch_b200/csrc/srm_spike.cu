@@ -18,17 +18,83 @@
 //     the taps in shared memory.
 //
 // Memory: 12 algorithmic bytes per element (read u, write u, write s), bound by HBM.  A warp
-// owns 32 rows and walks them in tiles of 32 time steps through the swizzled shared-memory
-// tiles of tile.cuh, prefetching the next tile with cp.async while it works on the current one.
+// owns 32 rows and walks them in time tiles staged in swizzled shared memory, so that global
+// memory only ever sees contiguous row segments.  Two data-movement paths feed the same
+// recurrence: bulk tensor copies (TMA) when rows are 16-byte aligned, cp.async otherwise.
 #include "common.cuh"
 #include "tile.cuh"
+#include "tma.cuh"
 
 namespace sb200 {
 
 constexpr int kMaxHistWords = 8;     // register history covers refractory kernels up to 257 taps
 
-// V: global access width in floats.  NB > 0: unrolled window of NB history bits (W must be 1).
-// NB == 0: looped window of W history words.
+// Per-row state of the recurrence and one time step of it.
+// NB > 0: unrolled window of NB history bits, taps in registers (W must be 1).
+// NB == 0: looped window of W history words, taps in shared memory.
+template <int NB, int W>
+struct SrmRow {
+    unsigned hist[W];        // bit b (word b/32, bit b%32) = "spiked b+1 steps ago"
+    unsigned wmask[W];       // keeps only b <= nuEff-2
+    float nu_r[NB > 0 ? NB : 1];   // nu_r[k] = tap of a spike k+1 steps ago
+    float nu0, theta, spikeVal;
+    bool has_nu0;
+    const float *nu_s;
+
+    __device__ __forceinline__ void init(const float *__restrict__ nu, const float *nu_smem, int nuEff,
+                                         float theta_, float spikeVal_)
+    {
+        theta = theta_;
+        spikeVal = spikeVal_;
+        nu_s = nu_smem;
+        has_nu0 = nuEff >= 1;
+        nu0 = has_nu0 ? __ldg(nu) : 0.0f;
+#pragma unroll
+        for (int k = 0; k < NB; ++k) nu_r[k] = (k + 1 < nuEff) ? __ldg(nu + k + 1) : 0.0f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) {
+            const int nb = nuEff - 1 - 32 * w;
+            wmask[w] = nb >= 32 ? 0xffffffffu : (nb <= 0 ? 0u : ((1u << nb) - 1u));
+        }
+    }
+
+    __device__ __forceinline__ void reset()
+    {
+#pragma unroll
+        for (int w = 0; w < W; ++w) hist[w] = 0u;
+    }
+
+    // v: original potential in, updated potential out; returns the spike sample
+    __device__ __forceinline__ float step(float &v)
+    {
+        // refractory taps of recent spikes, oldest spike first
+        if (NB > 0) {
+#pragma unroll
+            for (int k = NB - 1; k >= 0; --k)
+                if (hist[0] & (1u << k)) v += nu_r[k];
+        } else {
+#pragma unroll
+            for (int w = W - 1; w >= 0; --w) {
+                unsigned m = hist[w];
+                while (m) {
+                    const int k = 31 - __clz(m);
+                    v += nu_s[32 * w + k + 1];
+                    m &= ~(1u << k);
+                }
+            }
+        }
+        const bool spk = v >= theta;
+        if (spk && has_nu0) v += nu0;
+#pragma unroll
+        for (int w = W - 1; w > 0; --w) hist[w] = ((hist[w] << 1) | (hist[w - 1] >> 31)) & wmask[w];
+        hist[0] = ((hist[0] << 1) | (spk ? 1u : 0u)) & wmask[0];
+        return spk ? spikeVal : 0.0f;
+    }
+};
+
+// ---------------------------------------------------------------------------------------
+// cp.async path (any alignment).  V: global access width in floats.
+// ---------------------------------------------------------------------------------------
 template <int V, int NB, int W>
 __global__ void __launch_bounds__(256)
 srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
@@ -47,29 +113,15 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
         for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
         __syncthreads();
     }
-
-    const bool has_nu0 = nuEff >= 1;
-    const float nu0 = has_nu0 ? __ldg(nu) : 0.0f;
-    float nu_r[NB > 0 ? NB : 1];     // nu_r[k] = tap of a spike k+1 steps ago
-#pragma unroll
-    for (int k = 0; k < NB; ++k) nu_r[k] = (k + 1 < nuEff) ? __ldg(nu + k + 1) : 0.0f;
-
-    // bit b of the history (word b/32, bit b%32) = "spiked b+1 steps ago"; keep b <= nuEff-2
-    unsigned wmask[W];
-#pragma unroll
-    for (int w = 0; w < W; ++w) {
-        const int nb = nuEff - 1 - 32 * w;
-        wmask[w] = nb >= 32 ? 0xffffffffu : (nb <= 0 ? 0u : ((1u << nb) - 1u));
-    }
+    SrmRow<NB, W> st;
+    st.init(nu, nu_s, nuEff, theta, spikeVal);
 
     const int ntiles = (T + kTile - 1) / kTile;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
     for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
         const int64_t row0 = rb * kTile;
-        unsigned hist[W];
-#pragma unroll
-        for (int w = 0; w < W; ++w) hist[w] = 0u;
+        st.reset();
 
         tile_prefetch<V>(tiles, u, row0, rows, 0, T, lane);
         cp_async_commit();
@@ -88,37 +140,13 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
             for (int c4 = 0; c4 < kTile / 4; ++c4) {
                 float4 nxt = cur;
                 if (c4 + 1 < kTile / 4) nxt = *reinterpret_cast<const float4 *>(tile + tile_chunk(lane, c4 + 1));
-                float vv[4] = {cur.x, cur.y, cur.z, cur.w};
-                float sv[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float v = vv[j];
-                    // refractory taps of recent spikes, oldest spike first
-                    if (NB > 0) {
-#pragma unroll
-                        for (int k = NB - 1; k >= 0; --k)
-                            if (hist[0] & (1u << k)) v += nu_r[k];
-                    } else {
-#pragma unroll
-                        for (int w = W - 1; w >= 0; --w) {
-                            unsigned m = hist[w];
-                            while (m) {
-                                const int k = 31 - __clz(m);
-                                v += nu_s[32 * w + k + 1];
-                                m &= ~(1u << k);
-                            }
-                        }
-                    }
-                    const bool spk = v >= theta;
-                    vv[j] = (spk && has_nu0) ? v + nu0 : v;
-                    sv[j] = spk ? spikeVal : 0.0f;
-#pragma unroll
-                    for (int w = W - 1; w > 0; --w)
-                        hist[w] = ((hist[w] << 1) | (hist[w - 1] >> 31)) & wmask[w];
-                    hist[0] = ((hist[0] << 1) | (spk ? 1u : 0u)) & wmask[0];
-                }
-                *reinterpret_cast<float4 *>(tile + tile_chunk(lane, c4)) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-                *reinterpret_cast<float4 *>(tile_s + tile_chunk(lane, c4)) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+                float4 sp;
+                sp.x = st.step(cur.x);
+                sp.y = st.step(cur.y);
+                sp.z = st.step(cur.z);
+                sp.w = st.step(cur.w);
+                *reinterpret_cast<float4 *>(tile + tile_chunk(lane, c4)) = cur;
+                *reinterpret_cast<float4 *>(tile_s + tile_chunk(lane, c4)) = sp;
                 cur = nxt;
             }
             __syncwarp();
@@ -128,6 +156,129 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
             __syncwarp();
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Bulk-tensor-copy path (T % 4 == 0, 16-byte aligned bases).  All global traffic is issued by
+// one lane per warp as [32 rows x 16 steps] box copies, so the other lanes spend their issue
+// slots on the recurrence only.  Per warp: a ring of four potential tiles (one being walked,
+// one whose store is in flight, two being loaded) and two spike tiles; tiles use the 64-byte
+// swizzle so that a lane reading its own row's 16-byte chunks is bank-conflict free.
+// Every wait on a load barrier is bounded: if it runs out the warp records a status code and
+// stops, so a lost copy cannot hang the GPU.
+// ---------------------------------------------------------------------------------------
+constexpr int kBoxT = 16;                       // time steps per box
+constexpr int kBoxWords = kTile * kBoxT;        // 512 words = 2 KB
+constexpr int kBoxBytes = kBoxWords * 4;
+constexpr int kUStages = 4;
+constexpr int kSStages = 2;
+constexpr int kWarpTmaWords = (kUStages + kSStages) * kBoxWords;
+constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier before giving up
+
+// word offset of the 16-byte chunk c (0..3) of row r in a 64-byte-swizzled [32 x 16] tile
+__device__ __forceinline__ int box_chunk(int r, int c) { return r * kBoxT + ((c ^ ((r >> 1) & 3)) << 2); }
+
+template <int NB, int W>
+__global__ void __launch_bounds__(256)
+srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_s,
+                          const float *__restrict__ nu, int64_t rows, int nuEff, int T,
+                          float theta, float spikeVal, int *status)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int warps_per_block = blockDim.x >> 5;
+    // tiles need 512-byte alignment for the swizzle pattern; align the base to 1 KB
+    unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    float *wtiles = reinterpret_cast<float *>(base) + warp * kWarpTmaWords;
+    float *u_tiles = wtiles;                                  // kUStages boxes
+    float *s_tiles = wtiles + kUStages * kBoxWords;           // kSStages boxes
+    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<float *>(base) + warps_per_block * kWarpTmaWords)
+                     + warp * kUStages;
+    const int nuPad = (nuEff + 3) & ~3;
+    float *nu_s = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(reinterpret_cast<float *>(base)
+                  + warps_per_block * kWarpTmaWords) + warps_per_block * kUStages);
+    (void)nuPad;
+
+    if (NB == 0) {
+        for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < kUStages; ++i) mbar_init(bars + i, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    SrmRow<NB, W> st;
+    st.init(nu, nu_s, nuEff, theta, spikeVal);
+
+    const int ntiles = (T + kBoxT - 1) / kBoxT;
+    const int64_t nblocks = (rows + kTile - 1) / kTile;
+    const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
+    unsigned k = 0;                 // tiles this warp has walked so far: stage = k % 4, phase = (k / 4) & 1
+    bool failed = false;
+    for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks && !failed; rb += wstride) {
+        const int row0 = (int)(rb * kTile);
+        st.reset();
+
+        if (lane == 0) {
+            bulk_wait_read<0>();    // every earlier store of this warp has been read out of its tiles
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                if (p < ntiles) {
+                    const unsigned sg = (k + p) % kUStages;
+                    mbar_expect_tx(bars + sg, kBoxBytes);
+                    tma_load_2d(u_tiles + sg * kBoxWords, &map_u, p * kBoxT, row0, bars + sg);
+                }
+            }
+        }
+        for (int j = 0; j < ntiles; ++j, ++k) {
+            const unsigned sg = k % kUStages;
+            float *tile = u_tiles + sg * kBoxWords;
+            float *tile_s = s_tiles + (k % kSStages) * kBoxWords;
+            if (lane == 0) {
+                // all store groups but the latest have been read: frees the potential tile that
+                // is loaded next and the spike tile that is written next
+                bulk_wait_read<1>();
+                if (j + 2 < ntiles) {
+                    const unsigned s2 = (k + 2) % kUStages;
+                    mbar_expect_tx(bars + s2, kBoxBytes);
+                    tma_load_2d(u_tiles + s2 * kBoxWords, &map_u, (j + 2) * kBoxT, row0, bars + s2);
+                }
+            }
+            __syncwarp();
+            const bool ok = mbar_wait_bounded(bars + sg, (k / kUStages) & 1u, kLoadPollLimit);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) atomicExch(status, kStatusSrmLoadTimeout);
+                failed = true;
+                break;
+            }
+
+            float4 cur = *reinterpret_cast<const float4 *>(tile + box_chunk(lane, 0));
+#pragma unroll
+            for (int c4 = 0; c4 < kBoxT / 4; ++c4) {
+                float4 nxt = cur;
+                if (c4 + 1 < kBoxT / 4) nxt = *reinterpret_cast<const float4 *>(tile + box_chunk(lane, c4 + 1));
+                float4 sp;
+                sp.x = st.step(cur.x);
+                sp.y = st.step(cur.y);
+                sp.z = st.step(cur.z);
+                sp.w = st.step(cur.w);
+                *reinterpret_cast<float4 *>(tile + box_chunk(lane, c4)) = cur;
+                *reinterpret_cast<float4 *>(tile_s + box_chunk(lane, c4)) = sp;
+                cur = nxt;
+            }
+            fence_proxy_async();    // this lane's tile writes precede the bulk stores below
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(&map_u, j * kBoxT, row0, tile);
+                tma_store_2d(&map_s, j * kBoxT, row0, tile_s);
+                bulk_commit();
+            }
+        }
+    }
+    if (lane == 0) bulk_wait<0>();  // stores must complete before the shared memory is released
 }
 
 // Direct restatement for refractory kernels too long for the register history: one thread per
@@ -158,6 +309,7 @@ struct SrmArgs {
     int nuEff, T;
     float theta, spikeVal;
     cudaStream_t stream;
+    bool use_tma;
 };
 
 template <int V, int NB, int W>
@@ -165,6 +317,23 @@ static int launch_srm(const SrmArgs &a)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
     int warps, grid;
+    if (V == 4 && a.use_tma) {
+        CUtensorMap map_u, map_s;
+        int *status = device_status_word();
+        if (status && a.rows * (int64_t)kTile < (1LL << 31) &&
+            encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B) &&
+            encode_rows_tensor_map(&map_s, a.s, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B)) {
+            spike_launch_shape(nblocks, kWarpTmaWords * sizeof(float), warps, grid);
+            const size_t smem = 1024 + (size_t)warps * (kWarpTmaWords * sizeof(float) + kUStages * sizeof(uint64_t))
+                              + (NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) * sizeof(float);
+            auto kern = srm_get_spikes_tma_kernel<NB, W>;
+            int rc = reserve_dynamic_smem((const void *)kern, smem);
+            if (rc) return rc;
+            kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, map_s, a.nu, a.rows, a.nuEff, a.T, a.theta,
+                                                                 a.spikeVal, status);
+            return check_launch("srm_get_spikes (bulk tensor copy) kernel launch");
+        }
+    }
     spike_launch_shape(nblocks, 3 * kTileWords * sizeof(float), warps, grid);
     const size_t smem = (size_t)((NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) + warps * 3 * kTileWords) * sizeof(float);
     auto kern = srm_get_spikes_kernel<V, NB, W>;
@@ -214,7 +383,7 @@ extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
             s, u, nu, rows, nuSize, T, theta, spikeVal);
         return check_launch("srm_get_spikes (long refractory kernel) launch");
     }
-    const SrmArgs a = {s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream};
+    const SrmArgs a = {s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream, tma_enabled()};
     switch (tile_vec_width(T, {s, u})) {
         case 4: return dispatch_srm<4>(a);
         case 2: return dispatch_srm<2>(a);

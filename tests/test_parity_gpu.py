@@ -327,3 +327,29 @@ def test_linearity_and_adjointness_at_full_size():
     assert abs(lhs - rhs) < 1e-6 * max(1.0, abs(lhs))
     two = G.c_conv(2 * x, f, 1.0)
     assert torch.equal(two, 2 * cx)        # scaling by a power of two is exact
+
+
+# ------------------------------------------------ both data-movement paths of SRM getSpikes
+@pytest.mark.parametrize("T,nus", [(16, 11), (300, 11), (304, 3), (2000, 34), (500, 160)])
+def test_srm_bulk_tensor_and_cp_async_paths_agree(T, nus):
+    """T % 4 == 0 and aligned buffers take the bulk-tensor-copy kernel; with it switched off the
+    cp.async kernel runs.  Both must reproduce the oracle bit for bit."""
+    from slayerpytorch_b200 import capi
+    rng = np.random.RandomState(T + nus)
+    u, nu = srm_case(rng, (3, 5, 1, 7, T), nus)
+    s_want, u_want = co.srm_get_spikes(u, nu, 10.0, 1.0)
+    try:
+        for enable in (True, False):
+            capi.set_tma(enable)
+            ud = G.dev(u)
+            s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
+            np.testing.assert_array_equal(s, s_want, err_msg="tma=%s" % enable)
+            np.testing.assert_array_equal(G.host(ud).view(np.uint32), u_want.view(np.uint32))
+    finally:
+        capi.set_tma(True)
+    assert capi.device_status() == 0
+
+
+def test_device_status_word_is_clear_after_the_suite_so_far():
+    from slayerpytorch_b200 import capi
+    assert capi.device_status() == 0
