@@ -11,11 +11,17 @@
 // registers and never writes ahead of itself, so the recurrence reads memory strictly forward
 // and time can be tiled with no state in memory between tiles.
 //
-// Two variants of the inner step:
-//   - window of up to 32 steps (NB > 0): the taps live in registers and the step is a fully
-//     unrolled run of NB predicated adds, oldest first - no loop, no branch, no memory access;
-//   - longer windows (up to 256 steps, W history words): a loop over the set history bits with
-//     the taps in shared memory.
+// Three variants of the inner step, all producing the same bits:
+//   - "ring" (refractory window shorter than the time tile and every tap negative or -0.0,
+//     which is what refractory kernels look like): the last R spike samples are kept as 0.0 / 1.0
+//     floats in a register ring indexed at compile time (the time tile is fully unrolled), and
+//     the taps are applied as v = fma(flag, tap, v), oldest first.  fma(1, tap, v) is the add
+//     the definition asks for; fma(+0, tap, v) adds -0.0 and returns v unchanged, bit for bit.
+//     No predicates, no branches: the step runs on the FMA pipe, which has twice the issue
+//     rate of the integer pipe the bit tests of the next variant need;
+//   - "bits" (window of up to 32 steps, any taps): history bits in a register, a fully
+//     unrolled run of predicated adds, oldest first;
+//   - "loop" (windows up to 256 steps): a loop over the set history bits, taps in shared memory.
 //
 // Memory: 12 algorithmic bytes per element (read u, write u, write s), bound by HBM.  A warp
 // owns 32 rows and walks them in time tiles staged in swizzled shared memory, so that global
@@ -39,6 +45,7 @@ struct SrmRow {
     float nu_r[NB > 0 ? NB : 1];   // nu_r[k] = tap of a spike k+1 steps ago
     float nu0, theta, spikeVal;
     bool has_nu0;
+    bool taps_negative;      // every tap after the first has its sign bit set (ring variant is exact)
     const float *nu_s;
 
     __device__ __forceinline__ void init(const float *__restrict__ nu, const float *nu_smem, int nuEff,
@@ -49,8 +56,12 @@ struct SrmRow {
         nu_s = nu_smem;
         has_nu0 = nuEff >= 1;
         nu0 = has_nu0 ? __ldg(nu) : 0.0f;
+        taps_negative = true;
 #pragma unroll
-        for (int k = 0; k < NB; ++k) nu_r[k] = (k + 1 < nuEff) ? __ldg(nu + k + 1) : 0.0f;
+        for (int k = 0; k < NB; ++k) {
+            nu_r[k] = (k + 1 < nuEff) ? __ldg(nu + k + 1) : -0.0f;
+            taps_negative = taps_negative && (__float_as_uint(nu_r[k]) >> 31);
+        }
 #pragma unroll
         for (int w = 0; w < W; ++w) {
             const int nb = nuEff - 1 - 32 * w;
@@ -92,6 +103,61 @@ struct SrmRow {
     }
 };
 
+// v = a * b + v with IEEE rounding and no flushing, so that a flag of +0 leaves v untouched
+__device__ __forceinline__ void fma_keep(float &v, float a, float b)
+{
+    asm("fma.rn.f32 %0, %1, %2, %0;" : "+f"(v) : "f"(a), "f"(b));
+}
+
+// Word offset of 16-byte chunk c of row r in a time tile of R steps (R = 32: 128-byte swizzle
+// of tile.cuh, R = 16: 64-byte swizzle of the bulk-tensor boxes).
+template <int R>
+__device__ __forceinline__ int chunk_of(int r, int c)
+{
+    return R == 32 ? r * 32 + ((c ^ (r & 7)) << 2) : r * 16 + ((c ^ ((r >> 1) & 3)) << 2);
+}
+
+// Walk one time tile of R steps for this lane's row: potentials are updated in place in
+// `tile`, spike samples go to `tile_s`.  RING selects the ring variant (needs NB < R).
+template <int R, bool RING, int NB, int W>
+__device__ __forceinline__ void walk_tile(float *tile, float *tile_s, SrmRow<NB, W> &st, float (&ring)[R], int lane)
+{
+    float4 cur = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, 0));
+#pragma unroll
+    for (int c4 = 0; c4 < R / 4; ++c4) {
+        float4 nxt = cur;       // the next chunk is fetched before the current one is processed
+        if (c4 + 1 < R / 4) nxt = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, c4 + 1));
+        float vv[4] = {cur.x, cur.y, cur.z, cur.w};
+        float sv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (RING) {
+                const int i = c4 * 4 + j;
+                float v = vv[j];
+#pragma unroll
+                for (int k = NB; k >= 1; --k) fma_keep(v, ring[(i - k) & (R - 1)], st.nu_r[k - 1]);
+                const bool spk = v >= st.theta;
+                ring[i] = spk ? 1.0f : 0.0f;
+                if (spk && st.has_nu0) v += st.nu0;
+                vv[j] = v;
+                sv[j] = spk ? st.spikeVal : 0.0f;
+            } else {
+                sv[j] = st.step(vv[j]);
+            }
+        }
+        *reinterpret_cast<float4 *>(tile + chunk_of<R>(lane, c4)) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        *reinterpret_cast<float4 *>(tile_s + chunk_of<R>(lane, c4)) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+        cur = nxt;
+    }
+}
+
+template <int R>
+__device__ __forceinline__ void ring_reset(float (&ring)[R])
+{
+#pragma unroll
+    for (int i = 0; i < R; ++i) ring[i] = 0.0f;
+}
+
 // ---------------------------------------------------------------------------------------
 // cp.async path (any alignment).  V: global access width in floats.
 // ---------------------------------------------------------------------------------------
@@ -115,6 +181,9 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     }
     SrmRow<NB, W> st;
     st.init(nu, nu_s, nuEff, theta, spikeVal);
+    constexpr bool kRingOk = NB > 0 && NB < kTile;
+    const bool use_ring = kRingOk && st.taps_negative;      // uniform over the grid
+    float ring[kTile];
 
     const int ntiles = (T + kTile - 1) / kTile;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
@@ -122,6 +191,7 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
         const int64_t row0 = rb * kTile;
         st.reset();
+        ring_reset(ring);
 
         tile_prefetch<V>(tiles, u, row0, rows, 0, T, lane);
         cp_async_commit();
@@ -134,21 +204,8 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
             cp_async_wait<1>();
             __syncwarp();
 
-            // walk the 32 steps; the next chunk is fetched before the current one is processed
-            float4 cur = *reinterpret_cast<const float4 *>(tile + tile_chunk(lane, 0));
-#pragma unroll 2
-            for (int c4 = 0; c4 < kTile / 4; ++c4) {
-                float4 nxt = cur;
-                if (c4 + 1 < kTile / 4) nxt = *reinterpret_cast<const float4 *>(tile + tile_chunk(lane, c4 + 1));
-                float4 sp;
-                sp.x = st.step(cur.x);
-                sp.y = st.step(cur.y);
-                sp.z = st.step(cur.z);
-                sp.w = st.step(cur.w);
-                *reinterpret_cast<float4 *>(tile + tile_chunk(lane, c4)) = cur;
-                *reinterpret_cast<float4 *>(tile_s + tile_chunk(lane, c4)) = sp;
-                cur = nxt;
-            }
+            if (use_ring) walk_tile<kTile, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
+            else walk_tile<kTile, false, NB, W>(tile, tile_s, st, ring, lane);
             __syncwarp();
 
             tile_store<V>(tile, u, row0, rows, t0, T, lane);
@@ -174,9 +231,6 @@ constexpr int kUStages = 4;
 constexpr int kSStages = 2;
 constexpr int kWarpTmaWords = (kUStages + kSStages) * kBoxWords;
 constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier before giving up
-
-// word offset of the 16-byte chunk c (0..3) of row r in a 64-byte-swizzled [32 x 16] tile
-__device__ __forceinline__ int box_chunk(int r, int c) { return r * kBoxT + ((c ^ ((r >> 1) & 3)) << 2); }
 
 template <int NB, int W>
 __global__ void __launch_bounds__(256)
@@ -212,6 +266,9 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
 
     SrmRow<NB, W> st;
     st.init(nu, nu_s, nuEff, theta, spikeVal);
+    constexpr bool kRingOk = NB > 0 && NB < kBoxT;
+    const bool use_ring = kRingOk && st.taps_negative;      // uniform over the grid
+    float ring[kBoxT];
 
     const int ntiles = (T + kBoxT - 1) / kBoxT;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
@@ -221,6 +278,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
     for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks && !failed; rb += wstride) {
         const int row0 = (int)(rb * kTile);
         st.reset();
+        ring_reset(ring);
 
         if (lane == 0) {
             bulk_wait_read<0>();    // every earlier store of this warp has been read out of its tiles
@@ -255,20 +313,8 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
                 break;
             }
 
-            float4 cur = *reinterpret_cast<const float4 *>(tile + box_chunk(lane, 0));
-#pragma unroll
-            for (int c4 = 0; c4 < kBoxT / 4; ++c4) {
-                float4 nxt = cur;
-                if (c4 + 1 < kBoxT / 4) nxt = *reinterpret_cast<const float4 *>(tile + box_chunk(lane, c4 + 1));
-                float4 sp;
-                sp.x = st.step(cur.x);
-                sp.y = st.step(cur.y);
-                sp.z = st.step(cur.z);
-                sp.w = st.step(cur.w);
-                *reinterpret_cast<float4 *>(tile + box_chunk(lane, c4)) = cur;
-                *reinterpret_cast<float4 *>(tile_s + box_chunk(lane, c4)) = sp;
-                cur = nxt;
-            }
+            if (use_ring) walk_tile<kBoxT, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
+            else walk_tile<kBoxT, false, NB, W>(tile, tile_s, st, ring, lane);
             fence_proxy_async();    // this lane's tile writes precede the bulk stores below
             __syncwarp();
             if (lane == 0) {

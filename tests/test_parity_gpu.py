@@ -25,6 +25,12 @@ def teardown_module(module):
     co.set_ftz(False)
 
 
+def assert_same_floats(got, want):
+    """Bit-exact up to NaN payloads: equal values, equal signs (so -0.0 stays -0.0), NaN where NaN."""
+    np.testing.assert_array_equal(got, want)
+    np.testing.assert_array_equal(np.signbit(got), np.signbit(want))
+
+
 def assert_close_or_equal(got, want):
     if np.array_equal(got, want):
         return
@@ -149,7 +155,7 @@ def test_srm_get_spikes_bit_exact(T, nus):
     s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
     s_want, u_want = co.srm_get_spikes(u, nu, 10.0, 1.0)
     np.testing.assert_array_equal(s, s_want)
-    np.testing.assert_array_equal(G.host(ud).view(np.uint32), u_want.view(np.uint32))
+    assert_same_floats(G.host(ud), u_want)
     assert T < 4 or s.sum() > 0
 
 
@@ -182,7 +188,7 @@ def test_srm_edge_values():
             s_want, u_want = co.srm_get_spikes(u, nu, 10.0, Ts)
             np.testing.assert_array_equal(s > 0, s_want > 0)
             np.testing.assert_allclose(s, s_want, rtol=1e-6)
-            np.testing.assert_array_equal(G.host(ud).view(np.uint32), u_want.view(np.uint32))
+            assert_same_floats(G.host(ud), u_want)
 
 
 def test_srm_trace_of_reference_fixture(golden_dir):
@@ -344,7 +350,7 @@ def test_srm_bulk_tensor_and_cp_async_paths_agree(T, nus):
             ud = G.dev(u)
             s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
             np.testing.assert_array_equal(s, s_want, err_msg="tma=%s" % enable)
-            np.testing.assert_array_equal(G.host(ud).view(np.uint32), u_want.view(np.uint32))
+            assert_same_floats(G.host(ud), u_want)
     finally:
         capi.set_tma(True)
     assert capi.device_status() == 0
