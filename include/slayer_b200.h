@@ -108,6 +108,28 @@ int slayer_b200_spike_grad(float *out, const float *g, const float *u, int64_t n
                            float theta, float tau, float scale, void *stream);
 
 /*
+ * slayer_b200_srm_get_spikes without any memory allocation, for callers that cannot allocate
+ * device memory: an application that has already given all device memory to its own pool, or
+ * code that runs where entering the CUDA allocator is not allowed (another library's callback,
+ * a process whose memory footprint has been frozen).  The regular entry point obtains a small
+ * status buffer with cudaMalloc the first time a device is used; this one keeps its scratch -
+ * one int per block of 32 rows, in which a wait that ran out leaves its trace - in a fixed
+ * 256 KB array inside the library image, resident on every GPU that loads the library until
+ * the process exits.  Same arguments and results as slayer_b200_srm_get_spikes, restricted to
+ *   - rows <= 2,097,152 (65536 blocks of 32 rows); more is rejected with SLAYER_B200_EUNSUPPORTED,
+ *   - T % 4 == 0, s and u 16-byte aligned, nuSize <= 257 (else SLAYER_B200_EUNSUPPORTED).
+ * The first call on each device resolves the array's device address and raises the kernel's
+ * shared-memory limit; make that first call outside any stream capture.  The call itself
+ * runs no cudaMalloc / cudaFree and no allocating library routine.  All calls share the one
+ * array (each launch clears the entries it uses), so calls that overlap on the GPU - two
+ * streams, two host threads - race on it: issue them on one stream or serialise them.
+ * It has no counterpart in the reference.
+ */
+int slayer_b200_srm_get_spikes_noalloc(float *s, float *u, const float *nu,
+                                       int64_t rows, int64_t nuSize, int64_t T,
+                                       float theta, float Ts, void *stream);
+
+/*
  * Read and clear the device-side status word of the current device.  Kernels that wait on a
  * hardware barrier (bulk tensor copies) poll a bounded number of times; if a wait ever runs
  * out they record a non-zero code here and return instead of hanging.  *status_out is 0 when

@@ -27,6 +27,8 @@
 // owns 32 rows and walks them in time tiles staged in swizzled shared memory, so that global
 // memory only ever sees contiguous row segments.  Two data-movement paths feed the same
 // recurrence: bulk tensor copies (TMA) when rows are 16-byte aligned, cp.async otherwise.
+#include <mutex>
+
 #include "common.cuh"
 #include "tile.cuh"
 #include "tma.cuh"
@@ -232,7 +234,11 @@ constexpr int kSStages = 2;
 constexpr int kWarpTmaWords = (kUStages + kSStages) * kBoxWords;
 constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier before giving up
 
-template <int NB, int W>
+// PER_BLOCK selects where a wait that ran out is recorded: false = the single status word of
+// the device (`status` points to one int); true = one int per block of 32 rows (`status` points
+// to an array with an entry for every row block), which the warp clears when it starts the
+// block and sets to the number of tiles walked when it finishes it.
+template <int NB, int W, bool PER_BLOCK = false>
 __global__ void __launch_bounds__(256)
 srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_s,
                           const float *__restrict__ nu, int64_t rows, int nuEff, int T,
@@ -279,6 +285,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
         const int row0 = (int)(rb * kTile);
         st.reset();
         ring_reset(ring);
+        if (PER_BLOCK && lane == 0) status[rb] = 0;
 
         if (lane == 0) {
             bulk_wait_read<0>();    // every earlier store of this warp has been read out of its tiles
@@ -308,7 +315,10 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
             __syncwarp();
             const bool ok = mbar_wait_bounded(bars + sg, (k / kUStages) & 1u, kLoadPollLimit);
             if (__any_sync(0xffffffffu, !ok)) {
-                if (lane == 0) atomicExch(status, kStatusSrmLoadTimeout);
+                if (lane == 0) {
+                    if (PER_BLOCK) status[rb] = -kStatusSrmLoadTimeout;
+                    else atomicExch(status, kStatusSrmLoadTimeout);
+                }
                 failed = true;
                 break;
             }
@@ -323,6 +333,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
                 bulk_commit();
             }
         }
+        if (PER_BLOCK && !failed && lane == 0) status[rb] = ntiles;
     }
     if (lane == 0) bulk_wait<0>();  // stores must complete before the shared memory is released
 }
@@ -407,7 +418,123 @@ static int dispatch_srm(const SrmArgs &a)
     return launch_srm<V, 0, 8>(a);
 }
 
+// ---------------------------------------------------------------------------------------
+// Entry point that allocates nothing (slayer_b200_srm_get_spikes_noalloc).
+//
+// The bulk-tensor kernel needs a little global memory of its own to leave a trace when a wait
+// runs out.  The regular entry point gets that word from cudaMalloc the first time a device is
+// used.  Some callers must not allocate device memory at all - a host application that has
+// handed all of its device memory to its own pool, code running where the allocator may not be
+// entered (inside another library's callback, or after the process has frozen its memory
+// footprint) - so this variant keeps its scratch in a fixed array that is part of the loaded
+// library image: one int per block of 32 rows, kNoAllocMaxRowBlocks of them (256 KB, held by
+// every GPU that loads the library until the process exits).
+//
+// In host code the array's name is only a handle; the device address is obtained once per
+// device with cudaGetSymbolAddress while that device is current, and that address is what the
+// kernel receives.
+// ---------------------------------------------------------------------------------------
+constexpr int kNoAllocMaxRowBlocks = 65536;                 // 2,097,152 rows
+static __device__ __align__(256) int g_noalloc_block_status[kNoAllocMaxRowBlocks];
+
+struct NoAllocDevice {
+    bool ready;
+    int *scratch;            // device address of g_noalloc_block_status on this device
+    bool smem_set[13];       // per kernel instantiation: shared-memory limit raised
+};
+static NoAllocDevice g_noalloc_dev[64];
+static std::mutex g_noalloc_mu;
+
+template <int NB, int W>
+static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev, int slot)
+{
+    const int64_t nblocks = ceil_div(a.rows, kTile);
+    CUtensorMap map_u, map_s;
+    if (!encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !encode_rows_tensor_map(&map_s, a.s, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B)) {
+        set_error("srm_get_spikes_noalloc: cannot describe the buffers for bulk tensor copies");
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    int warps, grid;
+    spike_launch_shape(nblocks, kWarpTmaWords * sizeof(float), warps, grid);
+    const size_t smem = 1024 + (size_t)warps * (kWarpTmaWords * sizeof(float) + kUStages * sizeof(uint64_t))
+                      + (NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) * sizeof(float);
+    auto kern = srm_get_spikes_tma_kernel<NB, W, true>;
+    if (!dev.smem_set[slot]) {
+        // the largest request any launch of this instantiation can make (8 warps, 257 taps)
+        const int most = 1024 + 8 * (int)(kWarpTmaWords * sizeof(float) + kUStages * sizeof(uint64_t)) + 260 * 4;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e != cudaSuccess) {
+            set_error("srm_get_spikes_noalloc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+            return SLAYER_B200_ECUDA;
+        }
+        dev.smem_set[slot] = true;
+    }
+    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, map_s, a.nu, a.rows, a.nuEff, a.T, a.theta,
+                                                         a.spikeVal, dev.scratch);
+    return check_launch("srm_get_spikes_noalloc kernel launch");
+}
+
 }  // namespace sb200
+
+extern "C" int slayer_b200_srm_get_spikes_noalloc(float *s, float *u, const float *nu,
+                                                  int64_t rows, int64_t nuSize, int64_t T,
+                                                  float theta, float Ts, void *stream_)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(rows >= 0 && nuSize >= 0 && T >= 0, "srm_get_spikes_noalloc: negative size");
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    SB200_REQUIRE(s && u && (nu || nuSize == 0), "srm_get_spikes_noalloc: null pointer");
+    SB200_REQUIRE(s != u, "srm_get_spikes_noalloc: s must not alias u");
+    const int64_t nblocks = ceil_div(rows, kTile);
+    if (nblocks > kNoAllocMaxRowBlocks) {
+        set_error("srm_get_spikes_noalloc: %lld rows exceed the %lld this entry point has scratch for",
+                  (long long)rows, (long long)kNoAllocMaxRowBlocks * kTile);
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    const int64_t nuEff = nuSize < T ? nuSize : T;
+    if (T >= (1LL << 31) - 64 || (T & 3) || !aligned16(s) || !aligned16(u) || nuEff - 1 > 32 * kMaxHistWords) {
+        set_error("srm_get_spikes_noalloc: needs T %% 4 == 0, 16-byte aligned buffers and at most %d taps",
+                  32 * kMaxHistWords + 1);
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+
+    // set-up, once per device, with that device current
+    int d = 0;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess || d < 0 || d >= 64) {
+        set_error("srm_get_spikes_noalloc: no usable current device");
+        return SLAYER_B200_ECUDA;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDevice &dev = g_noalloc_dev[d];
+    if (!dev.ready) {
+        int *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_block_status);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("srm_get_spikes_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return SLAYER_B200_ECUDA;
+        }
+        dev.scratch = ptr;
+        dev.ready = true;
+    }
+
+    const SrmArgs a = {s, u, nu, rows, (int)nuEff, (int)T, theta, 1.0f / Ts, (cudaStream_t)stream_, true};
+    const int window = a.nuEff > 1 ? a.nuEff - 1 : 0;
+    if (window <= 2) return launch_srm_noalloc<2, 1>(a, dev, 0);
+    if (window <= 4) return launch_srm_noalloc<4, 1>(a, dev, 1);
+    if (window <= 6) return launch_srm_noalloc<6, 1>(a, dev, 2);
+    if (window <= 8) return launch_srm_noalloc<8, 1>(a, dev, 3);
+    if (window <= 10) return launch_srm_noalloc<10, 1>(a, dev, 4);
+    if (window <= 12) return launch_srm_noalloc<12, 1>(a, dev, 5);
+    if (window <= 16) return launch_srm_noalloc<16, 1>(a, dev, 6);
+    if (window <= 24) return launch_srm_noalloc<24, 1>(a, dev, 7);
+    if (window <= 32) return launch_srm_noalloc<32, 1>(a, dev, 8);
+    if (window <= 64) return launch_srm_noalloc<0, 2>(a, dev, 9);
+    if (window <= 128) return launch_srm_noalloc<0, 4>(a, dev, 10);
+    return launch_srm_noalloc<0, 8>(a, dev, 11);
+}
 
 extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
                                           int64_t rows, int64_t nuSize, int64_t T,
