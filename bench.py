@@ -50,7 +50,7 @@ KERNEL_OF = {"conv": "fir_kernel", "corr": "fir_kernel", "getSpikes": "srm_get_s
              "shift": "shift_vec4_kernel", "spikeGrad": "spike_grad_vec4_kernel"}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count); see the summaries under profiles/.  None = not captured yet.
-NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": None, "srm_get_spikes_kernel": None,
+NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_kernel": 12.13,
                            "shift_vec4_kernel": None, "spike_grad_vec4_kernel": None}
 
 
@@ -138,7 +138,7 @@ def make_workload(ops, device, seed, batch=BATCH):
     ga2 = ops.corr(gu2, srm, Ts)
     g1 = torch.einsum("oc,not->nct", w2, ga2[:, :, 0, 0, :]).reshape(batch, N_HID, 1, 1, T).contiguous()
     rates = {"hidden": float(s1.mean()), "output": float(s2.mean())}
-    return dict(a1=a1, a2=a2, g1=g1, g2=g2, delay=delay, srm=srm, ref=ref, rates=rates,
+    return dict(a1=a1, a2=a2, g1=g1, g2=g2, delay=delay, neg_delay=-delay, srm=srm, ref=ref, rates=rates,
                 theta=theta, tau=tau, scale=scale, Ts=Ts)
 
 
@@ -152,7 +152,7 @@ def hot_path(ops, wl, record=None):
     s1 = run("getSpikes", True, lambda: ops.getSpikes(u1, ref, theta, Ts))
     d1 = run("shift", True, lambda: ops.shift(s1, delay, Ts))
     # hidden layer: backward
-    b1 = run("shift", True, lambda: ops.shift(wl["g1"], -delay, Ts))
+    b1 = run("shift", True, lambda: ops.shift(wl["g1"], wl["neg_delay"], Ts))
     b2 = run("spikeGrad", True, lambda: ops.spikeGrad(b1, u1, theta, tau, scale))
     b3 = run("corr", True, lambda: ops.corr(b2, srm, Ts))
     # output layer: forward and backward
@@ -170,7 +170,7 @@ LAUNCHES_PER_STEP = 10
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
 
-    def __init__(self, device_index, period=0.005):
+    def __init__(self, device_index, period=0.002):
         super().__init__(daemon=True)
         self.period = period
         self.samples, self.reasons = [], set()
@@ -520,7 +520,7 @@ def time_reference_cuda(ops, steps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-scaled", action="store_true", help="skip the batch-scaled (>= 1 GiB tensors) variant")
