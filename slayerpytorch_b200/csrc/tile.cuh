@@ -146,11 +146,20 @@ __device__ __forceinline__ void mask_store(unsigned mask, float value, float *g,
 inline void spike_launch_shape(int64_t nblocks, size_t smem_per_warp, int &warps, int &grid)
 {
     const int sms = sm_count();
+    // CTA size that packs the most warps into one SM's shared memory (ties: the larger CTA)
+    const size_t budget = 216 * 1024;
+    int best_total = 0;
     warps = 8;
+    for (int w = 8; w >= 3; --w) {
+        const size_t per_cta = (size_t)w * smem_per_warp + 2048;       // tiles + barriers/taps/reserve
+        int ctas = (int)(budget / per_cta);
+        if (ctas * w > 32) ctas = 32 / w;
+        if (ctas * w > best_total) { best_total = ctas * w; warps = w; }
+    }
+    // small problems: smaller CTAs so that every SM takes part
     while (warps > 1 && (nblocks + warps - 1) / warps < 2 * (int64_t)sms) warps >>= 1;
-    int64_t per_sm_warps = (int64_t)(200 * 1024 / smem_per_warp);
-    if (per_sm_warps > 32) per_sm_warps = 32;
-    int64_t ctas_per_sm = per_sm_warps / warps;
+    int64_t ctas_per_sm = (int64_t)(budget / ((size_t)warps * smem_per_warp + 2048));
+    if (ctas_per_sm * warps > 32) ctas_per_sm = 32 / warps;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     int64_t g = (nblocks + warps - 1) / warps;
     if (g > ctas_per_sm * sms) g = ctas_per_sm * sms;
