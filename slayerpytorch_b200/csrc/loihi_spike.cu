@@ -37,24 +37,55 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
     float *tile_s = tiles_u + 3 * kTileWords;            // spike tile
     const float vMarkF = (float)vDecayMark;
 
-    const int ntiles = (T + kTile - 1) / kTile;
+    // The warp's work is one stream of tiles: all time tiles of its first block of 32 rows, then
+    // of its next block, ...  The tile after the current one - possibly the first tile of the
+    // next row block - is always in flight, so a change of row block costs no memory latency.
+    // V == 4 uses row-skewed tiles (tile.cuh): 16-byte accesses on 32-byte boundaries for any T.
+    // Samples before a row's start are padded with zeros and the sample at t = 0 is replaced by
+    // zero: with zero input the neuron's state stays zero and its outputs are zero, which is
+    // exactly what the definition prescribes for t = 0 (the host only picks this variant when
+    // theta is non-negative as a signed int, so that 0 > theta cannot fire).
+    const int ntiles = V == 4 ? skew_tiles(T) : (T + kTile - 1) / kTile;
+    const unsigned phase = (unsigned)(reinterpret_cast<uintptr_t>(w) >> 2) & 7u;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
-    for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
-        const int64_t row0 = rb * kTile;
-        int uOld = 0, vOld = 0;
-        unsigned refLeft = 0;                // steps until the refractory state clears
+    int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
+    if (rb >= nblocks) return;
+    int64_t rb_next = rb;           // (row block, tile) of the tile to prefetch next
+    int it_next = 0;
+    int skew = V == 4 ? block_skew(rb * kTile, T, phase) : 0;
+    int skew_next = skew;
+    int uOld = 0, vOld = 0;
+    unsigned refLeft = 0;           // steps until the refractory state clears
 
-        tile_prefetch<V>(tiles_u, w, row0, rows, 0, T, lane);
-        cp_async_commit();
-        for (int it = 0; it < ntiles; ++it) {
+    auto prefetch = [&](float *dst) {
+        if (V == 4) tile_prefetch_skew(dst, w, rb_next * kTile, rows, it_next, T, lane, skew_next, 0.0f);
+        else tile_prefetch<V>(dst, w, rb_next * kTile, rows, it_next * kTile, T, lane);
+        if (++it_next == ntiles) {
+            it_next = 0;
+            rb_next += wstride;
+            if (V == 4 && rb_next < nblocks) skew_next = block_skew(rb_next * kTile, T, phase);
+        }
+    };
+    prefetch(tiles_u);
+    cp_async_commit();
+
+    {
+        int it = 0;
+        for (unsigned q = 0; rb < nblocks; ++q) {
+            const int64_t row0 = rb * kTile;
             const int t0 = it * kTile;
-            float *tile_u = tiles_u + (it & 1) * kTileWords;
-            if (it + 1 < ntiles)
-                tile_prefetch<V>(tiles_u + ((it + 1) & 1) * kTileWords, w, row0, rows, t0 + kTile, T, lane);
+            float *tile_u = tiles_u + (q & 1) * kTileWords;
+            if (it == 0) {
+                uOld = 0;
+                vOld = 0;
+                refLeft = 0;
+            }
+            if (rb_next < nblocks) prefetch(tiles_u + ((q + 1) & 1) * kTileWords);
             cp_async_commit();
             cp_async_wait<1>();
             __syncwarp();
+            if (V == 4 && it == 0) tile_u[tile_word(lane, row_skew(skew, lane, T))] = 0.0f;   // w[t = 0] is ignored
 
             // walk the 32 steps; the next chunk is fetched before the current one is processed
             float4 cur = *reinterpret_cast<const float4 *>(tile_u + tile_chunk(lane, 0));
@@ -66,7 +97,7 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
                 float uo[4], vo[4], so[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    if (it == 0 && c4 == 0 && j == 0) {   // t = 0
+                    if (V != 4 && it == 0 && c4 == 0 && j == 0) {   // t = 0
                         uo[j] = 0.0f;
                         vo[j] = 0.0f;
                         so[j] = 0.0f;
@@ -97,10 +128,21 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
             }
             __syncwarp();
 
-            tile_store<V>(tile_u, u, row0, rows, t0, T, lane);
-            tile_store<V>(tile_v, v, row0, rows, t0, T, lane);
-            tile_store<V>(tile_s, s, row0, rows, t0, T, lane);
+            if (V == 4) {
+                tile_store_skew(tile_u, u, row0, rows, it, T, lane, skew);
+                tile_store_skew(tile_v, v, row0, rows, it, T, lane, skew);
+                tile_store_skew(tile_s, s, row0, rows, it, T, lane, skew);
+            } else {
+                tile_store<V>(tile_u, u, row0, rows, t0, T, lane);
+                tile_store<V>(tile_v, v, row0, rows, t0, T, lane);
+                tile_store<V>(tile_s, s, row0, rows, t0, T, lane);
+            }
             __syncwarp();
+            if (++it == ntiles) {
+                it = 0;
+                rb += wstride;
+                if (V == 4 && rb < nblocks) skew = block_skew(rb * kTile, T, phase);
+            }
         }
     }
 }
@@ -152,7 +194,12 @@ extern "C" int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const 
                   "loihi_get_spikes: output buffers must be distinct");
     const LoihiArgs a = {s, v, u, w, rows, (int)T, 1u << (6 + wgtExp), (int)theta,
                          4096u - iDecay, 4096u - vDecay, (int)vDecay, refDelay, (cudaStream_t)stream_};
-    switch (tile_vec_width(T, {s, v, u, w})) {
+    // 16-byte aligned buffers and a threshold below 2^31: row-skewed 16-byte tiles for any T;
+    // otherwise the widest access the alignment allows
+    int vw = tile_vec_width(T, {s, v, u, w});
+    if (all_aligned16({s, v, u, w}) && theta < 0x80000000u) vw = 4;
+    else if (vw == 4) vw = 2;
+    switch (vw) {
         case 4: return launch_loihi<4>(a);
         case 2: return launch_loihi<2>(a);
         default: return launch_loihi<1>(a);

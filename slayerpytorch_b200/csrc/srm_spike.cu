@@ -26,7 +26,8 @@
 // Memory: 12 algorithmic bytes per element (read u, write u, write s), bound by HBM.  A warp
 // owns 32 rows and walks them in time tiles staged in swizzled shared memory, so that global
 // memory only ever sees contiguous row segments.  Two data-movement paths feed the same
-// recurrence: bulk tensor copies (TMA) when rows are 16-byte aligned, cp.async otherwise.
+// recurrence: bulk tensor copies (TMA) when rows are 32-byte aligned (T % 8 == 0), cp.async
+// with row-skewed tiles otherwise.
 #include <mutex>
 
 #include "common.cuh"
@@ -187,32 +188,64 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     const bool use_ring = kRingOk && st.taps_negative;      // uniform over the grid
     float ring[kTile];
 
-    const int ntiles = (T + kTile - 1) / kTile;
+    // The warp's work is one stream of tiles: all time tiles of its first block of 32 rows, then
+    // of its next block, ...  The tile after the current one - possibly the first tile of the
+    // next row block - is always in flight, so a change of row block costs no memory latency.
+    // V == 4 uses row-skewed tiles (tile.cuh): 16-byte accesses on 32-byte boundaries for any T.
+    // Samples before a row's start are padded with -inf, which can neither spike nor be changed
+    // by a refractory tap, so the skewed lanes idle through them with their state untouched.
+    const int ntiles = V == 4 ? skew_tiles(T) : (T + kTile - 1) / kTile;
+    const unsigned phase = (unsigned)(reinterpret_cast<uintptr_t>(u) >> 2) & 7u;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
-    for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks; rb += wstride) {
+    int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
+    if (rb >= nblocks) return;
+    int64_t rb_next = rb;           // (row block, tile) of the tile to prefetch next
+    int it_next = 0;
+    int skew = V == 4 ? block_skew(rb * kTile, T, phase) : 0;        // of the block being walked
+    int skew_next = skew;                                             // of the block being prefetched
+    unsigned q = 0;                 // tiles walked so far: buffer = q & 1
+
+    auto prefetch = [&](float *dst) {
+        if (V == 4) tile_prefetch_skew(dst, u, rb_next * kTile, rows, it_next, T, lane, skew_next, -INFINITY);
+        else tile_prefetch<V>(dst, u, rb_next * kTile, rows, it_next * kTile, T, lane);
+        if (++it_next == ntiles) {
+            it_next = 0;
+            rb_next += wstride;
+            if (V == 4 && rb_next < nblocks) skew_next = block_skew(rb_next * kTile, T, phase);
+        }
+    };
+    prefetch(tiles);
+    cp_async_commit();
+
+    for (int it = 0; rb < nblocks; ++q) {
         const int64_t row0 = rb * kTile;
-        st.reset();
-        ring_reset(ring);
-
-        tile_prefetch<V>(tiles, u, row0, rows, 0, T, lane);
+        float *tile = tiles + (q & 1) * kTileWords;
+        if (it == 0) {
+            st.reset();
+            ring_reset(ring);
+        }
+        if (rb_next < nblocks) prefetch(tiles + ((q + 1) & 1) * kTileWords);
         cp_async_commit();
-        for (int it = 0; it < ntiles; ++it) {
-            const int t0 = it * kTile;
-            float *tile = tiles + (it & 1) * kTileWords;
-            if (it + 1 < ntiles)
-                tile_prefetch<V>(tiles + ((it + 1) & 1) * kTileWords, u, row0, rows, t0 + kTile, T, lane);
-            cp_async_commit();
-            cp_async_wait<1>();
-            __syncwarp();
+        cp_async_wait<1>();
+        __syncwarp();
 
-            if (use_ring) walk_tile<kTile, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
-            else walk_tile<kTile, false, NB, W>(tile, tile_s, st, ring, lane);
-            __syncwarp();
+        if (use_ring) walk_tile<kTile, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
+        else walk_tile<kTile, false, NB, W>(tile, tile_s, st, ring, lane);
+        __syncwarp();
 
-            tile_store<V>(tile, u, row0, rows, t0, T, lane);
-            tile_store<V>(tile_s, s, row0, rows, t0, T, lane);
-            __syncwarp();
+        if (V == 4) {
+            tile_store_skew(tile, u, row0, rows, it, T, lane, skew);
+            tile_store_skew(tile_s, s, row0, rows, it, T, lane, skew);
+        } else {
+            tile_store<V>(tile, u, row0, rows, it * kTile, T, lane);
+            tile_store<V>(tile_s, s, row0, rows, it * kTile, T, lane);
+        }
+        __syncwarp();
+        if (++it == ntiles) {
+            it = 0;
+            rb += wstride;
+            if (V == 4 && rb < nblocks) skew = block_skew(rb * kTile, T, phase);
         }
     }
 }
@@ -276,64 +309,69 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
     const bool use_ring = kRingOk && st.taps_negative;      // uniform over the grid
     float ring[kBoxT];
 
+    // The warp's work is one stream of tiles: all time tiles of its first block of 32 rows, then
+    // of its next block, ...  Loads run two tiles ahead of the walk across row-block boundaries,
+    // so a change of row block costs no memory latency.  Tile q uses potential stage q % 4
+    // (barrier phase (q / 4) & 1) and spike stage q % 2.
     const int ntiles = (T + kBoxT - 1) / kBoxT;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
-    unsigned k = 0;                 // tiles this warp has walked so far: stage = k % 4, phase = (k / 4) & 1
-    bool failed = false;
-    for (int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp; rb < nblocks && !failed; rb += wstride) {
+    int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
+    int64_t rb_next = rb;           // (row block, tile) of the next tile to load
+    int j_next = 0;
+    unsigned q_next = 0;
+    auto issue_load = [&]() {       // lane 0 only
+        const unsigned sg = q_next % kUStages;
+        mbar_expect_tx(bars + sg, kBoxBytes);
+        tma_load_2d(u_tiles + sg * kBoxWords, &map_u, j_next * kBoxT, (int)(rb_next * kTile), bars + sg);
+        ++q_next;
+        if (++j_next == ntiles) { j_next = 0; rb_next += wstride; }
+    };
+    if (lane == 0) {
+        if (rb_next < nblocks) issue_load();
+        if (rb_next < nblocks) issue_load();
+    }
+    int j = 0;
+    for (unsigned q = 0; rb < nblocks; ++q) {
         const int row0 = (int)(rb * kTile);
-        st.reset();
-        ring_reset(ring);
-        if (PER_BLOCK && lane == 0) status[rb] = 0;
-
+        const unsigned sg = q % kUStages;
+        float *tile = u_tiles + sg * kBoxWords;
+        float *tile_s = s_tiles + (q % kSStages) * kBoxWords;
+        if (j == 0) {
+            st.reset();
+            ring_reset(ring);
+            if (PER_BLOCK && lane == 0) status[rb] = 0;
+        }
         if (lane == 0) {
-            bulk_wait_read<0>();    // every earlier store of this warp has been read out of its tiles
-#pragma unroll
-            for (int p = 0; p < 2; ++p) {
-                if (p < ntiles) {
-                    const unsigned sg = (k + p) % kUStages;
-                    mbar_expect_tx(bars + sg, kBoxBytes);
-                    tma_load_2d(u_tiles + sg * kBoxWords, &map_u, p * kBoxT, row0, bars + sg);
-                }
-            }
+            // all store groups but the latest have been read out of shared memory: that frees
+            // the potential tile that is loaded next and the spike tile that is written next
+            bulk_wait_read<1>();
+            if (rb_next < nblocks) issue_load();
         }
-        for (int j = 0; j < ntiles; ++j, ++k) {
-            const unsigned sg = k % kUStages;
-            float *tile = u_tiles + sg * kBoxWords;
-            float *tile_s = s_tiles + (k % kSStages) * kBoxWords;
+        __syncwarp();
+        const bool ok = mbar_wait_bounded(bars + sg, (q / kUStages) & 1u, kLoadPollLimit);
+        if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) {
-                // all store groups but the latest have been read: frees the potential tile that
-                // is loaded next and the spike tile that is written next
-                bulk_wait_read<1>();
-                if (j + 2 < ntiles) {
-                    const unsigned s2 = (k + 2) % kUStages;
-                    mbar_expect_tx(bars + s2, kBoxBytes);
-                    tma_load_2d(u_tiles + s2 * kBoxWords, &map_u, (j + 2) * kBoxT, row0, bars + s2);
-                }
+                if (PER_BLOCK) status[rb] = -kStatusSrmLoadTimeout;
+                else atomicExch(status, kStatusSrmLoadTimeout);
             }
-            __syncwarp();
-            const bool ok = mbar_wait_bounded(bars + sg, (k / kUStages) & 1u, kLoadPollLimit);
-            if (__any_sync(0xffffffffu, !ok)) {
-                if (lane == 0) {
-                    if (PER_BLOCK) status[rb] = -kStatusSrmLoadTimeout;
-                    else atomicExch(status, kStatusSrmLoadTimeout);
-                }
-                failed = true;
-                break;
-            }
+            break;
+        }
 
-            if (use_ring) walk_tile<kBoxT, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
-            else walk_tile<kBoxT, false, NB, W>(tile, tile_s, st, ring, lane);
-            fence_proxy_async();    // this lane's tile writes precede the bulk stores below
-            __syncwarp();
-            if (lane == 0) {
-                tma_store_2d(&map_u, j * kBoxT, row0, tile);
-                tma_store_2d(&map_s, j * kBoxT, row0, tile_s);
-                bulk_commit();
-            }
+        if (use_ring) walk_tile<kBoxT, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
+        else walk_tile<kBoxT, false, NB, W>(tile, tile_s, st, ring, lane);
+        fence_proxy_async();    // this lane's tile writes precede the bulk stores below
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(&map_u, j * kBoxT, row0, tile);
+            tma_store_2d(&map_s, j * kBoxT, row0, tile_s);
+            bulk_commit();
         }
-        if (PER_BLOCK && !failed && lane == 0) status[rb] = ntiles;
+        if (++j == ntiles) {
+            if (PER_BLOCK && lane == 0) status[rb] = ntiles;
+            j = 0;
+            rb += wstride;
+        }
     }
     if (lane == 0) bulk_wait<0>();  // stores must complete before the shared memory is released
 }
@@ -374,7 +412,7 @@ static int launch_srm(const SrmArgs &a)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
     int warps, grid;
-    if (V == 4 && a.use_tma) {
+    if (V == 4 && a.use_tma && (a.T & 7) == 0) {
         CUtensorMap map_u, map_s;
         int *status = device_status_word();
         if (status && a.rows * (int64_t)kTile < (1LL << 31) &&
@@ -557,7 +595,9 @@ extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
         return check_launch("srm_get_spikes (long refractory kernel) launch");
     }
     const SrmArgs a = {s, u, nu, rows, (int)nuEff, (int)T, theta, spikeVal, stream, tma_enabled()};
-    switch (tile_vec_width(T, {s, u})) {
+    // 16-byte aligned buffers: row-skewed 16-byte tiles (or bulk tensor copies when rows are
+    // sector aligned); otherwise the widest access the alignment allows
+    switch (all_aligned16({s, u}) ? 4 : tile_vec_width(T, {s, u})) {
         case 4: return dispatch_srm<4>(a);
         case 2: return dispatch_srm<2>(a);
         default: return dispatch_srm<1>(a);

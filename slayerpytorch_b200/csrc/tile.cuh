@@ -110,35 +110,80 @@ __device__ __forceinline__ void tile_store(const float *tile, float *g,
     }
 }
 
-__device__ __forceinline__ float bit_value(unsigned m, int bit, float value) { return ((m >> bit) & 1u) ? value : 0.0f; }
+// ---------------------------------------------------------------------------------------
+// Row-skewed tiles.  A row of T samples starts wherever (row * T) falls; when T is not a
+// multiple of 8 most rows start in the middle of a 32-byte sector (and, when T is not a
+// multiple of 4, off a 16-byte boundary), and tiles cut at the same time index for every row
+// then cost half-used sectors or narrow accesses.  Rows are independent, so each lane may run
+// its row a few steps behind the others: row r's tiles start at time 32*j - a_r with
+// a_r = (base/4 + row*T) mod 8, which puts every tile on a 32-byte boundary of memory.  Then
+// all chunks move as 16-byte vectors whatever T is; only the (at most two) chunks that
+// straddle the ends of a row are moved sample by sample.  Columns before the row start are
+// filled with `pad` (the recurrences choose a value that keeps their state untouched), columns
+// past the row end with zeros, and neither is ever stored.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ int row_skew(int skew0, int r, int T) { return (skew0 + r * (T & 7)) & 7; }
 
-// Write a 0/value image of per-row bit masks (lane r holds the 32 time bits of row r).
-template <int V>
-__device__ __forceinline__ void mask_store(unsigned mask, float value, float *g,
-                                           int64_t row0, int64_t rows, int t0, int T, int lane)
+// skew of the first row of a block of 32 rows; phase = (base address / 4) mod 8
+__device__ __forceinline__ int block_skew(int64_t row0, int T, unsigned phase)
 {
-    constexpr int LPR = kTile / V;
-    constexpr int RPI = 32 / LPR;
-    const int c = (lane % LPR) * V;
-    const int rsub = lane / LPR;
+    return (int)((phase + (unsigned)((uint64_t)row0 * (uint64_t)T)) & 7u);
+}
+
+__device__ __forceinline__ void tile_prefetch_skew(float *tile, const float *g, int64_t row0, int64_t rows,
+                                                   int j, int T, int lane, int skew0, float pad)
+{
+    const int c = (lane & 7) * 4;
+    const int rsub = lane >> 3;
     const int64_t nrow = rows - row0;
-    const bool col_ok = t0 + c < T;
 #pragma unroll
-    for (int i = 0; i < kTile / RPI; ++i) {
-        const int r = i * RPI + rsub;
-        const unsigned m = __shfl_sync(0xffffffffu, mask, r);
-        if (col_ok && r < nrow) {
-            float *p = g + (row0 + r) * (int64_t)T + t0 + c;
-            if (V == 4)
-                *reinterpret_cast<float4 *>(p) = make_float4(bit_value(m, c, value), bit_value(m, c + 1, value),
-                                                             bit_value(m, c + 2, value), bit_value(m, c + 3, value));
-            else if (V == 2)
-                *reinterpret_cast<float2 *>(p) = make_float2(bit_value(m, c, value), bit_value(m, c + 1, value));
-            else
-                *p = bit_value(m, c, value);
+    for (int i = 0; i < kTile / 4; ++i) {
+        const int r = i * 4 + rsub;
+        const int t = kTile * j - row_skew(skew0, r, T) + c;      // time of the chunk's first sample
+        float *dst = tile + tile_word(r, c);
+        const float *src = g + (row0 + r) * (int64_t)T + t;
+        if (r >= nrow || t >= T) {
+            cp_async<16>(dst, g, false);
+        } else if (t >= 0 && t + 4 <= T) {
+            cp_async<16>(dst, src, true);
+        } else if (t + 4 <= 0) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(pad, pad, pad, pad);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (t + e < 0) dst[e] = pad;
+                else cp_async<4>(dst + e, (t + e < T) ? src + e : g, t + e < T);
+            }
         }
     }
 }
+
+__device__ __forceinline__ void tile_store_skew(const float *tile, float *g, int64_t row0, int64_t rows,
+                                                int j, int T, int lane, int skew0)
+{
+    const int c = (lane & 7) * 4;
+    const int rsub = lane >> 3;
+    const int64_t nrow = rows - row0;
+#pragma unroll
+    for (int i = 0; i < kTile / 4; ++i) {
+        const int r = i * 4 + rsub;
+        const int t = kTile * j - row_skew(skew0, r, T) + c;
+        if (r >= nrow || t >= T || t + 4 <= 0) continue;
+        const float4 v = *reinterpret_cast<const float4 *>(tile + tile_word(r, c));
+        float *dst = g + (row0 + r) * (int64_t)T + t;
+        if (t >= 0 && t + 4 <= T) {
+            *reinterpret_cast<float4 *>(dst) = v;
+        } else {
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (t + k >= 0 && t + k < T) dst[k] = e[k];
+        }
+    }
+}
+
+// number of 32-step tiles that cover a row of T samples for every skew (0..7)
+__host__ __device__ inline int skew_tiles(int T) { return (T + 7 + kTile - 1) / kTile; }
 
 // Launch shape of the warp-per-32-rows kernels: warps per CTA and a grid that gives every SM
 // the same number of resident warps (as many as shared memory allows, at most 32), each warp
@@ -164,6 +209,14 @@ inline void spike_launch_shape(int64_t nblocks, size_t smem_per_warp, int &warps
     int64_t g = (nblocks + warps - 1) / warps;
     if (g > ctas_per_sm * sms) g = ctas_per_sm * sms;
     grid = (int)g;
+}
+
+// true if every array starts on a 16-byte boundary (what the row-skewed tiles need)
+inline bool all_aligned16(std::initializer_list<const void *> ptrs)
+{
+    uintptr_t bits = 0;
+    for (const void *p : ptrs) bits |= reinterpret_cast<uintptr_t>(p);
+    return (bits & 15u) == 0;
 }
 
 // Access width the host may use for a set of [rows, T] arrays.
