@@ -4,15 +4,17 @@
 // covers every row of the batch; the per-neuron table is indexed by row % nNeurons.
 //
 // Work split: a group of LPR lanes (a power of two, up to a full warp) owns one row and
-// strides along time, so every global access of a group is contiguous.  When the row length
-// is a multiple of four and both buffers are 16-byte aligned, every access is a 128-bit
-// vector: the store is aligned, and the shifted source vector is assembled from the two
-// aligned source vectors that straddle it.  Because T % 4 == 0, an aligned source vector is
-// either wholly inside its row or wholly outside, so zero fill stays exact.
+// strides along time, so every global access of a group is contiguous.  When both buffers are
+// 16-byte aligned the row is walked in aligned 16-byte quads: a quad is one aligned 128-bit
+// store assembled from the two aligned source quads that straddle its source.  With T % 4 == 0
+// a quad is either wholly inside its row or wholly outside, so zero fill stays exact; for any
+// other row length the few quads at the ends of a row (or whose source crosses an end) go
+// sample by sample and no neighbouring row is touched.
 #include "common.cuh"
 
 namespace sb200 {
 
+// Row length a multiple of four: every aligned quad of the flat array lies inside one row.
 template <bool LUT>
 __global__ void __launch_bounds__(256)
 shift_vec4_kernel(float4 *__restrict__ out, const float4 *__restrict__ in,
@@ -56,6 +58,60 @@ shift_vec4_kernel(float4 *__restrict__ out, const float4 *__restrict__ in,
     }
 }
 
+// Any row length (16-byte aligned buffers): rows start anywhere in a quad.
+template <bool LUT>
+__global__ void __launch_bounds__(256)
+shift_flat4_kernel(float *__restrict__ out, const float *__restrict__ in,
+                  const float *__restrict__ lut, float shift, float Ts,
+                  int64_t rows, int T, int64_t nNeurons, int lpr_log2)
+{
+    const int lpr = 1 << lpr_log2;
+    const int lane_in_row = threadIdx.x & (lpr - 1);
+    const int64_t groups_per_block = blockDim.x >> lpr_log2;
+    const int64_t group0 = (int64_t)blockIdx.x * groups_per_block + (threadIdx.x >> lpr_log2);
+    const int64_t group_stride = (int64_t)gridDim.x * groups_per_block;
+    const int64_t total = rows * (int64_t)T;
+    const float4 *in4 = reinterpret_cast<const float4 *>(in);
+    float4 *out4 = reinterpret_cast<float4 *>(out);
+
+    for (int64_t row = group0; row < rows; row += group_stride) {
+        const float sv = LUT ? __ldg(lut + (row % nNeurons)) : shift;
+        const int d = shift_steps(sv, Ts);
+        const int64_t S = row * (int64_t)T, E = S + T;        // the row as a range of the flat array
+        const bool all_zero = d >= T || d <= -T;
+        // aligned 16-byte quads of the flat array that touch the row
+        for (int64_t q = (S >> 2) + lane_in_row; q < ((E + 3) >> 2); q += lpr) {
+            const int64_t F = q << 2;
+            const int64_t src = F - d;                            // flat index of the first source sample
+            if (F >= S && F + 4 <= E && all_zero) {
+                out4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else if (F >= S && F + 4 <= E && src >= S && src + 4 <= E && (src & ~3LL) + 8 <= total) {
+                // whole quad inside the row and fed from inside the row: two aligned source quads
+                const int64_t a = src >> 2;
+                const int o = (int)(src & 3);
+                const float4 v0 = __ldg(in4 + a);
+                float4 r = v0;
+                if (o != 0) {
+                    const float4 v1 = __ldg(in4 + a + 1);
+                    if (o == 1) r = make_float4(v0.y, v0.z, v0.w, v1.x);
+                    else if (o == 2) r = make_float4(v0.z, v0.w, v1.x, v1.y);
+                    else r = make_float4(v0.w, v1.x, v1.y, v1.z);
+                }
+                out4[q] = r;
+            } else {
+                // a quad at an end of the row, or one whose source crosses an end: sample by sample
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int64_t e = F + k;
+                    if (e < S || e >= E) continue;
+                    const int64_t ts = e - S - d;
+                    out[e] = (ts >= 0 && ts < T) ? __ldg(in + S + ts) : 0.0f;
+                }
+            }
+        }
+    }
+}
+
 template <bool LUT>
 __global__ void __launch_bounds__(256)
 shift_scalar_kernel(float *__restrict__ out, const float *__restrict__ in,
@@ -85,8 +141,10 @@ static int launch_shift(float *out, const float *in, const float *lut, float shi
                         int64_t rows, int64_t T, int64_t nNeurons, cudaStream_t stream)
 {
     if (rows == 0 || T == 0) return SLAYER_B200_OK;
-    const bool vec = (T % 4 == 0) && aligned16(out) && aligned16(in);
-    const int64_t units = vec ? T / 4 : T;       // accesses per row
+    const bool aligned = aligned16(out) && aligned16(in);
+    const bool vec = aligned && (T % 4 == 0);
+    const bool flat = aligned && !vec && T >= 8;
+    const int64_t units = vec ? T / 4 : (flat ? T / 4 + 1 : T);   // accesses per row
     int lpr_log2 = 0;
     while ((1 << lpr_log2) < units && lpr_log2 < 5) ++lpr_log2;
     const int threads = 256;
@@ -94,20 +152,18 @@ static int launch_shift(float *out, const float *in, const float *lut, float shi
     int64_t blocks = ceil_div(rows, groups_per_block);
     const int64_t cap = (int64_t)sm_count() * 8 * 4;   // a few waves of resident CTAs
     if (blocks > cap) blocks = cap;
+    const unsigned g = (unsigned)blocks;
+    const float *l = lut;
+    const int64_t nn = lut ? nNeurons : 1;
     if (vec) {
-        if (lut)
-            shift_vec4_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(
-                (float4 *)out, (const float4 *)in, lut, 0.f, Ts, rows, (int)(T / 4), nNeurons, lpr_log2);
-        else
-            shift_vec4_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>(
-                (float4 *)out, (const float4 *)in, nullptr, shift, Ts, rows, (int)(T / 4), 1, lpr_log2);
+        if (lut) shift_vec4_kernel<true><<<g, threads, 0, stream>>>((float4 *)out, (const float4 *)in, l, 0.f, Ts, rows, (int)(T / 4), nn, lpr_log2);
+        else shift_vec4_kernel<false><<<g, threads, 0, stream>>>((float4 *)out, (const float4 *)in, nullptr, shift, Ts, rows, (int)(T / 4), nn, lpr_log2);
+    } else if (flat) {
+        if (lut) shift_flat4_kernel<true><<<g, threads, 0, stream>>>(out, in, l, 0.f, Ts, rows, (int)T, nn, lpr_log2);
+        else shift_flat4_kernel<false><<<g, threads, 0, stream>>>(out, in, nullptr, shift, Ts, rows, (int)T, nn, lpr_log2);
     } else {
-        if (lut)
-            shift_scalar_kernel<true><<<(unsigned)blocks, threads, 0, stream>>>(
-                out, in, lut, 0.f, Ts, rows, (int)T, nNeurons, lpr_log2);
-        else
-            shift_scalar_kernel<false><<<(unsigned)blocks, threads, 0, stream>>>(
-                out, in, nullptr, shift, Ts, rows, (int)T, 1, lpr_log2);
+        if (lut) shift_scalar_kernel<true><<<g, threads, 0, stream>>>(out, in, l, 0.f, Ts, rows, (int)T, nn, lpr_log2);
+        else shift_scalar_kernel<false><<<g, threads, 0, stream>>>(out, in, nullptr, shift, Ts, rows, (int)T, nn, lpr_log2);
     }
     return check_launch("shift kernel launch");
 }
