@@ -108,6 +108,18 @@ int slayer_b200_spike_grad(float *out, const float *g, const float *u, int64_t n
                            float theta, float tau, float scale, void *stream);
 
 /*
+ * Gradient with respect to per-neuron axonal delays, fused into one pass:
+ *   grad_delay[n] = Ts * sum_{b,t} grad_output[b,n,t] * diff[b,n,t],
+ *   diff[b,n,t]   = (output[b,n,t-1] - output[b,n,t]) / Ts,   output[.., -1] = 0,
+ * with grad_output and output of shape [nBatch, nNeurons, T] and grad_delay of nNeurons
+ * floats (overwritten).  Replaces the composition in _delayFunction.backward,
+ * src/slayer.py:950-954: conv with [-1, 1]/Ts (convKernel, src/cuda/convKernels.h:10-35),
+ * an elementwise product and torch.sum over batch and time.
+ */
+int slayer_b200_delay_grad(float *grad_delay, const float *grad_output, const float *output,
+                           int64_t nBatch, int64_t nNeurons, int64_t T, float Ts, void *stream);
+
+/*
  * slayer_b200_srm_get_spikes without any memory allocation, for callers that cannot allocate
  * device memory: an application that has already given all device memory to its own pool, or
  * code that runs where entering the CUDA allocator is not allowed (another library's callback,

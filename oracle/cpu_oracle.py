@@ -46,6 +46,8 @@ def lib():
         L.oracle_loihi_get_spikes.argtypes = [f32p, f32p, f32p, f32p, i64, i64,
                                               u32, u32, u32, u32, u32]
         L.oracle_spike_grad.argtypes = [f32p, f32p, f32p, i64, fl, fl, fl]
+        L.oracle_delay_grad.argtypes = [f32p, f32p, f32p, i64, i64, i64, fl]
+        L.oracle_delay_grad.restype = None
         L.oracle_set_ftz.argtypes = [ctypes.c_int]
         L.oracle_set_threads.argtypes = [ctypes.c_int]
         L.oracle_max_threads.restype = ctypes.c_int
@@ -151,3 +153,14 @@ def spike_grad(g, u, theta, tau, scale):
     if g.size:
         lib().oracle_spike_grad(_p(out), _p(g), _p(u), g.size, float(theta), float(tau), float(scale))
     return out
+
+
+def delay_grad(g, out, Ts=1.0):
+    """gradDelay of shape g.shape[1:-1] (one value per neuron), as _delayFunction.backward."""
+    g, out = _f32(g), _f32(out)
+    n_batch, T = g.shape[0], g.shape[-1]
+    n_neurons = g.size // (n_batch * T) if n_batch * T else 0
+    res = np.zeros(n_neurons, np.float32)
+    if n_neurons:
+        lib().oracle_delay_grad(_p(res), _p(g), _p(out), n_batch, n_neurons, T, float(Ts))
+    return res.reshape(g.shape[1:-1])

@@ -34,6 +34,7 @@ CUDA_SOURCES = {
     "srm_spike.cu": ["-ftz=true"],
     "loihi_spike.cu": [],
     "spike_grad.cu": [],
+    "delay_grad.cu": [],
     "tma.cu": [],
 }
 HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", os.path.join(INCLUDE, "slayer_b200.h")]

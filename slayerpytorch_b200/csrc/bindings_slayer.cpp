@@ -7,7 +7,7 @@
 //   - a one-element shift tensor is read on the device (no host synchronisation);
 //   - the per-neuron shift covers the whole batch in one launch;
 //   - dtype is checked explicitly;
-//   - two additional operators are exported: spikeGrad and spikeGrad_ (in place).
+//   - additional operators are exported: spikeGrad, spikeGrad_ (in place) and delayGrad.
 #include "bindings_common.h"
 
 using namespace sb200py;
@@ -125,6 +125,28 @@ static torch::Tensor spikeGradInplaceCuda(torch::Tensor gradOut, torch::Tensor u
     return spikeGradImpl(gradOut, gradOut, u, theta, tau, scale);
 }
 
+// gradDelay of _delayFunction.backward (src/slayer.py:950-954) in one pass; the result has the
+// shape of gradOutput without its first (batch) and last (time) dimension.
+static torch::Tensor delayGradCuda(torch::Tensor gradOut, torch::Tensor output, float Ts)
+{
+    check_input(gradOut, "gradOutput");
+    check_input(output, "output");
+    check_device(gradOut, output, "gradOutput", "output");
+    TORCH_CHECK(gradOut.sizes() == output.sizes(), "gradOutput and output must have the same shape");
+    TORCH_CHECK(gradOut.dim() >= 2, "delayGrad expects [batch, ..., time] tensors");
+    c10::cuda::CUDAGuard guard(gradOut.device());
+    const int64_t nBatch = gradOut.size(0), T = gradOut.size(-1);
+    auto shape = gradOut.sizes().slice(1, gradOut.dim() - 2);
+    if (nBatch == 0 || T == 0) return torch::zeros(shape, gradOut.options());
+    const int64_t nNeurons = gradOut.numel() / (nBatch * T);
+    auto result = torch::empty(shape, gradOut.options());   // every element is written by the kernel
+    if (nNeurons > 0)
+        check_rc(slayer_b200_delay_grad(result.data_ptr<float>(), gradOut.data_ptr<float>(), output.data_ptr<float>(),
+                                        nBatch, nNeurons, T, Ts, current_stream()),
+                 "delayGrad");
+    return result;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
     m.def("getSpikes", &getSpikesCuda, "Get spikes (CUDA)");
@@ -137,5 +159,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("spikeGrad", &spikeGradCuda,
           "gradOutput * scale/tau * exp(-|u - theta| / tau) in one pass (CUDA)");
     m.def("spikeGrad_", &spikeGradInplaceCuda, "In-place variant of spikeGrad (overwrites gradOutput)");
+    m.def("delayGrad", &delayGradCuda, "Ts * sum over batch and time of gradOutput * d(output)/dt per neuron (CUDA)");
     m.attr("backend") = "slayer_b200";
 }

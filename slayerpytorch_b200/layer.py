@@ -11,6 +11,8 @@ differences that do not change results beyond fp32 rounding of ``exp``:
 
 * the surrogate-gradient backward is one fused kernel (``slayerCuda.spikeGrad``) instead of a
   chain of elementwise tensor operations;
+* the delay gradient is one fused reduction (``slayerCuda.delayGrad``) instead of a two-tap
+  conv, a product and a tensor sum;
 * scalars (``Ts``, ``theta`` ...) stay Python floats, so no backward pass synchronises the host
   to read a 0-dim device tensor.
 
@@ -118,10 +120,8 @@ class _DelayFunction(torch.autograd.Function):
         out, delay = ctx.saved_tensors
         Ts = ctx.Ts
         grad = grad.contiguous()
-        diff_filter = torch.tensor([-1.0, 1.0], dtype=grad.dtype, device=grad.device) / Ts
-        out_diff = slayerCuda.conv(out, diff_filter, 1)
-        grad_delay = torch.sum(grad * out_diff, [0, -1], keepdim=True).reshape(grad.shape[1:-1]) * Ts
-        return slayerCuda.shift(grad, -delay, Ts), grad_delay, None
+        grad_delay = slayerCuda.delayGrad(grad, out, Ts)      # one fused pass, no temporaries
+        return slayerCuda.shift(grad, -delay, Ts), grad_delay.reshape(delay.shape), None
 
 
 class _DelayShiftFunction(torch.autograd.Function):

@@ -74,3 +74,11 @@ def c_spike_grad(g, u, theta, tau, scale):
     capi.call("slayer_b200_spike_grad", ptr(out), ptr(g), ptr(u), g.numel(),
               float(theta), float(tau), float(scale), stream())
     return out
+
+
+def c_delay_grad(g, out, Ts):
+    nb, T = g.shape[0], g.shape[-1]
+    nn = g.numel() // (nb * T) if nb * T else 0
+    res = torch.full((max(nn, 1),), float("nan"), device=g.device, dtype=torch.float32)
+    capi.call("slayer_b200_delay_grad", ptr(res), ptr(g), ptr(out), nb, nn, T, float(Ts), stream())
+    return res[:nn]

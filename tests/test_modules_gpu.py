@@ -138,3 +138,20 @@ def test_mirror_delay_gradient_matches_hand_formula():
     dpsp = ops0.conv(psp_delayed.detach(), diff, 1)
     want = -torch.sum(upstream * dpsp, [0, -1], keepdim=True).reshape(25, 1, 1) * Ts
     assert torch.norm(want - delay.delay.grad).item() < 1e-4 * max(1.0, torch.norm(want).item())
+
+
+@pytest.mark.gpu
+def test_delay_grad_operator_shapes_and_errors():
+    ops0 = slayerpytorch_b200.load_ops()[0]
+    g = torch.randn(3, 4, 2, 1, 50, device="cuda")
+    o = torch.randn(3, 4, 2, 1, 50, device="cuda")
+    r = ops0.delayGrad(g, o, 1.0)
+    assert r.shape == (4, 2, 1)
+    diff = torch.tensor([-1.0, 1.0], device="cuda")
+    want = torch.sum(g * ops0.conv(o, diff, 1), [0, -1])
+    assert torch.allclose(r, want, rtol=1e-4, atol=1e-4)
+    assert ops0.delayGrad(g[:0], o[:0], 1.0).eq(0).all() and ops0.delayGrad(g[:0], o[:0], 1.0).shape == (4, 2, 1)
+    with pytest.raises(RuntimeError):
+        ops0.delayGrad(g, o[:2], 1.0)
+    with pytest.raises(RuntimeError):
+        ops0.delayGrad(g.cpu(), o.cpu(), 1.0)

@@ -231,6 +231,19 @@ def test_spike_grad_c_vs_numpy():
     np.testing.assert_allclose(co.spike_grad(g, u, 10, 10, 1), nl.spike_grad(g, u, 10, 10, 1), rtol=1e-6, atol=1e-12)
 
 
+def test_delay_grad_c_vs_composition():
+    """oracle delay_grad = Ts * sum(g * conv(out, [-1, 1]/Ts, 1)) (src/slayer.py:950-954)."""
+    rng = np.random.RandomState(8)
+    for Ts in (1.0, 0.5):
+        g = rng.randn(4, 3, 2, 1, 50).astype(np.float32)
+        out = rng.randn(4, 3, 2, 1, 50).astype(np.float32)
+        diff = co.conv(out, np.array([-1.0, 1.0], np.float32) / Ts, 1.0)
+        want = (g.astype(np.float64) * diff).sum(axis=(0, -1)) * Ts
+        got = co.delay_grad(g, out, Ts)
+        assert got.shape == (3, 2, 1)
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
 def test_srm_c_vs_numpy_random():
     rng = np.random.RandomState(11)
     for T, nus in ((1, 3), (7, 11), (64, 1), (300, 11), (97, 160)):

@@ -255,6 +255,40 @@ def test_spike_grad(n):
         np.testing.assert_allclose(got, ref.cpu().numpy(), rtol=REL, atol=1e-37)
 
 
+# ---------------------------------------------------------------------------- delay_grad
+@pytest.mark.parametrize("shape,Ts", [((1, 1, 1, 1, 1), 1.0), ((2, 3, 1, 1, 7), 1.0), ((9, 5, 2, 1, 300), 1.0),
+                                      ((4, 16, 3, 3, 301), 0.5), ((64, 10, 1, 1, 300), 1.0),
+                                      ((3, 2, 1, 1, 1450), 0.1), ((17, 4, 1, 1, 2000), 2.0)])
+def test_delay_grad(shape, Ts):
+    rng = np.random.RandomState(sum(shape))
+    g = rng.randn(*shape).astype(np.float32)
+    out = (rng.randn(*shape) * (rng.rand(*shape) < 0.4)).astype(np.float32)
+    got = G.host(G.c_delay_grad(G.dev(g), G.dev(out), Ts))
+    want = co.delay_grad(g, out, Ts).ravel()          # double-precision sum
+    scale = np.abs(want).max() + 1e-30
+    np.testing.assert_allclose(got, want, rtol=0, atol=2e-5 * scale * np.sqrt(shape[0] * shape[-1]) / 10)
+    # and against the composition it replaces (src/slayer.py:950-954) on the same device
+    gt, ot = G.dev(g), G.dev(out)
+    diff = torch.tensor([-1.0, 1.0], device="cuda") / Ts
+    ref = torch.sum(gt * G.c_conv(ot, diff, 1.0), [0, -1]).reshape(-1) * Ts
+    np.testing.assert_allclose(got, G.host(ref), rtol=0, atol=2e-5 * scale * np.sqrt(shape[0] * shape[-1]) / 10)
+    # determinism: a second call returns the same bits
+    again = G.host(G.c_delay_grad(gt, ot, Ts))
+    np.testing.assert_array_equal(got, again)
+
+
+def test_delay_grad_unaligned_and_empty():
+    rng = np.random.RandomState(5)
+    g = rng.randn(3 * 4 * 300 + 1).astype(np.float32)
+    o = rng.randn(3 * 4 * 300 + 1).astype(np.float32)
+    gd, od = G.dev(g)[1:].view(3, 4, 300), G.dev(o)[1:].view(3, 4, 300)
+    got = G.host(G.c_delay_grad(gd, od, 1.0))
+    want = co.delay_grad(g[1:].reshape(3, 4, 300), o[1:].reshape(3, 4, 300), 1.0).ravel()
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-4 * np.abs(want).max())
+    assert G.c_delay_grad(torch.empty(0, 4, 300, device="cuda"), torch.empty(0, 4, 300, device="cuda"), 1.0).eq(0).all()
+    assert G.c_delay_grad(torch.empty(2, 0, 300, device="cuda"), torch.empty(2, 0, 300, device="cuda"), 1.0).numel() == 0
+
+
 # ------------------------------------------- full-size runs checked on a random row sample
 def sample_rows(rows, n, seed):
     return np.sort(np.random.RandomState(seed).choice(rows, size=min(n, rows), replace=False))
