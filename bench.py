@@ -14,8 +14,11 @@ Metric: neuron-timesteps per second = batch * (512 + 10) * 300 per step / step t
 all GPUs (weak scaling: every rank processes its own batch of 64; no collective on this path).
 
 One JSON line is printed by rank 0.  ``value`` is measured with inputs resident in HBM, L2
-flushed between steps, CUDA events around each step; ``e2e`` is the same chain through the
-package's public layer API with host (pinned) buffers, copies inside the timed region;
+flushed between steps, CUDA events around each step, the step's ten launches replayed from a
+CUDA graph (``eager_ms_per_step`` is the same loop launched call by call); ``e2e`` is the same
+chain through the package's public layer API with host (pinned) buffers, copies inside the
+timed region, streamed in batch chunks by ``HostPipeline`` (``single_call_ms_per_step`` is one
+copy-in, one step, one copy-out);
 ``roofline`` describes the kernel with the largest share of the step; ``cpu_baseline`` is the C
 oracle on the host cores.  ``--impl reference`` times the explicit time-loop formulation (the C
 oracle, all host threads) on the same workload and, when the reference's own CUDA operators
@@ -226,6 +229,7 @@ def flush_l2(buf):
 def time_ours(args, rank, world, device):
     import slayerpytorch_b200
     from slayerpytorch_b200 import layer as L
+    from slayerpytorch_b200.hoststream import HostPipeline, chunk_bounds
     slayerCuda, _ = slayerpytorch_b200.load_ops()
     peak, peak_kind = measured_peak_gbs()
 
@@ -255,19 +259,46 @@ def time_ours(args, rank, world, device):
         flush_l2(flush)
         hot_path(slayerCuda, wl)
     barrier()
+
+    # The ten launches of a step are short (7-50 us), so the step is replayed from a CUDA graph
+    # captured once: the same kernels on the same buffers, without per-launch host overhead.
+    graph, graph_note = None, None
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                hot_path(slayerCuda, wl)
+            for _ in range(3):
+                flush_l2(flush)
+                graph.replay()
+        except Exception as e:             # reported, and the eager loop below is timed instead
+            graph, graph_note = None, "capture failed: %r" % (e,)
+        barrier()
+
+    def timed_steps(step):
+        events = []
+        for _ in range(args.steps):
+            flush_l2(flush)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            events.append((e0, e1))
+        barrier()
+        return sum(a.elapsed_time(b) for a, b in events)
+
     sampler = ClockSampler(device.index)
     sampler.start()
-    step_events, op_events = [], []
-    for _ in range(args.steps):
-        flush_l2(flush)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        hot_path(slayerCuda, wl, recorder(op_events))
-        e1.record()
-        step_events.append((e0, e1))
-    barrier()
+    eager_ms = timed_steps(lambda: hot_path(slayerCuda, wl))
+    total_ms = timed_steps(graph.replay) if graph is not None else eager_ms
     clocks = sampler.stop()
-    total_ms = sum(a.elapsed_time(b) for a, b in step_events)
+
+    # per-operator breakdown: a separate eager pass with an event pair around every launch
+    op_events = []
+    for _ in range(min(args.steps, 50)):
+        flush_l2(flush)
+        hot_path(slayerCuda, wl, recorder(op_events))
+    barrier()
     for name, big, a, b in op_events:
         per_op.setdefault((name, big), []).append(a.elapsed_time(b))
 
@@ -278,39 +309,45 @@ def time_ours(args, rank, world, device):
     h_out = {k: torch.empty_like(h_in[k]) .pin_memory() for k in ("a1", "a2", "g1", "g2")}
     delay_dev = wl["delay"]
 
-    def e2e_step():
-        a1 = h_in["a1"].to(device, non_blocking=True).requires_grad_(True)
-        a2 = h_in["a2"].to(device, non_blocking=True).requires_grad_(True)
-        g1 = h_in["g1"].to(device, non_blocking=True)
-        g2 = h_in["g2"].to(device, non_blocking=True)
+    def device_step(a1, a2, g1, g2):
+        a1 = a1.detach().requires_grad_(True)
+        a2 = a2.detach().requires_grad_(True)
         d1 = net.delayShift(net.spike(net.psp(a1)), delay_dev, SIM["Ts"])
         s2 = net.spike(net.psp(a2))
         torch.autograd.backward([d1, s2], [g1, g2])
-        h_out["a1"].copy_(d1.detach(), non_blocking=True)
-        h_out["a2"].copy_(s2.detach(), non_blocking=True)
-        h_out["g1"].copy_(a1.grad, non_blocking=True)
-        h_out["g2"].copy_(a2.grad, non_blocking=True)
+        return d1.detach(), s2.detach(), a1.grad, a2.grad
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e2e_events = []
-    for _ in range(args.steps):
-        flush_l2(flush)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        e2e_step()
-        e1.record()
-        e2e_events.append((e0, e1))
-    barrier()
-    e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_events)
+    order = ("a1", "a2", "g1", "g2")
+
+    def e2e_serial():
+        outs = device_step(*[h_in[k].to(device, non_blocking=True) for k in order])
+        for k, o in zip(order, outs):
+            h_out[k].copy_(o, non_blocking=True)
+
+    pipe = HostPipeline(device, chunks=args.e2e_chunks, capture=not args.no_graph)
+
+    def e2e_pipelined():
+        pipe.run(device_step, [h_in[k] for k in order], [h_out[k] for k in order])
+
+    def time_e2e(step):
+        for _ in range(3):
+            step()
+        barrier()
+        return timed_steps(step)
+
+    e2e_serial_ms = time_e2e(e2e_serial)
+    want = {k: h_out[k].clone() for k in order}
+    e2e_ms = time_e2e(e2e_pipelined)
+    for k in order:                        # chunking must not change a single bit
+        if not torch.equal(want[k].view(torch.int32), h_out[k].view(torch.int32)):
+            raise RuntimeError("pipelined end-to-end result differs from the single-call result in " + k)
     bytes_io = sum(t.numel() * 4 for t in h_in.values())
 
     # ---- max over ranks
-    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=device)
+    t = torch.tensor([total_ms, e2e_ms, eager_ms, e2e_serial_ms], dtype=torch.float64, device=device)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    total_ms, e2e_ms = float(t[0]), float(t[1])
+    total_ms, e2e_ms, eager_ms, e2e_serial_ms = (float(x) for x in t)
 
     if rank != 0:
         return None
@@ -360,7 +397,15 @@ def time_ours(args, rank, world, device):
         "clocks": clocks,
         "e2e": {"value": world * units * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io},
+                "h2d_bytes_per_step": bytes_io, "d2h_bytes_per_step": bytes_io,
+                "how": "HostPipeline: %d batch chunks, copies and kernels overlapped on three streams%s"
+                       % (len(chunk_bounds(BATCH, args.e2e_chunks)),
+                          "" if args.no_graph else ", each chunk's step one CUDA-graph launch"),
+                "single_call_ms_per_step": e2e_serial_ms / args.steps,
+                "pcie_GB/s_per_direction": round(bytes_io / (e2e_ms / args.steps * 1e-3) / 1e9, 1)},
+        "launch_mode": ("cuda graph replay of the step's %d launches" % LAUNCHES_PER_STEP) if graph is not None
+                       else ("eager" + (" (%s)" % graph_note if graph_note else "")),
+        "eager_ms_per_step": eager_ms / args.steps,
         "gpu_launches": LAUNCHES_PER_STEP * args.steps,
         "roofline": roofline,
         "cpu_baseline": cpu,
@@ -523,6 +568,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="time the eager launch loop instead of a CUDA-graph replay")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the end-to-end host pipeline")
     ap.add_argument("--no-scaled", action="store_true", help="skip the batch-scaled (>= 1 GiB tensors) variant")
     args = ap.parse_args()
 

@@ -1,0 +1,152 @@
+"""Streaming a host-resident batch through the device operators.
+
+The operators of this package work on device tensors.  A caller whose spike trains live in
+host memory pays two PCIe transfers around every step, and on a B200 those transfers, not the
+kernels, set the pace.  Rows of the ``[batch, ..., T]`` tensors are independent, so the batch
+can be cut into chunks and the three phases of consecutive chunks overlapped::
+
+    copy stream   : H2D(0) H2D(1) H2D(2) ...
+    compute stream:        step(0) step(1) step(2) ...
+    return stream :               D2H(0)  D2H(1)  D2H(2) ...
+
+``HostPipeline`` does exactly that with three CUDA streams, two sets of device staging buffers
+and events between the phases; there is no host-side synchronisation inside ``run``.  Results
+are the same as those of one call on the whole batch, because every operator treats rows
+independently (per-neuron tables are indexed inside a sample, and chunks hold whole samples).
+
+A chunk's step is a handful of short kernels, so issuing them call by call can cost the host
+more time than the copies take.  With ``capture=True`` the step is captured once per staging
+slot into a CUDA graph (forward and backward alike) and every full-size chunk is one graph
+launch; this requires a step without side effects other than its return values, because it is
+run once on zero-filled buffers before capture.
+"""
+import torch
+
+
+def chunk_bounds(batch, chunks):
+    """``chunks`` nearly equal [start, stop) ranges covering ``range(batch)``; fewer when the
+    batch is smaller than the number of chunks.  Sizes differ by at most one sample."""
+    if batch < 0 or chunks < 1:
+        raise ValueError("batch must be >= 0 and chunks >= 1")
+    chunks = max(1, min(chunks, batch))
+    base, extra = divmod(batch, chunks)
+    bounds, start = [], 0
+    for i in range(chunks):
+        stop = start + base + (1 if i < extra else 0)
+        bounds.append((start, stop))
+        start = stop
+    return bounds
+
+
+class HostPipeline:
+    """Overlaps host-to-device copies, a device step and device-to-host copies over chunks of
+    the batch axis (axis 0).
+
+    ``step`` is any callable taking the device chunks of the inputs (same order as
+    ``host_inputs``) and returning a tensor or a tuple of tensors whose axis 0 is the chunk's
+    batch; output k of every chunk is written to ``host_outputs[k][start:stop]``.  Host tensors
+    should be pinned: copies from pageable memory are staged by the driver and do not overlap.
+    """
+
+    def __init__(self, device, chunks=8, capture=False):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("HostPipeline needs a CUDA device: the operators have no CPU path")
+        self.chunks = int(chunks)
+        self.copy_stream = torch.cuda.Stream(self.device)
+        self.compute_stream = torch.cuda.Stream(self.device)
+        self.return_stream = torch.cuda.Stream(self.device)
+        self.capture = bool(capture)
+        self._slots = None
+        self._slot_key = None
+        self._graphs = None            # per slot: (graph, static outputs), for the step in _graph_step
+        self._graph_step = None
+
+    def _staging(self, host_inputs, rows):
+        key = tuple((tuple(t.shape[1:]), t.dtype) for t in host_inputs) + (rows,)
+        if self._slot_key != key:
+            self._slots = [[torch.empty((rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=self.device)
+                            for t in host_inputs] for _ in range(2)]
+            self._slot_key = key
+            self._graphs = None
+        return self._slots
+
+    def _captured(self, step, slots):
+        """One CUDA graph of ``step`` per staging slot, built on first use."""
+        if self._graphs is not None and self._graph_step is step:
+            return self._graphs
+        graphs = []
+        for bufs in slots:
+            with torch.cuda.stream(self.compute_stream):
+                for b in bufs:
+                    b.zero_()
+                step(*bufs)                                   # set-up calls happen outside the capture
+            self.compute_stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.compute_stream):
+                outs = step(*bufs)
+            graphs.append((g, (outs,) if torch.is_tensor(outs) else tuple(outs)))
+        self._graphs, self._graph_step = graphs, step
+        return graphs
+
+    def run(self, step, host_inputs, host_outputs):
+        host_inputs, host_outputs = list(host_inputs), list(host_outputs)
+        batch = host_inputs[0].shape[0]
+        for t in host_inputs + host_outputs:
+            if t.shape[0] != batch:
+                raise ValueError("every host tensor must have the same batch size on axis 0")
+        bounds = chunk_bounds(batch, self.chunks)
+        if batch == 0:
+            return
+        rows = max(b - a for a, b in bounds)
+        caller = torch.cuda.current_stream(self.device)
+        slots = self._staging(host_inputs, rows)
+        graphs = self._captured(step, slots) if self.capture else None
+        returned = [None, None]            # recorded on the return stream when a slot's outputs are copied
+        start = torch.cuda.Event()
+        start.record(caller)
+        for s in (self.copy_stream, self.compute_stream, self.return_stream):
+            s.wait_event(start)
+        slot_free = [None, None]           # recorded on the compute stream when a slot's step is enqueued
+        for i, (a, b) in enumerate(bounds):
+            k = i & 1
+            with torch.cuda.stream(self.copy_stream):
+                if slot_free[k] is not None:
+                    self.copy_stream.wait_event(slot_free[k])
+                dev_in = [buf[:b - a] for buf in slots[k]]
+                for buf, h in zip(dev_in, host_inputs):
+                    buf.copy_(h[a:b], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(self.copy_stream)
+            with torch.cuda.stream(self.compute_stream):
+                self.compute_stream.wait_event(ready)
+                replay = graphs is not None and b - a == rows
+                if replay:
+                    if returned[k] is not None:              # the graph writes the same output buffers again
+                        self.compute_stream.wait_event(returned[k])
+                    graphs[k][0].replay()
+                    outs = graphs[k][1]
+                else:
+                    outs = step(*dev_in)
+                    if torch.is_tensor(outs):
+                        outs = (outs,)
+                if len(outs) != len(host_outputs):
+                    raise ValueError("step returned %d tensors for %d host outputs" % (len(outs), len(host_outputs)))
+                done = torch.cuda.Event()
+                done.record(self.compute_stream)
+                slot_free[k] = done
+            with torch.cuda.stream(self.return_stream):
+                self.return_stream.wait_event(done)
+                for o, h in zip(outs, host_outputs):
+                    if not replay:
+                        o.record_stream(self.return_stream)  # keeps the allocator from reusing it early
+                    h[a:b].copy_(o[:b - a], non_blocking=True)
+                if replay:
+                    returned[k] = torch.cuda.Event()
+                    returned[k].record(self.return_stream)
+        finished = torch.cuda.Event()
+        finished.record(self.return_stream)
+        caller.wait_event(finished)
+        tail = torch.cuda.Event()
+        tail.record(self.compute_stream)
+        caller.wait_event(tail)

@@ -51,3 +51,21 @@ def test_mirror_loihi_layer_kernels_match_reference_python(golden_dir):
         np.testing.assert_array_equal(net.srmKernel.numpy(), g[tag + "_srmKernel"])
         np.testing.assert_array_equal(net.refKernel.numpy(), g[tag + "_refKernel"])
         assert net.neuron["theta"] == int(g[tag + "_theta"])
+
+
+def test_host_pipeline_chunk_bounds():
+    from slayerpytorch_b200.hoststream import chunk_bounds
+    assert chunk_bounds(64, 8) == [(8 * i, 8 * i + 8) for i in range(8)]
+    assert chunk_bounds(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert chunk_bounds(3, 8) == [(0, 1), (1, 2), (2, 3)]
+    assert chunk_bounds(0, 4) == [(0, 0)]
+    assert chunk_bounds(5, 1) == [(0, 5)]
+    for batch in range(1, 40):
+        for chunks in range(1, 12):
+            b = chunk_bounds(batch, chunks)
+            assert b[0][0] == 0 and b[-1][1] == batch
+            assert all(x[1] == y[0] for x, y in zip(b, b[1:]))
+            sizes = [y - x for x, y in b]
+            assert min(sizes) >= 1 and max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        chunk_bounds(4, 0)

@@ -155,3 +155,84 @@ def test_delay_grad_operator_shapes_and_errors():
         ops0.delayGrad(g, o[:2], 1.0)
     with pytest.raises(RuntimeError):
         ops0.delayGrad(g.cpu(), o.cpu(), 1.0)
+
+
+def _chain_layer():
+    from slayerpytorch_b200 import layer as L
+    neuron = {"type": "SRMALPHA", "theta": 10, "tauSr": 10.0, "tauRef": 1.0, "scaleRef": 2, "tauRho": 1, "scaleRho": 1}
+    return L.spikeLayer(neuron, {"Ts": 1.0, "tSample": 300}).cuda()
+
+
+@pytest.mark.parametrize("capture", [False, True])
+@pytest.mark.parametrize("batch,chunks", [(16, 4), (7, 3), (3, 8), (5, 1)])
+def test_host_pipeline_matches_single_call(batch, chunks, capture):
+    """Chunked, overlapped streaming of a host batch gives the bits of one call on the whole batch."""
+    from slayerpytorch_b200.hoststream import HostPipeline
+    net = _chain_layer()
+    g = torch.Generator().manual_seed(batch * 10 + chunks)
+    x = ((torch.rand(batch, 40, 1, 1, 300, generator=g) < 0.3).float() * 3).pin_memory()
+    up = torch.randn(batch, 40, 1, 1, 300, generator=g).pin_memory()
+    delay = (torch.rand(40, generator=g) * 5).cuda()
+
+    def step(xd, gd):
+        xd = xd.detach().requires_grad_(True)
+        y = net.delayShift(net.spike(net.psp(xd)), delay, 1.0)
+        y.backward(gd)
+        return y.detach(), xd.grad
+
+    y_ref, gx_ref = step(x.cuda(), up.cuda())
+    assert 0.005 < y_ref.mean().item() < 0.5
+    y_h, gx_h = torch.empty_like(x).pin_memory(), torch.empty_like(x).pin_memory()
+    pipe = HostPipeline("cuda", chunks=chunks, capture=capture)
+    for _ in range(3):                     # later runs reuse the staging buffers (and graphs)
+        y_h.fill_(-1)
+        gx_h.fill_(-1)
+        pipe.run(step, [x, up], [y_h, gx_h])
+        torch.cuda.synchronize()
+        assert torch.equal(y_h, y_ref.cpu())
+        assert torch.equal(gx_h.view(torch.int32), gx_ref.cpu().view(torch.int32))
+
+
+def test_host_pipeline_rejects_mismatched_batches():
+    from slayerpytorch_b200.hoststream import HostPipeline
+    pipe = HostPipeline("cuda", chunks=2)
+    with pytest.raises(ValueError):
+        pipe.run(lambda a, b: a, [torch.zeros(4, 3), torch.zeros(5, 3)], [torch.zeros(4, 3)])
+    with pytest.raises(ValueError):
+        pipe.run(lambda a: (a, a), [torch.zeros(4, 3).pin_memory()], [torch.zeros(4, 3).pin_memory()])
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError):
+        HostPipeline("cpu")
+
+
+def test_operator_chain_replays_from_a_cuda_graph():
+    """After one eager call per operator (set-up of per-device state), the chain captures into a
+    CUDA graph and every replay reproduces the eager results."""
+    ops0 = slayerpytorch_b200.load_ops()[0]
+    from slayerpytorch_b200.layer import alpha_kernel
+    g = torch.Generator(device="cuda").manual_seed(3)
+    srm = torch.tensor(alpha_kernel(10.0, 1.0, 300), device="cuda", dtype=torch.float32)
+    ref = torch.tensor(alpha_kernel(1.0, 1.0, 300, mult=-20.0), device="cuda", dtype=torch.float32)
+    x = (torch.rand(8, 64, 1, 1, 300, device="cuda", generator=g) < 0.3).float() * 3
+    up = torch.randn(8, 64, 1, 1, 300, device="cuda", generator=g)
+    delay = torch.rand(64, device="cuda", generator=g) * 5
+
+    def chain():
+        u = ops0.conv(x, srm, 1.0)
+        s = ops0.getSpikes(u, ref, 10.0, 1.0)
+        d = ops0.shift(s, delay, 1.0)
+        b = ops0.corr(ops0.spikeGrad(ops0.shift(up, -delay, 1.0), u, 10.0, 10.0, 1.0), srm, 1.0)
+        return d, b, ops0.delayGrad(up, d, 1.0)
+
+    want = [t.clone() for t in chain()]
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = chain()
+    for _ in range(3):
+        for t in outs:
+            t.fill_(7.0)
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(outs, want):
+            assert torch.equal(a.view(torch.int32), b.view(torch.int32))
