@@ -276,8 +276,8 @@ static inline int pad_stride(int w)       // smallest s >= w with s = 4 (mod 8)
 
 constexpr int kFirTileWordsPerRow = 432;  // 2 buffers x 32 rows x 432 words = 108 KB: two CTAs per SM
 
-// Tile shape for a row length T and K taps; returns false if the filter is too long to tile.
-static bool fir_shape(int64_t T, int64_t K, FirShape &sh)
+// Tile shape for rows of length T and K taps; returns false if the filter is too long to tile.
+static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
 {
     sh.halo = (int)(((K + 3) & ~3LL) + 8);     // taps rounded up plus two quads of look-ahead
     const int room = kFirTileWordsPerRow - 4 - sh.halo;       // words left for outputs (4 = stride padding)
@@ -285,10 +285,23 @@ static bool fir_shape(int64_t T, int64_t K, FirShape &sh)
     if (nseg_max < 1) return false;
     const int64_t segs = ceil_div(T, kFirSeg);
     sh.ttiles = (int)ceil_div(segs, nseg_max);
+    // few rows: cut time finer so that every SM gets a tile (the halo is re-read from L2)
+    const int64_t row_blocks = ceil_div(rows, kFirRows);
+    const int64_t want = 2 * (int64_t)sm_count();
+    if (row_blocks * sh.ttiles < want) {
+        int64_t tt = ceil_div(want, row_blocks);
+        if (tt > segs) tt = segs;
+        if (tt > sh.ttiles) sh.ttiles = (int)tt;
+    }
     sh.nseg = (int)ceil_div(segs, sh.ttiles);
+    sh.ttiles = (int)ceil_div(segs, sh.nseg);
     sh.SX = pad_stride(sh.nseg * kFirSeg + sh.halo);
     // Warps per CTA.  Warp w runs on scheduler w % 4 and takes segments w, w+nw, ...; pick the
     // multiple of four whose busiest scheduler has the least work, preferring 8 warps.
+    if (sh.nseg <= 8) {             // one segment per warp
+        sh.nwarps = sh.nseg;
+        return true;
+    }
     int best_load = 1 << 30;
     sh.nwarps = 8;
     const int candidates[4] = {8, 12, 16, 4};
@@ -314,7 +327,7 @@ static int launch_fir(float *out, const float *in, const float *filt,
     }
     const int64_t Keff = K < T ? K : T;              // taps beyond the row length never contribute
     FirShape sh;
-    const bool tiled = fir_shape(T, Keff, sh);
+    const bool tiled = fir_shape(rows, T, Keff, sh);
     const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
     if (!tiled) {
         const int64_t n = rows * T;
@@ -329,7 +342,10 @@ static int launch_fir(float *out, const float *in, const float *filt,
     auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
-    int64_t grid = 2 * (int64_t)sm_count();
+    int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    int64_t grid = ctas_per_sm * (int64_t)sm_count();
     if (grid > ntiles) grid = ntiles;
     kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles);
     return check_launch("fir kernel launch");

@@ -13,21 +13,25 @@
 //
 // Three variants of the inner step, all producing the same bits:
 //   - "ring" (refractory window shorter than the time tile and every tap negative or -0.0,
-//     which is what refractory kernels look like): the last R spike samples are kept as 0.0 / 1.0
-//     floats in a register ring indexed at compile time (the time tile is fully unrolled), and
-//     the taps are applied as v = fma(flag, tap, v), oldest first.  fma(1, tap, v) is the add
-//     the definition asks for; fma(+0, tap, v) adds -0.0 and returns v unchanged, bit for bit.
-//     No predicates, no branches: the step runs on the FMA pipe, which has twice the issue
-//     rate of the integer pipe the bit tests of the next variant need;
+//     which is what refractory kernels look like): spikes are kept as 0.0 / 1.0 flags in a
+//     register ring indexed at compile time (the time tile is fully unrolled), the potentials
+//     of the tile sit in registers, and once the flag of a step is known its taps go to the
+//     following samples as v = fma(flag, tap, v).  fma(1, tap, v) is the add the definition
+//     asks for; fma(+0, tap, v) adds -0.0 and returns v unchanged, bit for bit.  A sample still
+//     receives its taps oldest spike first, but the adds that follow one flag are independent,
+//     so the dependency from step to step is one multiply-add, one compare and one select.
+//     No predicates, no branches: the step runs on the FMA pipe;
 //   - "bits" (window of up to 32 steps, any taps): history bits in a register, a fully
 //     unrolled run of predicated adds, oldest first;
 //   - "loop" (windows up to 256 steps): a loop over the set history bits, taps in shared memory.
 //
 // Memory: 12 algorithmic bytes per element (read u, write u, write s), bound by HBM.  A warp
 // owns 32 rows and walks them in time tiles staged in swizzled shared memory, so that global
-// memory only ever sees contiguous row segments.  Two data-movement paths feed the same
-// recurrence: bulk tensor copies (TMA) when rows are 32-byte aligned (T % 8 == 0), cp.async
-// with row-skewed tiles otherwise.
+// memory only ever sees contiguous row segments; tiles are 64 steps wide (256 bytes per row)
+// wherever the buffers are 16-byte aligned, because DRAM serves longer row segments faster.
+// Three data-movement paths feed the same recurrence: bulk tensor copies (TMA) for the loads
+// when rows start on 16-byte boundaries (T % 4 == 0), cp.async with row-skewed wide tiles for
+// any other row length, and cp.async with 32-step tiles for unaligned buffers.
 #include <mutex>
 
 #include "common.cuh"
@@ -78,8 +82,8 @@ struct SrmRow {
         for (int w = 0; w < W; ++w) hist[w] = 0u;
     }
 
-    // v: original potential in, updated potential out; returns the spike sample
-    __device__ __forceinline__ float step(float &v)
+    // v: original potential in, updated potential out; returns whether the row spiked
+    __device__ __forceinline__ bool step(float &v)
     {
         // refractory taps of recent spikes, oldest spike first
         if (NB > 0) {
@@ -102,7 +106,7 @@ struct SrmRow {
 #pragma unroll
         for (int w = W - 1; w > 0; --w) hist[w] = ((hist[w] << 1) | (hist[w - 1] >> 31)) & wmask[w];
         hist[0] = ((hist[0] << 1) | (spk ? 1u : 0u)) & wmask[0];
-        return spk ? spikeVal : 0.0f;
+        return spk;
     }
 };
 
@@ -121,37 +125,76 @@ __device__ __forceinline__ int chunk_of(int r, int c)
 }
 
 // Walk one time tile of R steps for this lane's row: potentials are updated in place in
-// `tile`, spike samples go to `tile_s`.  RING selects the ring variant (needs NB < R).
-template <int R, bool RING, int NB, int W>
-__device__ __forceinline__ void walk_tile(float *tile, float *tile_s, SrmRow<NB, W> &st, float (&ring)[R], int lane)
+// `tile`; the spikes are returned as a bit mask (bit i = spiked at step i) and, with FLOATS,
+// also written as samples to `tile_s`.  RING selects the ring variant (needs NB < R).
+//
+// Ring variant.  ring[i] holds the 0/1 flag "spiked at step i" of the tile being walked (and,
+// until step i overwrites it, of the previous tile).  The R potentials of the tile sit in
+// registers; as soon as the flag of step i is known its refractory taps are added to the next
+// NB potentials.  A potential thus receives its terms in the order the spikes occurred (oldest
+// first, the order of a sequential walk), but the NB additions that follow one flag are
+// independent of each other, so the loop-carried dependency per step is a single multiply-add,
+// a compare and a select instead of a chain of NB multiply-adds.  Spikes of the previous tile
+// reach the first NB steps through a triangular block of additions at the start of the tile.
+template <int R, bool RING, int NB, int W, bool FLOATS = true>
+__device__ __forceinline__ unsigned walk_tile(float *tile, float *tile_s, SrmRow<NB, W> &st, float (&ring)[R], int lane)
 {
-    float4 cur = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, 0));
+    unsigned mask = 0u;
+    if constexpr (RING) {
+        float a[R];
 #pragma unroll
-    for (int c4 = 0; c4 < R / 4; ++c4) {
-        float4 nxt = cur;       // the next chunk is fetched before the current one is processed
-        if (c4 + 1 < R / 4) nxt = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, c4 + 1));
-        float vv[4] = {cur.x, cur.y, cur.z, cur.w};
-        float sv[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (RING) {
-                const int i = c4 * 4 + j;
-                float v = vv[j];
-#pragma unroll
-                for (int k = NB; k >= 1; --k) fma_keep(v, ring[(i - k) & (R - 1)], st.nu_r[k - 1]);
-                const bool spk = v >= st.theta;
-                ring[i] = spk ? 1.0f : 0.0f;
-                if (spk && st.has_nu0) v += st.nu0;
-                vv[j] = v;
-                sv[j] = spk ? st.spikeVal : 0.0f;
-            } else {
-                sv[j] = st.step(vv[j]);
-            }
+        for (int c4 = 0; c4 < R / 4; ++c4) {
+            const float4 x = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, c4));
+            a[4 * c4] = x.x; a[4 * c4 + 1] = x.y; a[4 * c4 + 2] = x.z; a[4 * c4 + 3] = x.w;
         }
-        *reinterpret_cast<float4 *>(tile + chunk_of<R>(lane, c4)) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-        *reinterpret_cast<float4 *>(tile_s + chunk_of<R>(lane, c4)) = make_float4(sv[0], sv[1], sv[2], sv[3]);
-        cur = nxt;
+        // spikes of the previous tile: step t < NB still lacks the taps k = NB .. t+1
+#pragma unroll
+        for (int t = 0; t < NB; ++t) {
+#pragma unroll
+            for (int k = NB; k > t; --k) fma_keep(a[t], ring[(t - k) & (R - 1)], st.nu_r[k - 1]);
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < R / 4; ++c4) {
+            float sv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = c4 * 4 + j;
+                const bool spk = a[i] >= st.theta;
+                const float f = spk ? 1.0f : 0.0f;
+                ring[i] = f;
+#pragma unroll
+                for (int d = 1; d <= NB; ++d)
+                    if (i + d < R) fma_keep(a[i + d], f, st.nu_r[d - 1]);
+                if (spk && st.has_nu0) a[i] += st.nu0;
+                if (FLOATS) sv[j] = spk ? st.spikeVal : 0.0f;
+                else if (spk) mask |= 1u << i;
+            }
+            *reinterpret_cast<float4 *>(tile + chunk_of<R>(lane, c4)) =
+                make_float4(a[4 * c4], a[4 * c4 + 1], a[4 * c4 + 2], a[4 * c4 + 3]);
+            if (FLOATS)
+                *reinterpret_cast<float4 *>(tile_s + chunk_of<R>(lane, c4)) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+        }
+    } else {
+        float4 cur = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, 0));
+#pragma unroll
+        for (int c4 = 0; c4 < R / 4; ++c4) {
+            float4 nxt = cur;       // the next chunk is fetched before the current one is processed
+            if (c4 + 1 < R / 4) nxt = *reinterpret_cast<const float4 *>(tile + chunk_of<R>(lane, c4 + 1));
+            float vv[4] = {cur.x, cur.y, cur.z, cur.w};
+            float sv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool spk = st.step(vv[j]);
+                if (FLOATS) sv[j] = spk ? st.spikeVal : 0.0f;
+                else if (spk) mask |= 1u << (c4 * 4 + j);
+            }
+            *reinterpret_cast<float4 *>(tile + chunk_of<R>(lane, c4)) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+            if (FLOATS)
+                *reinterpret_cast<float4 *>(tile_s + chunk_of<R>(lane, c4)) = make_float4(sv[0], sv[1], sv[2], sv[3]);
+            cur = nxt;
+        }
     }
+    return mask;
 }
 
 template <int R>
@@ -167,7 +210,7 @@ __device__ __forceinline__ void ring_reset(float (&ring)[R])
 template <int V, int NB, int W>
 __global__ void __launch_bounds__(256)
 srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
-                      int64_t rows, int nuEff, int T, float theta, float spikeVal)
+                      int64_t rows, int nuEff, int T, float theta, float spikeVal, int depth)
 {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31;
@@ -175,8 +218,9 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     const int warps_per_block = blockDim.x >> 5;
     const int nuPad = NB > 0 ? 0 : ((nuEff + 3) & ~3);
     float *nu_s = smem;
-    float *tiles = smem + nuPad + warp * (3 * kTileWords);   // two potential tiles (prefetch ring)
-    float *tile_s = tiles + 2 * kTileWords;                  // spike tile
+    // per warp: `depth` potential tiles (prefetch ring, depth = 2 or 4) and one spike tile
+    float *tiles = smem + nuPad + warp * ((depth + 1) * kTileWords);
+    float *tile_s = tiles + depth * kTileWords;
 
     if (NB == 0) {
         for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
@@ -189,8 +233,10 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     float ring[kTile];
 
     // The warp's work is one stream of tiles: all time tiles of its first block of 32 rows, then
-    // of its next block, ...  The tile after the current one - possibly the first tile of the
-    // next row block - is always in flight, so a change of row block costs no memory latency.
+    // of its next block, ...  The depth-1 tiles after the current one - possibly the first tiles
+    // of the next row block - are always in flight, so a change of row block costs no memory
+    // latency.  Large launches hide latency with many resident warps and use depth 2; launches
+    // with only a few warps per SM use depth 4 (more shared memory per warp, fewer stalls).
     // V == 4 uses row-skewed tiles (tile.cuh): 16-byte accesses on 32-byte boundaries for any T.
     // Samples before a row's start are padded with -inf, which can neither spike nor be changed
     // by a refractory tap, so the skewed lanes idle through them with their state untouched.
@@ -204,7 +250,8 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     int it_next = 0;
     int skew = V == 4 ? block_skew(rb * kTile, T, phase) : 0;        // of the block being walked
     int skew_next = skew;                                             // of the block being prefetched
-    unsigned q = 0;                 // tiles walked so far: buffer = q & 1
+    unsigned q = 0;                 // tiles walked so far: buffer = q & (depth - 1)
+    const unsigned dmask = (unsigned)depth - 1u;
 
     auto prefetch = [&](float *dst) {
         if (V == 4) tile_prefetch_skew(dst, u, rb_next * kTile, rows, it_next, T, lane, skew_next, -INFINITY);
@@ -215,19 +262,22 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
             if (V == 4 && rb_next < nblocks) skew_next = block_skew(rb_next * kTile, T, phase);
         }
     };
-    prefetch(tiles);
-    cp_async_commit();
+    for (int d = 0; d + 1 < depth; ++d) {
+        if (rb_next < nblocks) prefetch(tiles + d * kTileWords);
+        cp_async_commit();
+    }
 
     for (int it = 0; rb < nblocks; ++q) {
         const int64_t row0 = rb * kTile;
-        float *tile = tiles + (q & 1) * kTileWords;
+        float *tile = tiles + (q & dmask) * kTileWords;
         if (it == 0) {
             st.reset();
             ring_reset(ring);
         }
-        if (rb_next < nblocks) prefetch(tiles + ((q + 1) & 1) * kTileWords);
+        if (rb_next < nblocks) prefetch(tiles + ((q + dmask) & dmask) * kTileWords);
         cp_async_commit();
-        cp_async_wait<1>();
+        if (depth == 2) cp_async_wait<1>();
+        else cp_async_wait<3>();
         __syncwarp();
 
         if (use_ring) walk_tile<kTile, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
@@ -251,21 +301,174 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
 }
 
 // ---------------------------------------------------------------------------------------
-// Bulk-tensor-copy path (T % 4 == 0, 16-byte aligned bases).  All global traffic is issued by
-// one lane per warp as [32 rows x 16 steps] box copies, so the other lanes spend their issue
-// slots on the recurrence only.  Per warp: a ring of four potential tiles (one being walked,
-// one whose store is in flight, two being loaded) and two spike tiles; tiles use the 64-byte
-// swizzle so that a lane reading its own row's 16-byte chunks is bank-conflict free.
+// Wide-tile path (16-byte aligned bases, any T): row-skewed tiles of 64 steps, so that every
+// global request covers 256 contiguous bytes of a row, which is what DRAM needs to run near
+// its peak.  Per warp: `depth` potential tiles (8 KB each) and the spike bits of the tile being
+// walked (256 bytes); spikes are expanded to samples on their way out.  Samples before a row's
+// start are padded with -inf, which can neither spike nor be changed by a refractory tap, so
+// the skewed lanes idle through them with their state untouched.
+// ---------------------------------------------------------------------------------------
+template <int NB, int W, bool SKEW>
+__global__ void __launch_bounds__(256)
+srm_get_spikes_wide_kernel(float *s, float *u, const float *__restrict__ nu,
+                           int64_t rows, int nuEff, int T, float theta, float spikeVal, int depth)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int warps_per_block = blockDim.x >> 5;
+    const int nuPad = NB > 0 ? 0 : ((nuEff + 3) & ~3);
+    float *nu_s = smem;
+    float *tiles = smem + nuPad + warp * (depth * kWideWords + 2 * kTile);
+    unsigned *masks = reinterpret_cast<unsigned *>(tiles + depth * kWideWords);
+
+    if (NB == 0) {
+        for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
+        __syncthreads();
+    }
+    SrmRow<NB, W> st;
+    st.init(nu, nu_s, nuEff, theta, spikeVal);
+    constexpr bool kRingOk = NB > 0 && NB < kTile;
+    const bool use_ring = kRingOk && st.taps_negative;      // uniform over the grid
+    float ring[kTile];
+
+    const int ntiles = SKEW ? skew_wide_tiles(T) : (T + kWide - 1) / kWide;
+    const unsigned phase = (unsigned)(reinterpret_cast<uintptr_t>(u) >> 2) & 7u;
+    const int64_t nblocks = (rows + kTile - 1) / kTile;
+    const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
+    int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
+    if (rb >= nblocks) return;
+    int64_t rb_next = rb;           // (row block, tile) of the tile to prefetch next
+    int it_next = 0;
+    int skew = block_skew(rb * kTile, T, phase);          // of the block being walked
+    int skew_next = skew;                                  // of the block being prefetched
+    unsigned q = 0;                 // tiles walked so far: buffer = q & (depth - 1)
+    const unsigned dmask = (unsigned)depth - 1u;
+
+    auto prefetch = [&](float *dst) {
+        wide_prefetch_skew<SKEW>(dst, u, rb_next * kTile, rows, it_next, T, lane, skew_next, -INFINITY);
+        if (++it_next == ntiles) {
+            it_next = 0;
+            rb_next += wstride;
+            if (rb_next < nblocks) skew_next = block_skew(rb_next * kTile, T, phase);
+        }
+    };
+    for (int d = 0; d + 1 < depth; ++d) {
+        if (rb_next < nblocks) prefetch(tiles + d * kWideWords);
+        cp_async_commit();
+    }
+
+    for (int it = 0; rb < nblocks; ++q) {
+        const int64_t row0 = rb * kTile;
+        float *tile = tiles + (q & dmask) * kWideWords;
+        if (it == 0) {
+            st.reset();
+            ring_reset(ring);
+        }
+        if (rb_next < nblocks) prefetch(tiles + ((q + dmask) & dmask) * kWideWords);
+        cp_async_commit();
+        if (depth == 2) cp_async_wait<1>();
+        else cp_async_wait<3>();
+        __syncwarp();
+
+        // the second half lies wholly past the end of every row when even the most skewed row
+        // (7 steps behind) has run out of samples there
+        const bool second = kWide * it + kTile - (SKEW ? 7 : 0) < T;
+        unsigned m0 = 0u, m1 = 0u;
+#pragma unroll 1
+        for (int h = 0; h < (second ? 2 : 1); ++h) {
+            const unsigned mh = use_ring
+                ? walk_tile<kTile, kRingOk, NB, W, false>(tile + h * kTileWords, nullptr, st, ring, lane)
+                : walk_tile<kTile, false, NB, W, false>(tile + h * kTileWords, nullptr, st, ring, lane);
+            if (h == 0) m0 = mh;
+            else m1 = mh;
+        }
+        masks[lane] = m0;
+        masks[kTile + lane] = m1;
+        __syncwarp();
+
+        wide_store_skew<SKEW>(tile, u, row0, rows, it, T, lane, skew);
+        wide_store_spikes_skew<SKEW>(masks, s, row0, rows, it, T, lane, skew, spikeVal);
+        __syncwarp();
+        if (++it == ntiles) {
+            it = 0;
+            rb += wstride;
+            if (rb < nblocks) skew = block_skew(rb * kTile, T, phase);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Bulk-tensor-copy path (T % 4 == 0, 16-byte aligned bases).  The potentials arrive as
+// [32 rows x 32 steps] boxes requested by one lane per warp, so loading costs the warp no
+// issue slots.  A stage is a wide tile: two boxes that are adjacent in time.  Boxes use the
+// 128-byte swizzle, which is the layout of the 32-step tile (tile.cuh): a lane reading its own
+// row's 16-byte chunks is bank-conflict free.  Results leave as ordinary 16-byte stores that
+// cover 256 contiguous bytes of a row per 16 lanes (the updated potentials from the tile, the
+// spikes expanded from bit masks): DRAM runs measurably closer to its peak on 256-byte row
+// segments than on the 128-byte segments of a box, and writes are two thirds of the traffic.
+// Per warp: `ustages` stages (one being walked, the others being loaded) and the spike bits
+// of the tile being walked.
 // Every wait on a load barrier is bounded: if it runs out the warp records a status code and
 // stops, so a lost copy cannot hang the GPU.
 // ---------------------------------------------------------------------------------------
-constexpr int kBoxT = 16;                       // time steps per box
-constexpr int kBoxWords = kTile * kBoxT;        // 512 words = 2 KB
-constexpr int kBoxBytes = kBoxWords * 4;
-constexpr int kUStages = 4;
-constexpr int kSStages = 2;
-constexpr int kWarpTmaWords = (kUStages + kSStages) * kBoxWords;
+constexpr int kBoxT = kTile;                    // time steps per box
+constexpr int kBoxBytes = kTileWords * 4;       // 4 KB
+constexpr int kStageBytes = 2 * kBoxBytes;      // one wide tile
+constexpr int kUStages = 3;                     // stages per warp in large launches
+constexpr int kMaxUStages = 8;
 constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier before giving up
+
+// dynamic shared memory of a launch with `warps` warps per CTA and `ustages` stages per warp
+static inline size_t srm_tma_smem(int warps, int ustages, int nuEff, bool taps_in_smem)
+{
+    return 1024 + (size_t)warps * ((size_t)ustages * kStageBytes + 2 * kTile * sizeof(unsigned) + ustages * sizeof(uint64_t))
+         + (taps_in_smem ? (size_t)((nuEff + 3) & ~3) * sizeof(float) : 0);
+}
+
+// Potentials of an unskewed wide tile starting at time t0 (T % 4 == 0).
+__device__ __forceinline__ void wide_store(const float *tile, float *g, int64_t row0, int64_t rows,
+                                           int t0, int T, int lane)
+{
+    const int c16 = lane & 15;
+    const int rsub = lane >> 4;
+    const int t = t0 + c16 * 4;
+    if (t >= T) return;
+    const float *half = tile + (c16 >> 3) * kTileWords;
+    const int c = (c16 & 7) * 4;
+    const int64_t nrow = rows - row0;
+    float *dst = g + row0 * (int64_t)T + t;
+#pragma unroll
+    for (int i = 0; i < kTile / 2; ++i) {
+        const int r = i * 2 + rsub;
+        if (r < nrow)
+            *reinterpret_cast<float4 *>(dst + r * (int64_t)T) = *reinterpret_cast<const float4 *>(half + tile_word(r, c));
+    }
+}
+
+// Spike samples of an unskewed wide tile starting at time t0 (T % 4 == 0), from bit masks.
+__device__ __forceinline__ void wide_store_spikes(const unsigned *masks, float *g, int64_t row0, int64_t rows,
+                                                  int t0, int T, int lane, float value)
+{
+    const int c16 = lane & 15;
+    const int rsub = lane >> 4;
+    const int t = t0 + c16 * 4;
+    if (t >= T) return;
+    const unsigned *half = masks + (c16 >> 3) * kTile;
+    const int sh = (c16 & 7) * 4;
+    const int64_t nrow = rows - row0;
+    float *dst = g + row0 * (int64_t)T + t;
+#pragma unroll
+    for (int i = 0; i < kTile / 2; ++i) {
+        const int r = i * 2 + rsub;
+        if (r < nrow) {
+            const unsigned m = half[r] >> sh;
+            *reinterpret_cast<float4 *>(dst + r * (int64_t)T) =
+                make_float4((m & 1u) ? value : 0.0f, (m & 2u) ? value : 0.0f,
+                            (m & 4u) ? value : 0.0f, (m & 8u) ? value : 0.0f);
+        }
+    }
+}
 
 // PER_BLOCK selects where a wait that ran out is recorded: false = the single status word of
 // the device (`status` points to one int); true = one int per block of 32 rows (`status` points
@@ -273,83 +476,75 @@ constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier befor
 // block and sets to the number of tiles walked when it finishes it.
 template <int NB, int W, bool PER_BLOCK = false>
 __global__ void __launch_bounds__(256)
-srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_s,
+srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__restrict__ s, float *u,
                           const float *__restrict__ nu, int64_t rows, int nuEff, int T,
-                          float theta, float spikeVal, int *status)
+                          float theta, float spikeVal, int *status, int ustages)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int warps_per_block = blockDim.x >> 5;
-    // tiles need 512-byte alignment for the swizzle pattern; align the base to 1 KB
+    // the swizzle pattern repeats every 1 KB: align the tiles to that
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    float *wtiles = reinterpret_cast<float *>(base) + warp * kWarpTmaWords;
-    float *u_tiles = wtiles;                                  // kUStages boxes
-    float *s_tiles = wtiles + kUStages * kBoxWords;           // kSStages boxes
-    uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<float *>(base) + warps_per_block * kWarpTmaWords)
-                     + warp * kUStages;
-    const int nuPad = (nuEff + 3) & ~3;
-    float *nu_s = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(reinterpret_cast<float *>(base)
-                  + warps_per_block * kWarpTmaWords) + warps_per_block * kUStages);
-    (void)nuPad;
+    float *u_tiles = reinterpret_cast<float *>(base) + (size_t)warp * ustages * kWideWords;
+    unsigned char *after_tiles = base + (size_t)warps_per_block * ustages * kStageBytes;
+    unsigned *masks = reinterpret_cast<unsigned *>(after_tiles) + warp * 2 * kTile;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after_tiles + warps_per_block * 2 * kTile * sizeof(unsigned))
+                     + warp * ustages;
+    float *nu_s = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(
+                      after_tiles + warps_per_block * 2 * kTile * sizeof(unsigned)) + warps_per_block * ustages);
 
     if (NB == 0) {
         for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
     }
     if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < kUStages; ++i) mbar_init(bars + i, 1);
+        for (int i = 0; i < ustages; ++i) mbar_init(bars + i, 1);
         mbar_init_fence();
     }
     __syncthreads();
 
     SrmRow<NB, W> st;
     st.init(nu, nu_s, nuEff, theta, spikeVal);
-    constexpr bool kRingOk = NB > 0 && NB < kBoxT;
+    constexpr bool kRingOk = NB > 0 && NB < kTile;
     const bool use_ring = kRingOk && st.taps_negative;      // uniform over the grid
-    float ring[kBoxT];
+    float ring[kTile];
 
-    // The warp's work is one stream of tiles: all time tiles of its first block of 32 rows, then
-    // of its next block, ...  Loads run two tiles ahead of the walk across row-block boundaries,
-    // so a change of row block costs no memory latency.  Tile q uses potential stage q % 4
-    // (barrier phase (q / 4) & 1) and spike stage q % 2.
-    const int ntiles = (T + kBoxT - 1) / kBoxT;
+    // The warp's work is one stream of wide tiles: all of its first block of 32 rows, then of
+    // its next block, ...  Loads run ustages - 1 tiles ahead of the walk across row-block
+    // boundaries, so a change of row block costs no memory latency.
+    const int ntiles = (T + kWide - 1) / kWide;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
     int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
     int64_t rb_next = rb;           // (row block, tile) of the next tile to load
     int j_next = 0;
-    unsigned q_next = 0;
+    int sg_next = 0;                // stage the next load goes to
     auto issue_load = [&]() {       // lane 0 only
-        const unsigned sg = q_next % kUStages;
-        mbar_expect_tx(bars + sg, kBoxBytes);
-        tma_load_2d(u_tiles + sg * kBoxWords, &map_u, j_next * kBoxT, (int)(rb_next * kTile), bars + sg);
-        ++q_next;
+        const bool two = kWide * j_next + kBoxT < T;           // the second box starts inside the rows
+        float *dst = u_tiles + sg_next * kWideWords;
+        mbar_expect_tx(bars + sg_next, two ? kStageBytes : kBoxBytes);
+        tma_load_2d(dst, &map_u, kWide * j_next, (int)(rb_next * kTile), bars + sg_next);
+        if (two) tma_load_2d(dst + kTileWords, &map_u, kWide * j_next + kBoxT, (int)(rb_next * kTile), bars + sg_next);
+        if (++sg_next == ustages) sg_next = 0;
         if (++j_next == ntiles) { j_next = 0; rb_next += wstride; }
     };
     if (lane == 0) {
-        if (rb_next < nblocks) issue_load();
-        if (rb_next < nblocks) issue_load();
+        for (int i = 0; i + 1 < ustages; ++i)
+            if (rb_next < nblocks) issue_load();
     }
     int j = 0;
-    for (unsigned q = 0; rb < nblocks; ++q) {
-        const int row0 = (int)(rb * kTile);
-        const unsigned sg = q % kUStages;
-        float *tile = u_tiles + sg * kBoxWords;
-        float *tile_s = s_tiles + (q % kSStages) * kBoxWords;
+    int sg = 0;                     // stage of the tile being walked
+    unsigned parity = 0u;           // barrier phase of that stage
+    while (rb < nblocks) {
+        float *tile = u_tiles + sg * kWideWords;
         if (j == 0) {
             st.reset();
             ring_reset(ring);
             if (PER_BLOCK && lane == 0) status[rb] = 0;
         }
-        if (lane == 0) {
-            // all store groups but the latest have been read out of shared memory: that frees
-            // the potential tile that is loaded next and the spike tile that is written next
-            bulk_wait_read<1>();
-            if (rb_next < nblocks) issue_load();
-        }
-        __syncwarp();
-        const bool ok = mbar_wait_bounded(bars + sg, (q / kUStages) & 1u, kLoadPollLimit);
+        // the stage walked before this one was drained (and fenced) at the end of its iteration
+        if (lane == 0 && rb_next < nblocks) issue_load();
+        const bool ok = mbar_wait_bounded(bars + sg, parity, kLoadPollLimit);
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) {
                 if (PER_BLOCK) status[rb] = -kStatusSrmLoadTimeout;
@@ -358,22 +553,32 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, const __gri
             break;
         }
 
-        if (use_ring) walk_tile<kBoxT, kRingOk, NB, W>(tile, tile_s, st, ring, lane);
-        else walk_tile<kBoxT, false, NB, W>(tile, tile_s, st, ring, lane);
-        fence_proxy_async();    // this lane's tile writes precede the bulk stores below
-        __syncwarp();
-        if (lane == 0) {
-            tma_store_2d(&map_u, j * kBoxT, row0, tile);
-            tma_store_2d(&map_s, j * kBoxT, row0, tile_s);
-            bulk_commit();
+        const bool two = kWide * j + kBoxT < T;
+        unsigned m[2] = {0u, 0u};
+#pragma unroll 1
+        for (int h = 0; h < (two ? 2 : 1); ++h) {
+            const unsigned mh = use_ring
+                ? walk_tile<kTile, kRingOk, NB, W, false>(tile + h * kTileWords, nullptr, st, ring, lane)
+                : walk_tile<kTile, false, NB, W, false>(tile + h * kTileWords, nullptr, st, ring, lane);
+            if (h == 0) m[0] = mh;
+            else m[1] = mh;
         }
+        masks[lane] = m[0];
+        masks[kTile + lane] = m[1];
+        __syncwarp();
+        wide_store(tile, u, rb * kTile, rows, kWide * j, T, lane);
+        wide_store_spikes(masks, s, rb * kTile, rows, kWide * j, T, lane, spikeVal);
+        // the reads of this stage (and of the masks) precede the bulk load that refills it
+        fence_proxy_async();
+        __syncwarp();
+
+        if (++sg == ustages) { sg = 0; parity ^= 1u; }
         if (++j == ntiles) {
             if (PER_BLOCK && lane == 0) status[rb] = ntiles;
             j = 0;
             rb += wstride;
         }
     }
-    if (lane == 0) bulk_wait<0>();  // stores must complete before the shared memory is released
 }
 
 // Direct restatement for refractory kernels too long for the register history: one thread per
@@ -412,30 +617,57 @@ static int launch_srm(const SrmArgs &a)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
     int warps, grid;
-    if (V == 4 && a.use_tma && (a.T & 7) == 0) {
-        CUtensorMap map_u, map_s;
+    // Rows on 16-byte boundaries (T % 4 == 0): bulk tensor copies move the potentials, which
+    // leaves the warps' issue slots to the recurrence.  Any other row length: the wide-tile
+    // kernel with row-skewed cp.async tiles.
+    if (V == 4 && a.use_tma && (a.T & 3) == 0) {
+        CUtensorMap map_u;
         int *status = device_status_word();
         if (status && a.rows * (int64_t)kTile < (1LL << 31) &&
-            encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B) &&
-            encode_rows_tensor_map(&map_s, a.s, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B)) {
-            spike_launch_shape(nblocks, kWarpTmaWords * sizeof(float), warps, grid);
-            const size_t smem = 1024 + (size_t)warps * (kWarpTmaWords * sizeof(float) + kUStages * sizeof(uint64_t))
-                              + (NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) * sizeof(float);
+            encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_128B)) {
+            // stages per warp: as many (up to 8) as still let every warp of the launch be resident
+            const int sms = sm_count();
+            const int64_t warps_per_sm = ceil_div(nblocks, sms);
+            int ustages = (int)((208 * 1024) / (warps_per_sm * kStageBytes));
+            if (ustages > kMaxUStages) ustages = kMaxUStages;
+            if (ustages < kUStages) ustages = kUStages;
+            spike_launch_shape(nblocks, (size_t)ustages * kStageBytes + 512, warps, grid);
+            const size_t smem = srm_tma_smem(warps, ustages, a.nuEff, NB == 0);
             auto kern = srm_get_spikes_tma_kernel<NB, W>;
             int rc = reserve_dynamic_smem((const void *)kern, smem);
             if (rc) return rc;
-            kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, map_s, a.nu, a.rows, a.nuEff, a.T, a.theta,
-                                                                 a.spikeVal, status);
+            kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
+                                                                 a.spikeVal, status, ustages);
             return check_launch("srm_get_spikes (bulk tensor copy) kernel launch");
         }
     }
-    spike_launch_shape(nblocks, 3 * kTileWords * sizeof(float), warps, grid);
-    const size_t smem = (size_t)((NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) + warps * 3 * kTileWords) * sizeof(float);
-    auto kern = srm_get_spikes_kernel<V, NB, W>;
-    int rc = reserve_dynamic_smem((const void *)kern, smem);
-    if (rc) return rc;
-    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta, a.spikeVal);
-    return check_launch("srm_get_spikes kernel launch");
+    const size_t nu_bytes = (size_t)(NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) * sizeof(float);
+    if constexpr (V == 4) {
+        // prefetch depth 4 when every warp of the launch is resident at once even with the
+        // larger footprint (then latency, not bandwidth, bounds the launch), depth 2 otherwise
+        const size_t deep_bytes = (4 * kWideWords + 2 * kTile) * sizeof(float);
+        const int depth = nblocks <= (int64_t)((216 * 1024) / deep_bytes) * sm_count() ? 4 : 2;
+        const size_t warp_bytes = (size_t)(depth * kWideWords + 2 * kTile) * sizeof(float);
+        spike_launch_shape(nblocks, warp_bytes, warps, grid);
+        const size_t smem = nu_bytes + warps * warp_bytes;
+        // rows that start on 32-byte boundaries need no skew
+        const bool skew = (a.T & 7) != 0 || (reinterpret_cast<uintptr_t>(a.u) & 31u) != 0;
+        auto kern = skew ? srm_get_spikes_wide_kernel<NB, W, true> : srm_get_spikes_wide_kernel<NB, W, false>;
+        int rc = reserve_dynamic_smem((const void *)kern, smem);
+        if (rc) return rc;
+        kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta, a.spikeVal, depth);
+        return check_launch("srm_get_spikes (wide tile) kernel launch");
+    } else {
+        const int64_t deep_warps_per_sm = (216 * 1024) / (5 * kTileWords * (int64_t)sizeof(float));
+        const int depth = nblocks <= deep_warps_per_sm * sm_count() ? 4 : 2;
+        spike_launch_shape(nblocks, (depth + 1) * kTileWords * sizeof(float), warps, grid);
+        const size_t smem = nu_bytes + (size_t)warps * (depth + 1) * kTileWords * sizeof(float);
+        auto kern = srm_get_spikes_kernel<V, NB, W>;
+        int rc = reserve_dynamic_smem((const void *)kern, smem);
+        if (rc) return rc;
+        kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta, a.spikeVal, depth);
+        return check_launch("srm_get_spikes kernel launch");
+    }
 }
 
 template <int V>
@@ -487,20 +719,18 @@ template <int NB, int W>
 static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev, int slot)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
-    CUtensorMap map_u, map_s;
-    if (!encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B) ||
-        !encode_rows_tensor_map(&map_s, a.s, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_64B)) {
+    CUtensorMap map_u;
+    if (!encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_128B)) {
         set_error("srm_get_spikes_noalloc: cannot describe the buffers for bulk tensor copies");
         return SLAYER_B200_EUNSUPPORTED;
     }
     int warps, grid;
-    spike_launch_shape(nblocks, kWarpTmaWords * sizeof(float), warps, grid);
-    const size_t smem = 1024 + (size_t)warps * (kWarpTmaWords * sizeof(float) + kUStages * sizeof(uint64_t))
-                      + (NB > 0 ? 0 : ((a.nuEff + 3) & ~3)) * sizeof(float);
+    spike_launch_shape(nblocks, (size_t)kUStages * kStageBytes + 512, warps, grid);
+    const size_t smem = srm_tma_smem(warps, kUStages, a.nuEff, NB == 0);
     auto kern = srm_get_spikes_tma_kernel<NB, W, true>;
     if (!dev.smem_set[slot]) {
         // the largest request any launch of this instantiation can make (8 warps, 257 taps)
-        const int most = 1024 + 8 * (int)(kWarpTmaWords * sizeof(float) + kUStages * sizeof(uint64_t)) + 260 * 4;
+        const int most = (int)srm_tma_smem(8, kUStages, 260, true);
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
         if (e != cudaSuccess) {
             set_error("srm_get_spikes_noalloc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
@@ -508,8 +738,8 @@ static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev, int slot)
         }
         dev.smem_set[slot] = true;
     }
-    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, map_s, a.nu, a.rows, a.nuEff, a.T, a.theta,
-                                                         a.spikeVal, dev.scratch);
+    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
+                                                         a.spikeVal, dev.scratch, kUStages);
     return check_launch("srm_get_spikes_noalloc kernel launch");
 }
 

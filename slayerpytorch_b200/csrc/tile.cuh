@@ -185,6 +185,106 @@ __device__ __forceinline__ void tile_store_skew(const float *tile, float *g, int
 // number of 32-step tiles that cover a row of T samples for every skew (0..7)
 __host__ __device__ inline int skew_tiles(int T) { return (T + 7 + kTile - 1) / kTile; }
 
+// ---------------------------------------------------------------------------------------
+// Wide row-skewed tiles: 64 time steps = two 32-step halves, each laid out like the tile
+// above, `half` h at word offset h * kTileWords.  DRAM throughput on this part depends on how
+// many contiguous bytes of a row one request covers: 128 bytes per row (a 32-step tile)
+// sustain about three quarters of what 256 bytes do.  So the fills and drains below cover a
+// whole 256-byte row segment per group of 16 lanes, two rows per instruction; the walk still
+// sees two ordinary 32-step tiles.
+// ---------------------------------------------------------------------------------------
+constexpr int kWide = 2 * kTile;                // time steps per wide tile
+constexpr int kWideWords = 2 * kTileWords;
+
+// number of wide tiles that cover a row of T samples for every skew (0..7)
+__host__ __device__ inline int skew_wide_tiles(int T) { return (T + 7 + kWide - 1) / kWide; }
+
+template <bool SKEW = true>
+__device__ __forceinline__ void wide_prefetch_skew(float *tile, const float *g, int64_t row0, int64_t rows,
+                                                   int j, int T, int lane, int skew0, float pad)
+{
+    const int c16 = lane & 15;                  // 16-byte chunk of the 256-byte row segment
+    const int rsub = lane >> 4;
+    float *half = tile + (c16 >> 3) * kTileWords;
+    const int c = (c16 & 7) * 4;                // column inside the half
+    const int64_t nrow = rows - row0;
+#pragma unroll
+    for (int i = 0; i < kTile / 2; ++i) {
+        const int r = i * 2 + rsub;
+        const int t = kWide * j - (SKEW ? row_skew(skew0, r, T) : 0) + c16 * 4;      // time of the chunk's first sample
+        float *dst = half + tile_word(r, c);
+        const float *src = g + (row0 + r) * (int64_t)T + t;
+        if (r >= nrow || t >= T) {
+            cp_async<16>(dst, g, false);
+        } else if (t >= 0 && t + 4 <= T) {
+            cp_async<16>(dst, src, true);
+        } else if (t + 4 <= 0) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(pad, pad, pad, pad);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (t + e < 0) dst[e] = pad;
+                else cp_async<4>(dst + e, (t + e < T) ? src + e : g, t + e < T);
+            }
+        }
+    }
+}
+
+// Store four samples starting at time t of a row (clipped to [0, T)).
+__device__ __forceinline__ void store_clipped4(float *row, int t, int T, const float4 &v)
+{
+    if (t >= T || t + 4 <= 0) return;
+    if (t >= 0 && t + 4 <= T) {
+        *reinterpret_cast<float4 *>(row + t) = v;
+    } else {
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (t + k >= 0 && t + k < T) row[t + k] = e[k];
+    }
+}
+
+template <bool SKEW = true>
+__device__ __forceinline__ void wide_store_skew(const float *tile, float *g, int64_t row0, int64_t rows,
+                                                int j, int T, int lane, int skew0)
+{
+    const int c16 = lane & 15;
+    const int rsub = lane >> 4;
+    const float *half = tile + (c16 >> 3) * kTileWords;
+    const int c = (c16 & 7) * 4;
+    const int64_t nrow = rows - row0;
+#pragma unroll
+    for (int i = 0; i < kTile / 2; ++i) {
+        const int r = i * 2 + rsub;
+        if (r >= nrow) continue;
+        const int t = kWide * j - (SKEW ? row_skew(skew0, r, T) : 0) + c16 * 4;
+        store_clipped4(g + (row0 + r) * (int64_t)T, t, T, *reinterpret_cast<const float4 *>(half + tile_word(r, c)));
+    }
+}
+
+// Spike samples of a wide tile kept as bit masks: masks[h * 32 + r] bit i = row r spiked at
+// step i of half h.  They are expanded to `value` / 0 on their way to global memory.
+template <bool SKEW = true>
+__device__ __forceinline__ void wide_store_spikes_skew(const unsigned *masks, float *g, int64_t row0, int64_t rows,
+                                                       int j, int T, int lane, int skew0, float value)
+{
+    const int c16 = lane & 15;
+    const int rsub = lane >> 4;
+    const unsigned *half = masks + (c16 >> 3) * kTile;
+    const int sh = (c16 & 7) * 4;
+    const int64_t nrow = rows - row0;
+#pragma unroll
+    for (int i = 0; i < kTile / 2; ++i) {
+        const int r = i * 2 + rsub;
+        if (r >= nrow) continue;
+        const int t = kWide * j - (SKEW ? row_skew(skew0, r, T) : 0) + c16 * 4;
+        const unsigned m = half[r] >> sh;
+        store_clipped4(g + (row0 + r) * (int64_t)T, t, T,
+                       make_float4((m & 1u) ? value : 0.0f, (m & 2u) ? value : 0.0f,
+                                   (m & 4u) ? value : 0.0f, (m & 8u) ? value : 0.0f));
+    }
+}
+
 // Launch shape of the warp-per-32-rows kernels: warps per CTA and a grid that gives every SM
 // the same number of resident warps (as many as shared memory allows, at most 32), each warp
 // then strides over the row blocks.  Small problems get smaller CTAs so that all SMs take part.
