@@ -27,25 +27,41 @@ delay_grad_kernel(float *__restrict__ grad_delay, const float *__restrict__ g, c
 
     for (int64_t n = blockIdx.x; n < nNeurons; n += gridDim.x) {
         float acc = 0.0f;
-        for (int64_t b = warp; b < nBatch; b += kDelayGradWarps) {
-            const float *gr = g + (b * nNeurons + n) * (int64_t)T;
-            const float *orow = out + (b * nNeurons + n) * (int64_t)T;
+        // two batch samples per pass, so that each lane keeps four 128-bit loads in flight
+        for (int64_t b = warp; b < nBatch; b += 2 * kDelayGradWarps) {
+            const int64_t b2 = b + kDelayGradWarps;
+            const bool two = b2 < nBatch;
+            const float *g0 = g + (b * nNeurons + n) * (int64_t)T;
+            const float *o0 = out + (b * nNeurons + n) * (int64_t)T;
+            const float *g1 = two ? g + (b2 * nNeurons + n) * (int64_t)T : g0;
+            const float *o1 = two ? out + (b2 * nNeurons + n) * (int64_t)T : o0;
+            float acc1 = 0.0f;
             if (VEC) {
                 for (int t = lane * 4; t < T; t += 128) {
-                    const float4 gv = __ldg(reinterpret_cast<const float4 *>(gr + t));
-                    const float4 ov = __ldg(reinterpret_cast<const float4 *>(orow + t));
-                    const float prev = t > 0 ? __ldg(orow + t - 1) : 0.0f;
-                    acc = fmaf(gv.x, fmaf(prev, f1, ov.x * f0), acc);
-                    acc = fmaf(gv.y, fmaf(ov.x, f1, ov.y * f0), acc);
-                    acc = fmaf(gv.z, fmaf(ov.y, f1, ov.z * f0), acc);
-                    acc = fmaf(gv.w, fmaf(ov.z, f1, ov.w * f0), acc);
+                    const float4 ga = __ldg(reinterpret_cast<const float4 *>(g0 + t));
+                    const float4 oa = __ldg(reinterpret_cast<const float4 *>(o0 + t));
+                    const float4 gb = __ldg(reinterpret_cast<const float4 *>(g1 + t));
+                    const float4 ob = __ldg(reinterpret_cast<const float4 *>(o1 + t));
+                    const float pa = t > 0 ? __ldg(o0 + t - 1) : 0.0f;
+                    const float pb = t > 0 ? __ldg(o1 + t - 1) : 0.0f;
+                    acc = fmaf(ga.x, fmaf(pa, f1, oa.x * f0), acc);
+                    acc = fmaf(ga.y, fmaf(oa.x, f1, oa.y * f0), acc);
+                    acc = fmaf(ga.z, fmaf(oa.y, f1, oa.z * f0), acc);
+                    acc = fmaf(ga.w, fmaf(oa.z, f1, oa.w * f0), acc);
+                    acc1 = fmaf(gb.x, fmaf(pb, f1, ob.x * f0), acc1);
+                    acc1 = fmaf(gb.y, fmaf(ob.x, f1, ob.y * f0), acc1);
+                    acc1 = fmaf(gb.z, fmaf(ob.y, f1, ob.z * f0), acc1);
+                    acc1 = fmaf(gb.w, fmaf(ob.z, f1, ob.w * f0), acc1);
                 }
             } else {
                 for (int t = lane; t < T; t += 32) {
-                    const float prev = t > 0 ? __ldg(orow + t - 1) : 0.0f;
-                    acc = fmaf(__ldg(gr + t), fmaf(prev, f1, __ldg(orow + t) * f0), acc);
+                    const float pa = t > 0 ? __ldg(o0 + t - 1) : 0.0f;
+                    const float pb = t > 0 ? __ldg(o1 + t - 1) : 0.0f;
+                    acc = fmaf(__ldg(g0 + t), fmaf(pa, f1, __ldg(o0 + t) * f0), acc);
+                    acc1 = fmaf(__ldg(g1 + t), fmaf(pb, f1, __ldg(o1 + t) * f0), acc1);
                 }
             }
+            if (two) acc += acc1;
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
