@@ -49,11 +49,11 @@ TGT_TRUE, TGT_FALSE = 60, 10
 
 # algorithmic bytes per neuron-timestep of each operator (read + write of fp32 tensors)
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12}
-KERNEL_OF = {"conv": "fir_kernel", "corr": "fir_kernel", "getSpikes": "srm_get_spikes_kernel",
+KERNEL_OF = {"conv": "fir_kernel", "corr": "fir_kernel", "getSpikes": "srm_get_spikes_tma_kernel",
              "shift": "shift_vec4_kernel", "spikeGrad": "spike_grad_vec4_kernel"}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count); see the summaries under profiles/.  None = not captured yet.
-NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_kernel": 12.13,
+NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_tma_kernel": 11.62,
                            "shift_vec4_kernel": None, "spike_grad_vec4_kernel": None}
 
 
