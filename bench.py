@@ -14,7 +14,7 @@ Metric: neuron-timesteps per second = batch * (512 + 10) * 300 per step / step t
 all GPUs (weak scaling: every rank processes its own batch of 64; no collective on this path).
 
 One JSON line is printed by rank 0.  ``value`` is measured with inputs resident in HBM, L2
-flushed between steps, CUDA events around each step, the step's ten launches replayed from a
+flushed between steps, CUDA events around each step, the step's launches replayed from a
 CUDA graph (``eager_ms_per_step`` is the same loop launched call by call); ``e2e`` is the same
 chain through the package's public layer API with host (pinned) buffers, copies inside the
 timed region, streamed in batch chunks by ``HostPipeline`` (``single_call_ms_per_step`` is one
@@ -48,9 +48,10 @@ BATCH, N_IN, N_HID, N_OUT, T = 64, 2312, 512, 10, 300
 TGT_TRUE, TGT_FALSE = 60, 10
 
 # algorithmic bytes per neuron-timestep of each operator (read + write of fp32 tensors)
-ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12}
+ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12, "spikeGradShift": 12}
 KERNEL_OF = {"conv": "fir_kernel", "corr": "fir_kernel", "getSpikes": "srm_get_spikes_tma_kernel",
-             "shift": "shift_vec4_kernel", "spikeGrad": "spike_grad_vec4_kernel"}
+             "shift": "shift_vec4_kernel", "spikeGrad": "spike_grad_vec4_kernel",
+             "spikeGradShift": "shift_vec4_kernel"}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count); see the summaries under profiles/.  None = not captured yet.
 NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_tma_kernel": 11.62,
@@ -145,6 +146,11 @@ def make_workload(ops, device, seed, batch=BATCH):
                 theta=theta, tau=tau, scale=scale, Ts=Ts)
 
 
+def workload_name(wl):
+    return ("config 2: SRM MLP 2312-512-10 hot path, batch 64 per GPU, T=300, Ts=1, input rate 5%%, psp K=%d, "
+            "refractory %d taps, delays U(0,5)" % (wl["srm"].numel(), wl["ref"].numel()))
+
+
 def hot_path(ops, wl, record=None):
     """One step.  `record(name, rows, fn)` wraps an operator call for per-kernel timing."""
     Ts, theta, tau, scale = wl["Ts"], wl["theta"], wl["tau"], wl["scale"]
@@ -155,8 +161,12 @@ def hot_path(ops, wl, record=None):
     s1 = run("getSpikes", True, lambda: ops.getSpikes(u1, ref, theta, Ts))
     d1 = run("shift", True, lambda: ops.shift(s1, delay, Ts))
     # hidden layer: backward
-    b1 = run("shift", True, lambda: ops.shift(wl["g1"], wl["neg_delay"], Ts))
-    b2 = run("spikeGrad", True, lambda: ops.spikeGrad(b1, u1, theta, tau, scale))
+    if wl.get("unfused"):
+        b1 = run("shift", True, lambda: ops.shift(wl["g1"], wl["neg_delay"], Ts))
+        b2 = run("spikeGrad", True, lambda: ops.spikeGrad(b1, u1, theta, tau, scale))
+    else:       # shift back and surrogate gradient in one pass (same bits, no intermediate tensor)
+        b2 = run("spikeGradShift", True,
+                 lambda: ops.spikeGradShift(wl["g1"], u1, wl["neg_delay"], theta, tau, scale, Ts))
     b3 = run("corr", True, lambda: ops.corr(b2, srm, Ts))
     # output layer: forward and backward
     u2 = run("conv", False, lambda: ops.conv(wl["a2"], srm, Ts))
@@ -166,7 +176,8 @@ def hot_path(ops, wl, record=None):
     return d1, b3, s2, c3
 
 
-LAUNCHES_PER_STEP = 10
+def launches_per_step(wl):
+    return 10 if wl.get("unfused") else 9
 
 
 # ------------------------------------------------------------------------------ GPU clocks
@@ -234,6 +245,7 @@ def time_ours(args, rank, world, device):
     peak, peak_kind = measured_peak_gbs()
 
     wl = make_workload(slayerCuda, device, seed=1002 + 97 * rank)
+    wl["unfused"] = bool(args.unfused)
     units = BATCH * (N_HID + N_OUT) * T
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
@@ -260,7 +272,7 @@ def time_ours(args, rank, world, device):
         hot_path(slayerCuda, wl)
     barrier()
 
-    # The ten launches of a step are short (7-50 us), so the step is replayed from a CUDA graph
+    # The launches of a step are short (7-50 us), so the step is replayed from a CUDA graph
     # captured once: the same kernels on the same buffers, without per-launch host overhead.
     graph, graph_note = None, None
     if not args.no_graph:
@@ -312,7 +324,10 @@ def time_ours(args, rank, world, device):
     def device_step(a1, a2, g1, g2):
         a1 = a1.detach().requires_grad_(True)
         a2 = a2.detach().requires_grad_(True)
-        d1 = net.delayShift(net.spike(net.psp(a1)), delay_dev, SIM["Ts"])
+        if args.unfused:
+            d1 = net.delayShift(net.spike(net.psp(a1)), delay_dev, SIM["Ts"])
+        else:
+            d1 = net.spikeDelayed(net.psp(a1), delay_dev)
         s2 = net.spike(net.psp(a2))
         torch.autograd.backward([d1, s2], [g1, g2])
         return d1.detach(), s2.detach(), a1.grad, a2.grad
@@ -389,9 +404,10 @@ def time_ours(args, rank, world, device):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 2: SRM MLP 2312-512-10 hot path, batch 64 per GPU, T=300, Ts=1, "
-                               "input rate 5%%, psp K=%d, refractory %d taps, delays U(0,5)"
-                               % (wl["srm"].numel(), wl["ref"].numel()),
+        "config": {"workload": workload_name(wl),
+                   "backward": "hidden layer: shift back and surrogate gradient as two launches (reference sequence)"
+                               if args.unfused else
+                               "hidden layer: shift back and surrogate gradient fused into one launch (spikeGradShift)",
                    "neuron_timesteps_per_step_per_gpu": units, "l2": "flushed between steps (256 MiB write)",
                    "spike_rates": wl["rates"], "parallelism": "batch sharded, no collective"},
         "clocks": clocks,
@@ -403,10 +419,10 @@ def time_ours(args, rank, world, device):
                           "" if args.no_graph else ", each chunk's step one CUDA-graph launch"),
                 "single_call_ms_per_step": e2e_serial_ms / args.steps,
                 "pcie_GB/s_per_direction": round(bytes_io / (e2e_ms / args.steps * 1e-3) / 1e9, 1)},
-        "launch_mode": ("cuda graph replay of the step's %d launches" % LAUNCHES_PER_STEP) if graph is not None
+        "launch_mode": ("cuda graph replay of the step's %d launches" % launches_per_step(wl)) if graph is not None
                        else ("eager" + (" (%s)" % graph_note if graph_note else "")),
         "eager_ms_per_step": eager_ms / args.steps,
-        "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+        "gpu_launches": launches_per_step(wl) * args.steps,
         "roofline": roofline,
         "cpu_baseline": cpu,
         "per_op": op_table,
@@ -426,6 +442,7 @@ def scaled_variant(ops, device, peak):
          * (torch.rand(batch, N_HID, 1, 1, T, device=device, generator=gen) < 0.3)).float()
     g = torch.randn(batch, N_HID, 1, 1, T, device=device, generator=gen)
     delay = torch.rand(N_HID, device=device, generator=gen) * 5
+    neg_delay = -delay
     Ts, theta, tau, scale = 1.0, 10.0, 10.0, 1.0
     times = {}
 
@@ -442,26 +459,31 @@ def scaled_variant(ops, device, peak):
         u = run("conv", lambda: ops.conv(a, srm, Ts))
         s = run("getSpikes", lambda: ops.getSpikes(u, ref, theta, Ts))
         d = run("shift", lambda: ops.shift(s, delay, Ts))
-        b1 = run("shift", lambda: ops.shift(g, -delay, Ts))
+        b1 = run("shift", lambda: ops.shift(g, neg_delay, Ts))
         b2 = run("spikeGrad", lambda: ops.spikeGrad(b1, u, theta, tau, scale))
+        b2f = run("spikeGradShift", lambda: ops.spikeGradShift(g, u, neg_delay, theta, tau, scale, Ts))
         b3 = run("corr", lambda: ops.corr(b2, srm, Ts))
         if rate is None:
             rate = float(s.mean())
-        del u, s, d, b1, b2, b3
+        del u, s, d, b1, b2, b2f, b3
     torch.cuda.synchronize()
-    res, total = {}, 0.0
+    res, t_of = {}, {}
     for name, evs in times.items():
         ms = [a_.elapsed_time(b_) for a_, b_ in evs[len(evs) // 5 * 2:]]     # drop 2 warm-up rounds
         t = sum(ms) / len(ms)
-        per_round = t * (2 if name == "shift" else 1)
-        total += per_round
+        t_of[name] = t
         gbs = ALG_BYTES[name] * el / (t * 1e-3) / 1e9
         res[name] = {"ms": round(t, 4), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4)}
+    # the chain as the benchmark step runs it: conv, getSpikes, shift, spikeGradShift, corr (48 bytes
+    # per element); the reference's sequence has one more shift and a separate spikeGrad (56 bytes)
+    total = t_of["conv"] + t_of["getSpikes"] + t_of["shift"] + t_of["spikeGradShift"] + t_of["corr"]
+    total_ref_seq = t_of["conv"] + t_of["getSpikes"] + 2 * t_of["shift"] + t_of["spikeGrad"] + t_of["corr"]
     return {"workload": "hidden-layer chain, batch %d (%d x %d fp32 = %.2f GiB per tensor)"
                         % (batch, batch * N_HID, T, el * 4 / 2 ** 30),
             "value": el / (total * 1e-3), "unit": UNIT, "ms_per_step": total,
-            "chain_GB/s": round(56 * el / (total * 1e-3) / 1e9, 1),
-            "chain_frac_of_hbm_peak": round(56 * el / (total * 1e-3) / 1e9 / peak, 4),
+            "chain_GB/s": round(48 * el / (total * 1e-3) / 1e9, 1),
+            "chain_frac_of_hbm_peak": round(48 * el / (total * 1e-3) / 1e9 / peak, 4),
+            "reference_sequence_ms_per_step": total_ref_seq,
             "spike_rate": rate, "per_op": res}
 
 
@@ -469,6 +491,7 @@ def scaled_variant(ops, device, peak):
 def cpu_baseline_value(reps=3, ops=None):
     ops = ops or OracleOps()
     wl = make_workload(ops, torch.device("cpu"), seed=1002)
+    wl["unfused"] = True            # the reference's own sequence of operators
     units = BATCH * (N_HID + N_OUT) * T
     best = None
     for _ in range(reps):
@@ -512,6 +535,7 @@ def time_reference(args, rank, world):
         return None
     ops = OracleOps()
     wl = make_workload(ops, torch.device("cpu"), seed=1002)
+    wl["unfused"] = True            # the reference's own sequence of operators
     units = BATCH * (N_HID + N_OUT) * T
     for _ in range(max(1, min(args.warmup, 3))):
         hot_path(ops, wl)
@@ -524,7 +548,7 @@ def time_reference(args, rank, world):
            "steps": args.steps, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": dt / args.steps * 1e3,
            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
            "data": "synthetic",
-           "config": {"workload": "config 2: SRM MLP 2312-512-10 hot path, batch 64, T=300 (same tensors as the GPU arm)",
+           "config": {"workload": workload_name(wl),
                       "what": "explicit time-loop formulation of the reference operators (C restatement, OpenMP) on the host cores"},
            "cpu_baseline": {"value": value, "unit": UNIT, "cores": ops.threads, "kind": "port",
                             "sample": "full config-2 batch per step"},
@@ -543,6 +567,7 @@ def time_reference_cuda(ops, steps):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     wl = make_workload(ops, device, seed=1002)
+    wl["unfused"] = True
     units = BATCH * (N_HID + N_OUT) * T
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     for _ in range(3):
@@ -568,6 +593,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--unfused", action="store_true",
+                    help="backward pass of the hidden layer as the reference's two operators (shift, then surrogate "
+                         "gradient) instead of the fused spikeGradShift")
     ap.add_argument("--no-graph", action="store_true", help="time the eager launch loop instead of a CUDA-graph replay")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the end-to-end host pipeline")
     ap.add_argument("--no-scaled", action="store_true", help="skip the batch-scaled (>= 1 GiB tensors) variant")

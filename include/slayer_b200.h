@@ -108,6 +108,20 @@ int slayer_b200_spike_grad(float *out, const float *g, const float *u, int64_t n
                            float theta, float tau, float scale, void *stream);
 
 /*
+ * Backward step of "spike, then delay" in one pass:
+ *   out[b,n,t] = shifted(b,n,t) * scale/tau * exp(-|u[b,n,t] - theta| / tau),
+ *   shifted(b,n,t) = grad_output[b,n,t - d_n] if 0 <= t - d_n < T else 0,
+ *   d_n = trunc(shift_n / Ts),  shift_n = shift_lut[n] if shift_lut is not NULL, else `shift`.
+ * The same result as slayer_b200_shift_lut / _scalar followed by slayer_b200_spike_grad, bit
+ * for bit, without the intermediate tensor.  The caller passes the shift to apply to the
+ * gradient, i.e. minus the forward delay (as _delayFunction.backward does, src/slayer.py:957,
+ * before the expression at src/slayer.py:862).  out must not alias grad_output.
+ */
+int slayer_b200_spike_grad_shift(float *out, const float *grad_output, const float *u, const float *shift_lut,
+                                 float shift, int64_t nBatch, int64_t nNeurons, int64_t T, float Ts,
+                                 float theta, float tau, float scale, void *stream);
+
+/*
  * Gradient with respect to per-neuron axonal delays, fused into one pass:
  *   grad_delay[n] = Ts * sum_{b,t} grad_output[b,n,t] * diff[b,n,t],
  *   diff[b,n,t]   = (output[b,n,t-1] - output[b,n,t]) / Ts,   output[.., -1] = 0,

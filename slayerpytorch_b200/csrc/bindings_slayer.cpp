@@ -7,7 +7,8 @@
 //   - a one-element shift tensor is read on the device (no host synchronisation);
 //   - the per-neuron shift covers the whole batch in one launch;
 //   - dtype is checked explicitly;
-//   - additional operators are exported: spikeGrad, spikeGrad_ (in place) and delayGrad.
+//   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift and
+//     delayGrad.
 #include "bindings_common.h"
 
 using namespace sb200py;
@@ -125,6 +126,36 @@ static torch::Tensor spikeGradInplaceCuda(torch::Tensor gradOut, torch::Tensor u
     return spikeGradImpl(gradOut, gradOut, u, theta, tau, scale);
 }
 
+// spikeGrad(shift(gradOutput, shiftLUT, Ts), membranePotential, ...) in one pass: the backward
+// step of a spike layer followed by a delay.  shiftLUT is the shift to apply to the gradient
+// (minus the forward delay): one value per neuron, or a single value for all rows.
+static torch::Tensor spikeGradShiftCuda(torch::Tensor gradOut, torch::Tensor u, torch::Tensor shiftLUT,
+                                        float theta, float tau, float scale, float Ts)
+{
+    check_input(gradOut, "gradOutput");
+    check_input(u, "membranePotential");
+    check_input(shiftLUT, "shiftLUT");
+    check_device(gradOut, u, "gradOutput", "membranePotential");
+    check_device(gradOut, shiftLUT, "gradOutput", "shiftLUT");
+    TORCH_CHECK(gradOut.sizes() == u.sizes(), "gradOutput and membranePotential must have the same shape");
+    TORCH_CHECK(gradOut.dim() >= 2, "spikeGradShift expects [batch, ..., time] tensors");
+    c10::cuda::CUDAGuard guard(gradOut.device());
+    auto output = torch::empty_like(gradOut);
+    const int64_t T = gradOut.size(-1);
+    const int64_t rows = T ? gradOut.numel() / T : 0;
+    int64_t nBatch = rows, nNeurons = 1;
+    if (shiftLUT.numel() != 1) {
+        nBatch = gradOut.size(0);
+        nNeurons = nBatch ? rows / nBatch : 0;
+        TORCH_CHECK(shiftLUT.numel() == nNeurons, "shift and number of neurons must be same");
+    }
+    check_rc(slayer_b200_spike_grad_shift(output.data_ptr<float>(), gradOut.data_ptr<float>(), u.data_ptr<float>(),
+                                          shiftLUT.data_ptr<float>(), 0.0f, nBatch, nNeurons, T, Ts, theta, tau, scale,
+                                          current_stream()),
+             "spikeGradShift");
+    return output;
+}
+
 // gradDelay of _delayFunction.backward (src/slayer.py:950-954) in one pass; the result has the
 // shape of gradOutput without its first (batch) and last (time) dimension.
 static torch::Tensor delayGradCuda(torch::Tensor gradOut, torch::Tensor output, float Ts)
@@ -159,6 +190,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("spikeGrad", &spikeGradCuda,
           "gradOutput * scale/tau * exp(-|u - theta| / tau) in one pass (CUDA)");
     m.def("spikeGrad_", &spikeGradInplaceCuda, "In-place variant of spikeGrad (overwrites gradOutput)");
+    m.def("spikeGradShift", &spikeGradShiftCuda, "Surrogate gradient of the time-shifted gradient in one pass (CUDA)");
     m.def("delayGrad", &delayGradCuda, "Ts * sum over batch and time of gradOutput * d(output)/dt per neuron (CUDA)");
     m.attr("backend") = "slayer_b200";
 }

@@ -57,4 +57,14 @@ __host__ __device__ inline int shift_steps(float shift, float Ts)
 #endif
 }
 
+#ifdef __CUDACC__
+// g * (c * exp(-|u - theta| / tau)): the surrogate gradient of the spike function applied to
+// an incoming gradient sample; c = scale / tau.  IEEE division, as the tensor expression.
+__device__ __forceinline__ float rho_times(float g, float u, float theta, float tau, float c)
+{
+    const float e = expf(__fdiv_rn(-fabsf(u - theta), tau));
+    return g * (c * e);
+}
+#endif
+
 }  // namespace sb200

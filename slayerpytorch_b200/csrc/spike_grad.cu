@@ -7,12 +7,6 @@
 
 namespace sb200 {
 
-__device__ __forceinline__ float rho_times(float g, float u, float theta, float tau, float c)
-{
-    const float e = expf(__fdiv_rn(-fabsf(u - theta), tau));
-    return g * (c * e);
-}
-
 __global__ void __launch_bounds__(256)
 spike_grad_vec4_kernel(float4 *out, const float4 *g,
                        const float4 *__restrict__ u, int64_t n4,

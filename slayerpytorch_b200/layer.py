@@ -13,6 +13,8 @@ differences that do not change results beyond fp32 rounding of ``exp``:
   chain of elementwise tensor operations;
 * the delay gradient is one fused reduction (``slayerCuda.delayGrad``) instead of a two-tap
   conv, a product and a tensor sum;
+* ``spikeDelayed`` (an addition to the interface) runs spike generation and the delay that
+  follows it as one autograd node whose backward is a single pass (``slayerCuda.spikeGradShift``);
 * scalars (``Ts``, ``theta`` ...) stay Python floats, so no backward pass synchronises the host
   to read a 0-dim device tensor.
 
@@ -122,6 +124,41 @@ class _DelayFunction(torch.autograd.Function):
         grad = grad.contiguous()
         grad_delay = slayerCuda.delayGrad(grad, out, Ts)      # one fused pass, no temporaries
         return slayerCuda.shift(grad, -delay, Ts), grad_delay.reshape(delay.shape), None
+
+
+class _SpikeDelayFunction(torch.autograd.Function):
+    """Spike generation followed by a per-neuron (or uniform) delay as one autograd node.
+
+    Forward is ``shift(getSpikes(u), delay)`` on the two operators; backward is one fused pass
+    ``spikeGradShift`` (shifted gradient times surrogate gradient, src/slayer.py:957 and :862
+    combined) plus, when the delay is learnable, the fused delay gradient.  Results equal those
+    of ``_SpikeFunction`` followed by ``_DelayFunction`` / ``_DelayShiftFunction`` bit for bit."""
+
+    @staticmethod
+    def forward(ctx, u, refKernel, neuron, Ts, delay):
+        u = u.contiguous()
+        Ts = float(Ts)
+        spikes = slayerCuda.getSpikes(u, refKernel, neuron['theta'], Ts)
+        d = delay.detach()
+        out = slayerCuda.shift(spikes, d, Ts)
+        ctx.learn_delay = bool(delay.requires_grad)
+        ctx.delay_shape = delay.shape
+        ctx.save_for_backward(u, d, out if ctx.learn_delay else d)
+        ctx.theta = float(neuron['theta'])
+        ctx.tau = float(neuron['tauRho'] * neuron['theta'])
+        ctx.scale = float(neuron['scaleRho'])
+        ctx.Ts = Ts
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        u, d, out = ctx.saved_tensors
+        grad = grad.contiguous()
+        grad_delay = None
+        if ctx.learn_delay:
+            grad_delay = slayerCuda.delayGrad(grad, out, ctx.Ts).reshape(ctx.delay_shape)
+        grad_u = slayerCuda.spikeGradShift(grad, u, -d, ctx.theta, ctx.tau, ctx.scale, ctx.Ts)
+        return grad_u, None, None, None, grad_delay
 
 
 class _DelayShiftFunction(torch.autograd.Function):
@@ -247,6 +284,21 @@ class spikeLayer(torch.nn.Module):
 
     def delayShift(self, input, delay, Ts=1):
         return _DelayShiftFunction.apply(input, delay, Ts)
+
+    def spikeDelayed(self, membranePotential, delay):
+        """``spike`` followed by a delay, as one autograd node with a fused backward pass.
+
+        ``delay`` is a delay layer made by ``self.delay(...)`` (learnable: its parameter
+        receives the delay gradient), or a tensor with one value per neuron or a single value
+        (fixed, like ``delayShift``).  Not part of the reference's interface."""
+        if isinstance(delay, _DelayLayer):
+            d = delay.delay
+            N, C, H, W, Ns = membranePotential.shape
+            if membranePotential.numel() != d.numel() * Ns * N:
+                d = d.repeat((1, H, W))
+        else:
+            d = torch.as_tensor(delay, dtype=torch.float32, device=membranePotential.device)
+        return _SpikeDelayFunction.apply(membranePotential, self.refKernel, self.neuron, self.simulation['Ts'], d)
 
     def delay(self, inputSize):
         return _DelayLayer(inputSize, self.simulation['Ts'])

@@ -2,7 +2,7 @@
 
     python -m slayerpytorch_b200.opbench --op getSpikes --rows 262144 --T 300 --iters 5
 
-Operators: conv, corr, getSpikes, shift, shiftScalar, spikeGrad, delayGrad, loihi.  Prints one JSON line with
+Operators: conv, corr, getSpikes, shift, shiftScalar, spikeGrad, spikeGradShift, delayGrad, loihi.  Prints one JSON line with
 the average launch time, algorithmic GB/s (8 bytes per element for conv/corr/shift, 12 for
 getSpikes/spikeGrad, 16 for loihi) and elements per second.  Small enough to run under a
 profiler: every iteration is exactly one kernel launch of the operator (getSpikes works in
@@ -17,7 +17,7 @@ import torch
 import slayerpytorch_b200
 from slayerpytorch_b200.layer import alpha_kernel, loihi_psp_kernel
 
-ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "delayGrad": 8,
+ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "spikeGradShift": 12, "delayGrad": 8,
              "loihi": 16}
 
 
@@ -69,6 +69,10 @@ def main(argv=None):
     elif args.op == "spikeGrad":
         g = torch.randn(shape, device=dev, generator=gen)
         fn = lambda: sc.spikeGrad(g, a, 10.0, 10.0, 1.0)
+    elif args.op == "spikeGradShift":
+        g = torch.randn(shape, device=dev, generator=gen)
+        d = -(torch.rand(neurons, device=dev, generator=gen) * 5)
+        fn = lambda: sc.spikeGradShift(g, a, d, 10.0, 10.0, 1.0, 1.0)
     elif args.op == "delayGrad":
         g = torch.randn(shape, device=dev, generator=gen)
         fn = lambda: sc.delayGrad(g, a, 1.0)

@@ -82,3 +82,16 @@ def c_delay_grad(g, out, Ts):
     res = torch.full((max(nn, 1),), float("nan"), device=g.device, dtype=torch.float32)
     capi.call("slayer_b200_delay_grad", ptr(res), ptr(g), ptr(out), nb, nn, T, float(Ts), stream())
     return res[:nn]
+
+
+def c_spike_grad_shift(g, u, lut, theta, tau, scale, Ts, scalar=None):
+    out = torch.empty_like(g)
+    nb, T = g.shape[0], g.shape[-1]
+    rows = g.numel() // T if T else 0
+    if lut is None:
+        capi.call("slayer_b200_spike_grad_shift", ptr(out), ptr(g), ptr(u), None, float(scalar), rows, 1, T,
+                  float(Ts), float(theta), float(tau), float(scale), stream())
+    else:
+        capi.call("slayer_b200_spike_grad_shift", ptr(out), ptr(g), ptr(u), ptr(lut), 0.0, nb, rows // nb, T,
+                  float(Ts), float(theta), float(tau), float(scale), stream())
+    return out

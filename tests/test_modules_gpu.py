@@ -236,3 +236,35 @@ def test_operator_chain_replays_from_a_cuda_graph():
         torch.cuda.synchronize()
         for a, b in zip(outs, want):
             assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+
+
+@pytest.mark.parametrize("learnable", [True, False])
+def test_spike_delayed_matches_the_two_separate_nodes(learnable):
+    """spikeDelayed == delay(spike(u)) in outputs and in every gradient, bit for bit."""
+    net = _chain_layer()
+    g = torch.Generator().manual_seed(5)
+    x = ((torch.rand(6, 40, 1, 1, 300, generator=g) < 0.3).float() * 3).cuda()
+    up = torch.randn(6, 40, 1, 1, 300, generator=g).cuda()
+    if learnable:
+        dl_a, dl_b = net.delay(40).cuda(), net.delay(40).cuda()
+        with torch.no_grad():
+            dl_a.delay.copy_(torch.rand(40, 1, 1, generator=g) * 6)
+            dl_b.delay.copy_(dl_a.delay)
+    else:
+        fixed = (torch.rand(40, generator=g) * 6).cuda()
+
+    xa = x.clone().requires_grad_(True)
+    ua = net.psp(xa)
+    ya = dl_a(net.spike(ua)) if learnable else net.delayShift(net.spike(ua), fixed, 1.0)
+    ya.backward(up)
+
+    xb = x.clone().requires_grad_(True)
+    ub = net.psp(xb)
+    yb = net.spikeDelayed(ub, dl_b if learnable else fixed)
+    yb.backward(up)
+
+    assert 0.005 < ya.mean().item() < 0.5
+    assert torch.equal(ya, yb)
+    assert torch.equal(xa.grad.view(torch.int32), xb.grad.view(torch.int32))
+    if learnable:
+        assert torch.equal(dl_a.delay.grad, dl_b.delay.grad)

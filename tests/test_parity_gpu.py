@@ -146,7 +146,7 @@ def srm_case(rng, shape, nus, scale=8.0):
     return u, nu
 
 
-@pytest.mark.parametrize("T", [1, 2, 31, 32, 33, 300, 500, 2000])
+@pytest.mark.parametrize("T", [1, 2, 31, 32, 33, 64, 68, 100, 128, 132, 300, 500, 2000])
 @pytest.mark.parametrize("nus", [1, 2, 11, 33, 34, 65, 110, 160, 257])
 def test_srm_get_spikes_bit_exact(T, nus):
     rng = np.random.RandomState(T * 1000 + nus)
@@ -253,6 +253,42 @@ def test_spike_grad(n):
         th, ta, sc = (torch.tensor(v, device="cuda", dtype=torch.float32) for v in (theta, tau, scale))
         ref = gt * (sc / ta * torch.exp(-torch.abs(ut - th) / ta))
         np.testing.assert_allclose(got, ref.cpu().numpy(), rtol=REL, atol=1e-37)
+
+
+# ----------------------------------------------------------------------- spike_grad_shift
+@pytest.mark.parametrize("shape,Ts", [((1, 1, 1, 1, 1), 1.0), ((2, 3, 1, 1, 7), 1.0), ((5, 10, 4, 3, 500), 0.1),
+                                      ((3, 16, 1, 1, 300), 1.0), ((4, 8, 2, 1, 301), 0.5), ((2, 6, 1, 1, 1450), 1.0),
+                                      ((3, 5, 1, 1, 33), 2.0)])
+def test_spike_grad_shift_equals_shift_then_spike_grad(shape, Ts):
+    """The fused backward pass gives the bits of the two operators it replaces, and of the oracle."""
+    rng = np.random.RandomState(sum(shape) + 1)
+    n_neurons = int(np.prod(shape[1:-1]))
+    g = rng.randn(*shape).astype(np.float32)
+    u = (rng.randn(*shape) * 30).astype(np.float32)
+    lut = ((rng.rand(n_neurons) * 2 - 1) * min(shape[-1] + 2, 12) * Ts).astype(np.float32)
+    lut[0] = 0.0
+    gd, ud, ld = G.dev(g), G.dev(u), G.dev(lut)
+    for theta, tau, scale in ((10.0, 10.0, 1.0), (5120.0, 5120.0, 1 / 195.0)):
+        got = G.host(G.c_spike_grad_shift(gd, ud, ld, theta, tau, scale, Ts))
+        two = G.host(G.c_spike_grad(G.c_shift_lut(gd, ld, Ts), ud, theta, tau, scale))
+        assert_same_floats(got, two)
+        want = co.spike_grad(co.shift(g, lut, Ts), u, theta, tau, scale)
+        np.testing.assert_allclose(got, want, rtol=REL, atol=1e-37)
+        for sv in (0.0, 3.0 * Ts, -2.0 * Ts, 1e9):
+            got = G.host(G.c_spike_grad_shift(gd, ud, None, theta, tau, scale, Ts, scalar=sv))
+            two = G.host(G.c_spike_grad(G.c_shift_scalar(gd, sv, Ts), ud, theta, tau, scale))
+            assert_same_floats(got, two)
+
+
+def test_spike_grad_shift_unaligned_buffers():
+    rng = np.random.RandomState(77)
+    n = 3 * 4 * 300
+    g, u = rng.randn(n + 1).astype(np.float32), (rng.randn(n + 1) * 20).astype(np.float32)
+    lut = (rng.rand(4) * 6 - 3).astype(np.float32)
+    gd, ud = G.dev(g)[1:].view(3, 4, 300), G.dev(u)[1:].view(3, 4, 300)
+    got = G.host(G.c_spike_grad_shift(gd, ud, G.dev(lut), 10.0, 10.0, 1.0, 1.0))
+    want = co.spike_grad(co.shift(g[1:].reshape(3, 4, 300), lut, 1.0), u[1:].reshape(3, 4, 300), 10.0, 10.0, 1.0)
+    np.testing.assert_allclose(got, want, rtol=REL, atol=1e-37)
 
 
 # ---------------------------------------------------------------------------- delay_grad
