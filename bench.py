@@ -48,10 +48,11 @@ BATCH, N_IN, N_HID, N_OUT, T = 64, 2312, 512, 10, 300
 TGT_TRUE, TGT_FALSE = 60, 10
 
 # algorithmic bytes per neuron-timestep of each operator (read + write of fp32 tensors)
-ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12, "spikeGradShift": 12}
+ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12, "spikeGradShift": 12,
+             "getSpikesDelayed": 12}
 KERNEL_OF = {"conv": "fir_kernel", "corr": "fir_kernel", "getSpikes": "srm_get_spikes_tma_kernel",
              "shift": "shift_vec4_kernel", "spikeGrad": "spike_grad_vec4_kernel",
-             "spikeGradShift": "shift_vec4_kernel"}
+             "spikeGradShift": "spike_grad_shift_rows_kernel", "getSpikesDelayed": "srm_get_spikes_tma_kernel"}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count); see the summaries under profiles/.  None = not captured yet.
 NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_tma_kernel": 11.62,
@@ -158,8 +159,11 @@ def hot_path(ops, wl, record=None):
     run = record or (lambda name, big, fn: fn())
     # hidden layer: forward
     u1 = run("conv", True, lambda: ops.conv(wl["a1"], srm, Ts))
-    s1 = run("getSpikes", True, lambda: ops.getSpikes(u1, ref, theta, Ts))
-    d1 = run("shift", True, lambda: ops.shift(s1, delay, Ts))
+    if wl.get("unfused"):
+        s1 = run("getSpikes", True, lambda: ops.getSpikes(u1, ref, theta, Ts))
+        d1 = run("shift", True, lambda: ops.shift(s1, delay, Ts))
+    else:       # the spikes are written once, already delayed (same bits as the two launches)
+        d1 = run("getSpikesDelayed", True, lambda: ops.getSpikesDelayed(u1, ref, theta, Ts, delay))
     # hidden layer: backward
     if wl.get("unfused"):
         b1 = run("shift", True, lambda: ops.shift(wl["g1"], wl["neg_delay"], Ts))
@@ -177,7 +181,7 @@ def hot_path(ops, wl, record=None):
 
 
 def launches_per_step(wl):
-    return 10 if wl.get("unfused") else 9
+    return 10 if wl.get("unfused") else 8
 
 
 # ------------------------------------------------------------------------------ GPU clocks
@@ -405,9 +409,9 @@ def time_ours(args, rank, world, device):
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(wl),
-                   "backward": "hidden layer: shift back and surrogate gradient as two launches (reference sequence)"
-                               if args.unfused else
-                               "hidden layer: shift back and surrogate gradient fused into one launch (spikeGradShift)",
+                   "fusion": "none: the reference's sequence of ten launches" if args.unfused else
+                             "hidden layer: getSpikes+delay as one launch (getSpikesDelayed), shift back + surrogate "
+                             "gradient as one launch (spikeGradShift); same results, eight launches",
                    "neuron_timesteps_per_step_per_gpu": units, "l2": "flushed between steps (256 MiB write)",
                    "spike_rates": wl["rates"], "parallelism": "batch sharded, no collective"},
         "clocks": clocks,
@@ -459,6 +463,9 @@ def scaled_variant(ops, device, peak):
         u = run("conv", lambda: ops.conv(a, srm, Ts))
         s = run("getSpikes", lambda: ops.getSpikes(u, ref, theta, Ts))
         d = run("shift", lambda: ops.shift(s, delay, Ts))
+        u_again = ops.conv(a, srm, Ts)
+        df = run("getSpikesDelayed", lambda: ops.getSpikesDelayed(u_again, ref, theta, Ts, delay))
+        del u_again, df
         b1 = run("shift", lambda: ops.shift(g, neg_delay, Ts))
         b2 = run("spikeGrad", lambda: ops.spikeGrad(b1, u, theta, tau, scale))
         b2f = run("spikeGradShift", lambda: ops.spikeGradShift(g, u, neg_delay, theta, tau, scale, Ts))
@@ -474,15 +481,15 @@ def scaled_variant(ops, device, peak):
         t_of[name] = t
         gbs = ALG_BYTES[name] * el / (t * 1e-3) / 1e9
         res[name] = {"ms": round(t, 4), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4)}
-    # the chain as the benchmark step runs it: conv, getSpikes, shift, spikeGradShift, corr (48 bytes
-    # per element); the reference's sequence has one more shift and a separate spikeGrad (56 bytes)
-    total = t_of["conv"] + t_of["getSpikes"] + t_of["shift"] + t_of["spikeGradShift"] + t_of["corr"]
+    # the chain as the benchmark step runs it: conv, getSpikesDelayed, spikeGradShift, corr (40 bytes
+    # per element); the reference's sequence has two shifts and a separate spikeGrad (56 bytes)
+    total = t_of["conv"] + t_of["getSpikesDelayed"] + t_of["spikeGradShift"] + t_of["corr"]
     total_ref_seq = t_of["conv"] + t_of["getSpikes"] + 2 * t_of["shift"] + t_of["spikeGrad"] + t_of["corr"]
     return {"workload": "hidden-layer chain, batch %d (%d x %d fp32 = %.2f GiB per tensor)"
                         % (batch, batch * N_HID, T, el * 4 / 2 ** 30),
             "value": el / (total * 1e-3), "unit": UNIT, "ms_per_step": total,
-            "chain_GB/s": round(48 * el / (total * 1e-3) / 1e9, 1),
-            "chain_frac_of_hbm_peak": round(48 * el / (total * 1e-3) / 1e9 / peak, 4),
+            "chain_GB/s": round(40 * el / (total * 1e-3) / 1e9, 1),
+            "chain_frac_of_hbm_peak": round(40 * el / (total * 1e-3) / 1e9 / peak, 4),
             "reference_sequence_ms_per_step": total_ref_seq,
             "spike_rate": rate, "per_op": res}
 
@@ -594,8 +601,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--unfused", action="store_true",
-                    help="backward pass of the hidden layer as the reference's two operators (shift, then surrogate "
-                         "gradient) instead of the fused spikeGradShift")
+                    help="the reference's sequence of ten launches per step instead of the fused "
+                         "getSpikesDelayed / spikeGradShift operators")
     ap.add_argument("--no-graph", action="store_true", help="time the eager launch loop instead of a CUDA-graph replay")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the end-to-end host pipeline")
     ap.add_argument("--no-scaled", action="store_true", help="skip the batch-scaled (>= 1 GiB tensors) variant")

@@ -134,6 +134,22 @@ int slayer_b200_delay_grad(float *grad_delay, const float *grad_output, const fl
                            int64_t nBatch, int64_t nNeurons, int64_t T, float Ts, void *stream);
 
 /*
+ * SRM spike generation followed by an axonal delay, with the spikes written once, already
+ * delayed: delayed = shift(getSpikes(u), d), d_n = trunc(shift_n / Ts), shift_n = shift_lut[n]
+ * if shift_lut is not NULL (nNeurons values, rows are [nBatch, nNeurons]) else `shift`.  u is
+ * updated in place as by slayer_b200_srm_get_spikes.  Same bits as that call followed by
+ * slayer_b200_shift_lut / _scalar (getSpikes<float>, src/cuda/spikeKernels.h:54-60, then
+ * shift<float>, src/cuda/shiftKernels.h:63-136).  When T % 4 == 0, T <= 2048 and the buffers are
+ * 16-byte aligned the undelayed spikes never reach memory and s_scratch is not touched (it may
+ * be NULL); otherwise s_scratch (rows * T floats) receives them and the two steps run one after
+ * the other, or, if s_scratch is NULL, the call returns SLAYER_B200_EUNSUPPORTED.
+ */
+int slayer_b200_srm_get_spikes_delayed(float *delayed, float *s_scratch, float *u, const float *nu,
+                                       const float *shift_lut, float shift,
+                                       int64_t nBatch, int64_t nNeurons, int64_t nuSize, int64_t T,
+                                       float theta, float Ts, void *stream);
+
+/*
  * slayer_b200_srm_get_spikes without any memory allocation, for callers that cannot allocate
  * device memory: an application that has already given all device memory to its own pool, or
  * code that runs where entering the CUDA allocator is not allowed (another library's callback,

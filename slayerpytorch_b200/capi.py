@@ -28,6 +28,7 @@ SYMBOLS = {
     "slayer_b200_srm_get_spikes_noalloc": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_loihi_get_spikes": (_int, [_p, _p, _p, _p, _i64, _i64, _u32, _u32, _u32, _u32, _u32, _p]),
     "slayer_b200_spike_grad": (_int, [_p, _p, _p, _i64, _f, _f, _f, _p]),
+    "slayer_b200_srm_get_spikes_delayed": (_int, [_p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_spike_grad_shift": (_int, [_p, _p, _p, _p, _f, _i64, _i64, _i64, _f, _f, _f, _f, _p]),
     "slayer_b200_delay_grad": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "slayer_b200_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),

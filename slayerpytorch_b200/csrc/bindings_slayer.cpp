@@ -7,8 +7,8 @@
 //   - a one-element shift tensor is read on the device (no host synchronisation);
 //   - the per-neuron shift covers the whole batch in one launch;
 //   - dtype is checked explicitly;
-//   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift and
-//     delayGrad.
+//   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift,
+//     getSpikesDelayed and delayGrad.
 #include "bindings_common.h"
 
 using namespace sb200py;
@@ -28,6 +28,42 @@ static torch::Tensor getSpikesCuda(torch::Tensor d_u, const torch::Tensor &d_nu,
                                         rows, nuSize, Ns, theta, Ts, current_stream()),
              "getSpikes");
     return d_s;
+}
+
+// shift(getSpikes(d_u, d_nu, theta, Ts), delayLUT, Ts) with the spikes written once, already
+// delayed; d_u is updated in place like getSpikes does.  delayLUT: one value per neuron or a
+// single value.  Sizes the fused kernel does not take run as the two operators.
+static torch::Tensor getSpikesDelayedCuda(torch::Tensor d_u, const torch::Tensor &d_nu, const float theta, const float Ts,
+                                          torch::Tensor delayLUT)
+{
+    check_input(d_u, "d_u");
+    check_input(d_nu, "d_nu");
+    check_input(delayLUT, "delayLUT");
+    check_device(d_u, d_nu, "d_u", "d_nu");
+    check_device(d_u, delayLUT, "d_u", "delayLUT");
+    TORCH_CHECK_INDEX(d_u.dim() >= 4, "getSpikesDelayed expects a tensor with at least 4 dimensions (NCHWT), got ", d_u.dim());
+    c10::cuda::CUDAGuard guard(d_u.device());
+    auto delayed = torch::empty_like(d_u);
+    const int64_t Ns = d_u.size(-1);
+    const int64_t rows = Ns ? d_u.numel() / Ns : 0;
+    const int64_t nuSize = d_nu.dim() ? d_nu.size(-1) : 1;
+    int64_t nBatch = rows, nNeurons = 1;
+    if (delayLUT.numel() != 1) {
+        nBatch = d_u.size(0);
+        nNeurons = nBatch ? rows / nBatch : 0;
+        TORCH_CHECK(delayLUT.numel() == nNeurons, "shift and number of neurons must be same");
+    }
+    int rc = slayer_b200_srm_get_spikes_delayed(delayed.data_ptr<float>(), nullptr, d_u.data_ptr<float>(),
+                                                d_nu.data_ptr<float>(), delayLUT.data_ptr<float>(), 0.0f,
+                                                nBatch, nNeurons, nuSize, Ns, theta, Ts, current_stream());
+    if (rc == SLAYER_B200_EUNSUPPORTED) {
+        auto scratch = torch::empty_like(d_u);
+        rc = slayer_b200_srm_get_spikes_delayed(delayed.data_ptr<float>(), scratch.data_ptr<float>(), d_u.data_ptr<float>(),
+                                                d_nu.data_ptr<float>(), delayLUT.data_ptr<float>(), 0.0f,
+                                                nBatch, nNeurons, nuSize, Ns, theta, Ts, current_stream());
+    }
+    check_rc(rc, "getSpikesDelayed");
+    return delayed;
 }
 
 static torch::Tensor convCuda(torch::Tensor input, torch::Tensor filter, float Ts)
@@ -187,6 +223,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("shift", &shift1Cuda, "Element shift in time (CUDA)");
     m.def("shift", &shiftFlCuda, "Element shift in time (CUDA)");
     m.def("shift", &shiftFl1Cuda, "Element shift in time (CUDA)");
+    m.def("getSpikesDelayed", &getSpikesDelayedCuda, "Get spikes, written once and already delayed (CUDA)");
     m.def("spikeGrad", &spikeGradCuda,
           "gradOutput * scale/tau * exp(-|u - theta| / tau) in one pass (CUDA)");
     m.def("spikeGrad_", &spikeGradInplaceCuda, "In-place variant of spikeGrad (overwrites gradOutput)");

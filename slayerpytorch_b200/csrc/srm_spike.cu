@@ -420,11 +420,23 @@ constexpr int kMaxUStages = 8;
 constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier before giving up
 
 // dynamic shared memory of a launch with `warps` warps per CTA and `ustages` stages per warp
-static inline size_t srm_tma_smem(int warps, int ustages, int nuEff, bool taps_in_smem)
+// mask_tiles: wide tiles whose spike bits a warp keeps (1, or all tiles of a row for the
+// delayed-output variant)
+static inline size_t srm_tma_smem(int warps, int ustages, int nuEff, bool taps_in_smem, int mask_tiles = 1)
 {
-    return 1024 + (size_t)warps * ((size_t)ustages * kStageBytes + 2 * kTile * sizeof(unsigned) + ustages * sizeof(uint64_t))
+    return 1024 + (size_t)warps * ((size_t)ustages * kStageBytes + (size_t)mask_tiles * 2 * kTile * sizeof(unsigned)
+                                   + ustages * sizeof(uint64_t))
          + (taps_in_smem ? (size_t)((nuEff + 3) & ~3) * sizeof(float) : 0);
 }
+
+// What the delayed-output variant needs to know about the delay that follows the spikes.
+struct DelayArgs {
+    float *out;                 // delayed spikes
+    const float *lut;           // one delay per neuron, or NULL
+    float shift;                // the delay of every row when lut is NULL
+    float Ts;
+    int64_t nNeurons;
+};
 
 // Potentials of an unskewed wide tile starting at time t0 (T % 4 == 0).
 __device__ __forceinline__ void wide_store(const float *tile, float *g, int64_t row0, int64_t rows,
@@ -470,15 +482,53 @@ __device__ __forceinline__ void wide_store_spikes(const unsigned *masks, float *
     }
 }
 
+// Delayed spike samples of a block of 32 rows from the spike bits of the whole rows:
+// out[r, t] = value if row r spiked at t - d_r (0 <= t - d_r < T), else 0.  masks is word-major
+// ([word][row], nwords words per row, bits past T clear); lane l holds d of row l.
+__device__ __forceinline__ void store_delayed_spikes(const unsigned *masks, int nwords, float *g, int64_t row0,
+                                                     int64_t rows, int T, int lane, int d_lane, float value)
+{
+    const int c16 = lane & 15;
+    const int rsub = lane >> 4;
+    const int64_t nrow = rows - row0;
+    const int T4 = T >> 2;
+    for (int q0 = 0; q0 < T4; q0 += 16) {
+        const int q = q0 + c16;
+#pragma unroll 4
+        for (int i = 0; i < kTile / 2; ++i) {
+            const int r = i * 2 + rsub;
+            const int d = __shfl_sync(0xffffffffu, d_lane, r);
+            if (q >= T4 || r >= nrow) continue;
+            const int64_t src = (int64_t)4 * q - d;              // time of the first source sample
+            unsigned m = 0u;
+            if (src > -4 && src < T) {
+                const int w = (int)(src >> 5), off = (int)(src & 31);
+                const unsigned lo = (w >= 0 && w < nwords) ? masks[w * kTile + r] : 0u;
+                const unsigned hi = (w + 1 >= 0 && w + 1 < nwords) ? masks[(w + 1) * kTile + r] : 0u;
+                m = __funnelshift_r(lo, hi, off);
+            }
+            *reinterpret_cast<float4 *>(g + (row0 + r) * (int64_t)T + 4 * q) =
+                make_float4((m & 1u) ? value : 0.0f, (m & 2u) ? value : 0.0f,
+                            (m & 4u) ? value : 0.0f, (m & 8u) ? value : 0.0f);
+        }
+    }
+}
+
 // PER_BLOCK selects where a wait that ran out is recorded: false = the single status word of
 // the device (`status` points to one int); true = one int per block of 32 rows (`status` points
 // to an array with an entry for every row block), which the warp clears when it starts the
 // block and sets to the number of tiles walked when it finishes it.
-template <int NB, int W, bool PER_BLOCK = false>
+//
+// DELAYED: the spikes are not written where they occur but shifted by a per-row delay, which is
+// what an axonal delay right after the spike function does (out[t] = s[t - d], zero filled).
+// The warp keeps the spike bits of the whole row (T / 32 words per row) in shared memory and
+// writes the shifted samples when it has walked the row, so any delay - positive, negative,
+// beyond the row - costs the same and the undelayed spikes never reach global memory.
+template <int NB, int W, bool PER_BLOCK = false, bool DELAYED = false>
 __global__ void __launch_bounds__(256)
 srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__restrict__ s, float *u,
                           const float *__restrict__ nu, int64_t rows, int nuEff, int T,
-                          float theta, float spikeVal, int *status, int ustages)
+                          float theta, float spikeVal, int *status, int ustages, DelayArgs da)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -488,11 +538,13 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
     unsigned char *base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     float *u_tiles = reinterpret_cast<float *>(base) + (size_t)warp * ustages * kWideWords;
     unsigned char *after_tiles = base + (size_t)warps_per_block * ustages * kStageBytes;
-    unsigned *masks = reinterpret_cast<unsigned *>(after_tiles) + warp * 2 * kTile;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(after_tiles + warps_per_block * 2 * kTile * sizeof(unsigned))
+    const int ntiles = (T + kWide - 1) / kWide;
+    const int mask_words = (DELAYED ? ntiles : 1) * 2 * kTile;       // per warp; word-major: [word][row]
+    unsigned *masks = reinterpret_cast<unsigned *>(after_tiles) + warp * mask_words;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after_tiles + warps_per_block * mask_words * sizeof(unsigned))
                      + warp * ustages;
     float *nu_s = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(
-                      after_tiles + warps_per_block * 2 * kTile * sizeof(unsigned)) + warps_per_block * ustages);
+                      after_tiles + warps_per_block * mask_words * sizeof(unsigned)) + warps_per_block * ustages);
 
     if (NB == 0) {
         for (int i = threadIdx.x; i < nuEff; i += blockDim.x) nu_s[i] = nu[i];
@@ -512,13 +564,13 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
     // The warp's work is one stream of wide tiles: all of its first block of 32 rows, then of
     // its next block, ...  Loads run ustages - 1 tiles ahead of the walk across row-block
     // boundaries, so a change of row block costs no memory latency.
-    const int ntiles = (T + kWide - 1) / kWide;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
     int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
     int64_t rb_next = rb;           // (row block, tile) of the next tile to load
     int j_next = 0;
     int sg_next = 0;                // stage the next load goes to
+    int delay_steps = 0;            // DELAYED: the delay of this lane's row, in steps
     auto issue_load = [&]() {       // lane 0 only
         const bool two = kWide * j_next + kBoxT < T;           // the second box starts inside the rows
         float *dst = u_tiles + sg_next * kWideWords;
@@ -541,6 +593,10 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
             st.reset();
             ring_reset(ring);
             if (PER_BLOCK && lane == 0) status[rb] = 0;
+            if (DELAYED) {
+                const int64_t row = rb * kTile + lane;
+                delay_steps = shift_steps(da.lut ? __ldg(da.lut + (row % da.nNeurons)) : da.shift, da.Ts);
+            }
         }
         // the stage walked before this one was drained (and fenced) at the end of its iteration
         if (lane == 0 && rb_next < nblocks) issue_load();
@@ -563,11 +619,22 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
             if (h == 0) m[0] = mh;
             else m[1] = mh;
         }
-        masks[lane] = m[0];
-        masks[kTile + lane] = m[1];
+        if (DELAYED) {
+            // keep the bits of the whole row; bits of steps past the row end must read as zero
+            const int left = T - kWide * j;                  // > 0
+            if (left < kTile) m[0] &= (1u << left) - 1u;
+            if (left < kWide) m[1] &= left > kTile ? (1u << (left - kTile)) - 1u : 0u;
+            masks[(2 * j) * kTile + lane] = m[0];
+            masks[(2 * j + 1) * kTile + lane] = m[1];
+        } else {
+            masks[lane] = m[0];
+            masks[kTile + lane] = m[1];
+        }
         __syncwarp();
         wide_store(tile, u, rb * kTile, rows, kWide * j, T, lane);
-        wide_store_spikes(masks, s, rb * kTile, rows, kWide * j, T, lane, spikeVal);
+        if (!DELAYED) wide_store_spikes(masks, s, rb * kTile, rows, kWide * j, T, lane, spikeVal);
+        if (DELAYED && j == ntiles - 1)
+            store_delayed_spikes(masks, 2 * ntiles, da.out, rb * kTile, rows, T, lane, delay_steps, spikeVal);
         // the reads of this stage (and of the masks) precede the bulk load that refills it
         fence_proxy_async();
         __syncwarp();
@@ -637,7 +704,7 @@ static int launch_srm(const SrmArgs &a)
             int rc = reserve_dynamic_smem((const void *)kern, smem);
             if (rc) return rc;
             kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
-                                                                 a.spikeVal, status, ustages);
+                                                                 a.spikeVal, status, ustages, DelayArgs{});
             return check_launch("srm_get_spikes (bulk tensor copy) kernel launch");
         }
     }
@@ -686,6 +753,57 @@ static int dispatch_srm(const SrmArgs &a)
     if (window <= 64) return launch_srm<V, 0, 2>(a);
     if (window <= 128) return launch_srm<V, 0, 4>(a);
     return launch_srm<V, 0, 8>(a);
+}
+
+// Spikes written already delayed (slayer_b200_srm_get_spikes_delayed): the bulk-tensor kernel
+// with the spike bits of whole rows kept in shared memory.  Needs what that kernel needs
+// (T % 4 == 0, 16-byte aligned buffers) and rows short enough for the bits to fit.
+constexpr int kDelayedMaxTiles = 32;            // T <= 2048
+
+template <int NB, int W>
+static int launch_srm_delayed(const SrmArgs &a, const DelayArgs &da)
+{
+    const int64_t nblocks = ceil_div(a.rows, kTile);
+    const int ntiles = (int)ceil_div((int64_t)a.T, (int64_t)kWide);
+    CUtensorMap map_u;
+    int *status = device_status_word();
+    if (!status || a.rows * (int64_t)kTile >= (1LL << 31) ||
+        !encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        set_error("srm_get_spikes_delayed: cannot describe the buffers for bulk tensor copies");
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    const int sms = sm_count();
+    const size_t mask_bytes = (size_t)ntiles * 2 * kTile * sizeof(unsigned);
+    const int64_t warps_per_sm = ceil_div(nblocks, (int64_t)sms);
+    int ustages = (int)(((208 * 1024) / warps_per_sm - (int64_t)mask_bytes) / kStageBytes);
+    if (ustages > kMaxUStages) ustages = kMaxUStages;
+    if (ustages < kUStages) ustages = kUStages;
+    int warps, grid;
+    spike_launch_shape(nblocks, (size_t)ustages * kStageBytes + mask_bytes + 256, warps, grid);
+    const size_t smem = srm_tma_smem(warps, ustages, a.nuEff, NB == 0, ntiles);
+    auto kern = srm_get_spikes_tma_kernel<NB, W, false, true>;
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
+    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, nullptr, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
+                                                         a.spikeVal, status, ustages, da);
+    return check_launch("srm_get_spikes_delayed kernel launch");
+}
+
+static int dispatch_srm_delayed(const SrmArgs &a, const DelayArgs &da)
+{
+    const int window = a.nuEff > 1 ? a.nuEff - 1 : 0;     // history bits needed
+    if (window <= 2) return launch_srm_delayed<2, 1>(a, da);
+    if (window <= 4) return launch_srm_delayed<4, 1>(a, da);
+    if (window <= 6) return launch_srm_delayed<6, 1>(a, da);
+    if (window <= 8) return launch_srm_delayed<8, 1>(a, da);
+    if (window <= 10) return launch_srm_delayed<10, 1>(a, da);
+    if (window <= 12) return launch_srm_delayed<12, 1>(a, da);
+    if (window <= 16) return launch_srm_delayed<16, 1>(a, da);
+    if (window <= 24) return launch_srm_delayed<24, 1>(a, da);
+    if (window <= 32) return launch_srm_delayed<32, 1>(a, da);
+    if (window <= 64) return launch_srm_delayed<0, 2>(a, da);
+    if (window <= 128) return launch_srm_delayed<0, 4>(a, da);
+    return launch_srm_delayed<0, 8>(a, da);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -739,7 +857,7 @@ static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev, int slot)
         dev.smem_set[slot] = true;
     }
     kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
-                                                         a.spikeVal, dev.scratch, kUStages);
+                                                         a.spikeVal, dev.scratch, kUStages, DelayArgs{});
     return check_launch("srm_get_spikes_noalloc kernel launch");
 }
 
@@ -832,4 +950,42 @@ extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
         case 2: return dispatch_srm<2>(a);
         default: return dispatch_srm<1>(a);
     }
+}
+
+extern "C" int slayer_b200_shift_lut(float *out, const float *in, const float *lut,
+                                     int64_t nBatch, int64_t nNeurons, int64_t T, float Ts, void *stream);
+extern "C" int slayer_b200_shift_scalar(float *out, const float *in, float shift,
+                                        int64_t rows, int64_t T, float Ts, void *stream);
+
+extern "C" int slayer_b200_srm_get_spikes_delayed(float *delayed, float *s_scratch, float *u, const float *nu,
+                                                  const float *shift_lut, float shift,
+                                                  int64_t nBatch, int64_t nNeurons, int64_t nuSize, int64_t T,
+                                                  float theta, float Ts, void *stream_)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(nBatch >= 0 && nNeurons >= 0 && nuSize >= 0 && T >= 0, "srm_get_spikes_delayed: negative size");
+    SB200_REQUIRE(T < (1LL << 31) - 64, "srm_get_spikes_delayed: T=%lld too large", (long long)T);
+    const int64_t rows = nBatch * nNeurons;
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    SB200_REQUIRE(delayed && u && (nu || nuSize == 0), "srm_get_spikes_delayed: null pointer");
+    SB200_REQUIRE(delayed != u && s_scratch != u && s_scratch != delayed, "srm_get_spikes_delayed: buffers must not alias");
+    const int64_t nuEff = nuSize < T ? nuSize : T;
+    const bool fused = tma_enabled() && (T & 3) == 0 && aligned16(delayed) && aligned16(u) &&
+                       nuEff - 1 <= 32 * kMaxHistWords && ceil_div(T, (int64_t)kWide) <= kDelayedMaxTiles;
+    if (fused) {
+        const SrmArgs a = {nullptr, u, nu, rows, (int)nuEff, (int)T, theta, 1.0f / Ts, (cudaStream_t)stream_, true};
+        const DelayArgs da = {delayed, shift_lut, shift, Ts, shift_lut ? nNeurons : 1};
+        const int rc = dispatch_srm_delayed(a, da);
+        if (rc != SLAYER_B200_EUNSUPPORTED) return rc;
+    }
+    if (!s_scratch) {
+        set_error("srm_get_spikes_delayed: these sizes need a scratch buffer for the undelayed spikes "
+                  "(fused path: T %% 4 == 0, T <= %d, 16-byte aligned buffers)", kDelayedMaxTiles * kWide);
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    int rc = slayer_b200_srm_get_spikes(s_scratch, u, nu, rows, nuSize, T, theta, Ts, stream_);
+    if (rc) return rc;
+    if (shift_lut) return slayer_b200_shift_lut(delayed, s_scratch, shift_lut, nBatch, nNeurons, T, Ts, stream_);
+    return slayer_b200_shift_scalar(delayed, s_scratch, shift, rows, T, Ts, stream_);
 }

@@ -129,7 +129,7 @@ class _DelayFunction(torch.autograd.Function):
 class _SpikeDelayFunction(torch.autograd.Function):
     """Spike generation followed by a per-neuron (or uniform) delay as one autograd node.
 
-    Forward is ``shift(getSpikes(u), delay)`` on the two operators; backward is one fused pass
+    Forward is ``getSpikesDelayed`` (the spikes are written once, already delayed); backward is one fused pass
     ``spikeGradShift`` (shifted gradient times surrogate gradient, src/slayer.py:957 and :862
     combined) plus, when the delay is learnable, the fused delay gradient.  Results equal those
     of ``_SpikeFunction`` followed by ``_DelayFunction`` / ``_DelayShiftFunction`` bit for bit."""
@@ -138,9 +138,8 @@ class _SpikeDelayFunction(torch.autograd.Function):
     def forward(ctx, u, refKernel, neuron, Ts, delay):
         u = u.contiguous()
         Ts = float(Ts)
-        spikes = slayerCuda.getSpikes(u, refKernel, neuron['theta'], Ts)
-        d = delay.detach()
-        out = slayerCuda.shift(spikes, d, Ts)
+        d = delay.detach().contiguous()
+        out = slayerCuda.getSpikesDelayed(u, refKernel, neuron['theta'], Ts, d)
         ctx.learn_delay = bool(delay.requires_grad)
         ctx.delay_shape = delay.shape
         ctx.save_for_backward(u, d, out if ctx.learn_delay else d)

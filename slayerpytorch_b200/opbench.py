@@ -2,7 +2,8 @@
 
     python -m slayerpytorch_b200.opbench --op getSpikes --rows 262144 --T 300 --iters 5
 
-Operators: conv, corr, getSpikes, shift, shiftScalar, spikeGrad, spikeGradShift, delayGrad, loihi.  Prints one JSON line with
+Operators: conv, corr, getSpikes, getSpikesDelayed, shift, shiftScalar, spikeGrad, spikeGradShift,
+delayGrad, loihi.  Prints one JSON line with
 the average launch time, algorithmic GB/s (8 bytes per element for conv/corr/shift, 12 for
 getSpikes/spikeGrad, 16 for loihi) and elements per second.  Small enough to run under a
 profiler: every iteration is exactly one kernel launch of the operator (getSpikes works in
@@ -18,6 +19,7 @@ import slayerpytorch_b200
 from slayerpytorch_b200.layer import alpha_kernel, loihi_psp_kernel
 
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "spikeGradShift": 12, "delayGrad": 8,
+             "getSpikesDelayed": 12,
              "loihi": 16}
 
 
@@ -61,6 +63,12 @@ def main(argv=None):
         u = torch.empty_like(u0)
         restore = lambda: u.copy_(u0)
         fn = lambda: sc.getSpikes(u, ref, 10.0, 1.0)
+    elif args.op == "getSpikesDelayed":
+        u0 = sc.conv(a, srm, 1.0)
+        u = torch.empty_like(u0)
+        restore = lambda: u.copy_(u0)
+        dl = torch.rand(neurons, device=dev, generator=gen) * 5
+        fn = lambda: sc.getSpikesDelayed(u, ref, 10.0, 1.0, dl)
     elif args.op == "shift":
         d = torch.rand(neurons, device=dev, generator=gen) * 5
         fn = lambda: sc.shift(a, d, 1.0)
@@ -93,7 +101,7 @@ def main(argv=None):
         torch.cuda.synchronize()
         if it >= args.warmup:
             times.append(e0.elapsed_time(e1))
-    if args.op == "getSpikes":
+    if args.op in ("getSpikes", "getSpikesDelayed"):
         extra["spike_rate"] = float(out.mean())
     if args.op == "loihi":
         extra["spike_rate"] = float(out[0].mean())

@@ -95,3 +95,18 @@ def c_spike_grad_shift(g, u, lut, theta, tau, scale, Ts, scalar=None):
         capi.call("slayer_b200_spike_grad_shift", ptr(out), ptr(g), ptr(u), ptr(lut), 0.0, nb, rows // nb, T,
                   float(Ts), float(theta), float(tau), float(scale), stream())
     return out
+
+
+def c_srm_delayed(u, nu, lut, theta, Ts, scalar=None, scratch=False):
+    """In place on u; returns the delayed spikes.  scratch=True passes a buffer for the unfused path."""
+    d = torch.full_like(u, float("nan"))
+    sc = torch.empty_like(u) if scratch else None
+    nb, T = u.shape[0], u.shape[-1]
+    rows = u.numel() // T if T else 0
+    if lut is None:
+        capi.call("slayer_b200_srm_get_spikes_delayed", ptr(d), ptr(sc) if scratch else None, ptr(u), ptr(nu), None,
+                  float(scalar), rows, 1, nu.numel(), T, float(theta), float(Ts), stream())
+    else:
+        capi.call("slayer_b200_srm_get_spikes_delayed", ptr(d), ptr(sc) if scratch else None, ptr(u), ptr(nu), ptr(lut),
+                  0.0, nb, rows // nb, nu.numel(), T, float(theta), float(Ts), stream())
+    return d

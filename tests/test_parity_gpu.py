@@ -255,6 +255,66 @@ def test_spike_grad(n):
         np.testing.assert_allclose(got, ref.cpu().numpy(), rtol=REL, atol=1e-37)
 
 
+# ------------------------------------------------------------------- srm_get_spikes_delayed
+@pytest.mark.parametrize("T", [4, 32, 36, 64, 100, 128, 300, 500, 2000, 2048])
+@pytest.mark.parametrize("nus", [1, 11, 34, 110])
+def test_srm_delayed_equals_get_spikes_then_shift(T, nus):
+    """Spikes written once, already delayed: the bits of getSpikes followed by shift."""
+    rng = np.random.RandomState(T * 7 + nus)
+    shape = (3, 5, 2, 1, T)
+    u0, nu = srm_case(rng, shape, nus)
+    n_neurons = 10
+    Ts = 0.5
+    lut = ((rng.rand(n_neurons) * 2 - 1) * min(T + 3, 70) * Ts).astype(np.float32)
+    lut[0], lut[1], lut[2], lut[3] = 0.0, 3.0 * Ts, -2.0 * Ts, 1e6
+    nud, ld = G.dev(nu), G.dev(lut)
+    ua = G.dev(u0)
+    want_s = G.c_srm(ua, nud, 10.0, Ts)
+    want_d = G.host(G.c_shift_lut(want_s, ld, Ts))
+    assert want_d.any() or T < 8
+    ub = G.dev(u0)
+    got_d = G.host(G.c_srm_delayed(ub, nud, ld, 10.0, Ts))
+    np.testing.assert_array_equal(got_d, want_d)
+    assert_same_floats(G.host(ub), G.host(ua))
+    # oracle
+    s_o, u_o = co.srm_get_spikes(u0, nu, 10.0, Ts)
+    np.testing.assert_array_equal(got_d, co.shift(s_o, lut, Ts))
+    # one delay for every row
+    for sv in (0.0, 2.0 * Ts, -5.0 * Ts, -1e9):
+        uc = G.dev(u0)
+        got = G.host(G.c_srm_delayed(uc, nud, None, 10.0, Ts, scalar=sv))
+        np.testing.assert_array_equal(got, G.host(G.c_shift_scalar(want_s, sv, Ts)))
+
+
+def test_srm_delayed_rows_not_a_multiple_of_32_and_positive_theta_padding():
+    rng = np.random.RandomState(99)
+    shape = (7, 9, 1, 1, 300)                     # 63 rows
+    u0, nu = srm_case(rng, shape, 11)
+    lut = (rng.rand(9) * 8 - 2).astype(np.float32)
+    for theta in (10.0, -1.0):                    # theta < 0: the zero padding past the row end would spike
+        ua, ub = G.dev(u0), G.dev(u0)
+        want = G.host(G.c_shift_lut(G.c_srm(ua, G.dev(nu), theta, 1.0), G.dev(lut), 1.0))
+        got = G.host(G.c_srm_delayed(ub, G.dev(nu), G.dev(lut), theta, 1.0))
+        np.testing.assert_array_equal(got, want)
+        assert_same_floats(G.host(ub), G.host(ua))
+
+
+@pytest.mark.parametrize("T", [1, 7, 301, 1450, 2052])
+def test_srm_delayed_sizes_outside_the_fused_path(T):
+    """T % 4 != 0 or T > 2048: needs the scratch buffer, then runs as the two operators."""
+    from slayerpytorch_b200.capi import SlayerB200Error
+    rng = np.random.RandomState(T)
+    shape = (2, 6, 1, 1, T)
+    u0, nu = srm_case(rng, shape, 11)
+    lut = (rng.rand(6) * 8 - 2).astype(np.float32)
+    ua, ub = G.dev(u0), G.dev(u0)
+    want = G.host(G.c_shift_lut(G.c_srm(ua, G.dev(nu), 10.0, 1.0), G.dev(lut), 1.0))
+    got = G.host(G.c_srm_delayed(ub, G.dev(nu), G.dev(lut), 10.0, 1.0, scratch=True))
+    np.testing.assert_array_equal(got, want)
+    with pytest.raises(SlayerB200Error):
+        G.c_srm_delayed(G.dev(u0), G.dev(nu), G.dev(lut), 10.0, 1.0, scratch=False)
+
+
 # ----------------------------------------------------------------------- spike_grad_shift
 @pytest.mark.parametrize("shape,Ts", [((1, 1, 1, 1, 1), 1.0), ((2, 3, 1, 1, 7), 1.0), ((5, 10, 4, 3, 500), 0.1),
                                       ((3, 16, 1, 1, 300), 1.0), ((4, 8, 2, 1, 301), 0.5), ((2, 6, 1, 1, 1450), 1.0),
