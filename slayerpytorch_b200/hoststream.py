@@ -9,10 +9,16 @@ can be cut into chunks and the three phases of consecutive chunks overlapped::
     compute stream:        step(0) step(1) step(2) ...
     return stream :               D2H(0)  D2H(1)  D2H(2) ...
 
-``HostPipeline`` does exactly that with three CUDA streams, two sets of device staging buffers
+``HostPipeline`` does exactly that with three CUDA streams, three sets of device staging buffers
 and events between the phases; there is no host-side synchronisation inside ``run``.  Results
 are the same as those of one call on the whole batch, because every operator treats rows
 independently (per-neuron tables are indexed inside a sample, and chunks hold whole samples).
+
+Every copy over PCIe costs some tens of microseconds of set-up whatever its size, so tensors
+whose chunks are small (below ``small_bytes`` per chunk, e.g. the ten output neurons of a
+classifier next to its hidden layers) do not travel chunk by chunk: a small input crosses once
+for the whole batch before the first chunk and is sliced on the device, a small output is
+gathered on the device and crosses once after the last chunk.
 
 A chunk's step is a handful of short kernels, so issuing them call by call can cost the host
 more time than the copies take.  With ``capture=True`` the step is captured once per staging
@@ -48,7 +54,7 @@ class HostPipeline:
     should be pinned: copies from pageable memory are staged by the driver and do not overlap.
     """
 
-    def __init__(self, device, chunks=8, capture=False):
+    def __init__(self, device, chunks=8, capture=False, slots=3, small_bytes=256 * 1024):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("HostPipeline needs a CUDA device: the operators have no CPU path")
@@ -57,6 +63,9 @@ class HostPipeline:
         self.compute_stream = torch.cuda.Stream(self.device)
         self.return_stream = torch.cuda.Stream(self.device)
         self.capture = bool(capture)
+        self.slots = max(2, int(slots))      # sets of device staging buffers (and captured graphs)
+        self.small_bytes = int(small_bytes)
+        self._whole = {}                      # device copies of whole small tensors, by (role, index, shape)
         self._slots = None
         self._slot_key = None
         self._graphs = None            # per slot: (graph, static outputs), for the step in _graph_step
@@ -66,7 +75,7 @@ class HostPipeline:
         key = tuple((tuple(t.shape[1:]), t.dtype) for t in host_inputs) + (rows,)
         if self._slot_key != key:
             self._slots = [[torch.empty((rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=self.device)
-                            for t in host_inputs] for _ in range(2)]
+                            for t in host_inputs] for _ in range(self.slots)]
             self._slot_key = key
             self._graphs = None
         return self._slots
@@ -102,24 +111,53 @@ class HostPipeline:
         caller = torch.cuda.current_stream(self.device)
         slots = self._staging(host_inputs, rows)
         graphs = self._captured(step, slots) if self.capture else None
-        returned = [None, None]            # recorded on the return stream when a slot's outputs are copied
+
+        def chunk_bytes(t):
+            return rows * (t.numel() // batch) * t.element_size()
+
+        def whole(role, idx, t):           # persistent device buffer for a whole small tensor
+            key = (role, idx, tuple(t.shape), t.dtype)
+            if key not in self._whole:
+                self._whole[key] = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+            return self._whole[key]
+
+        many = len(bounds) > 1
+        small_in = [many and chunk_bytes(t) < self.small_bytes for t in host_inputs]
+        small_out = [many and chunk_bytes(t) < self.small_bytes for t in host_outputs]
+        whole_in = [whole("in", i, t) if sm else None for i, (t, sm) in enumerate(zip(host_inputs, small_in))]
+        whole_out = [whole("out", i, t) if sm else None for i, (t, sm) in enumerate(zip(host_outputs, small_out))]
+
         start = torch.cuda.Event()
         start.record(caller)
         for s in (self.copy_stream, self.compute_stream, self.return_stream):
             s.wait_event(start)
-        slot_free = [None, None]           # recorded on the compute stream when a slot's step is enqueued
+        small_ready = None
+        if any(small_in):
+            with torch.cuda.stream(self.copy_stream):
+                for w, h in zip(whole_in, host_inputs):
+                    if w is not None:
+                        w.copy_(h, non_blocking=True)
+                small_ready = torch.cuda.Event()
+                small_ready.record(self.copy_stream)
+            self.compute_stream.wait_event(small_ready)
+        returned = [None] * self.slots     # recorded on the return stream when a slot's outputs are copied
+        slot_free = [None] * self.slots    # recorded on the compute stream when a slot's step is enqueued
         for i, (a, b) in enumerate(bounds):
-            k = i & 1
+            k = i % self.slots
+            dev_in = [buf[:b - a] for buf in slots[k]]
             with torch.cuda.stream(self.copy_stream):
                 if slot_free[k] is not None:
                     self.copy_stream.wait_event(slot_free[k])
-                dev_in = [buf[:b - a] for buf in slots[k]]
-                for buf, h in zip(dev_in, host_inputs):
-                    buf.copy_(h[a:b], non_blocking=True)
+                for buf, h, sm in zip(dev_in, host_inputs, small_in):
+                    if not sm:
+                        buf.copy_(h[a:b], non_blocking=True)
                 ready = torch.cuda.Event()
                 ready.record(self.copy_stream)
             with torch.cuda.stream(self.compute_stream):
                 self.compute_stream.wait_event(ready)
+                for buf, w in zip(dev_in, whole_in):
+                    if w is not None:
+                        buf.copy_(w[a:b], non_blocking=True)          # device to device
                 replay = graphs is not None and b - a == rows
                 if replay:
                     if returned[k] is not None:              # the graph writes the same output buffers again
@@ -132,21 +170,33 @@ class HostPipeline:
                         outs = (outs,)
                 if len(outs) != len(host_outputs):
                     raise ValueError("step returned %d tensors for %d host outputs" % (len(outs), len(host_outputs)))
+                for o, w in zip(outs, whole_out):
+                    if w is not None:
+                        w[a:b].copy_(o[:b - a], non_blocking=True)    # gathered on the device
                 done = torch.cuda.Event()
                 done.record(self.compute_stream)
                 slot_free[k] = done
             with torch.cuda.stream(self.return_stream):
                 self.return_stream.wait_event(done)
-                for o, h in zip(outs, host_outputs):
+                for o, h, sm in zip(outs, host_outputs, small_out):
+                    if sm:
+                        continue
                     if not replay:
                         o.record_stream(self.return_stream)  # keeps the allocator from reusing it early
                     h[a:b].copy_(o[:b - a], non_blocking=True)
                 if replay:
                     returned[k] = torch.cuda.Event()
                     returned[k].record(self.return_stream)
+        with torch.cuda.stream(self.return_stream):         # `done` of the last chunk has been waited for
+            for w, h in zip(whole_out, host_outputs):
+                if w is not None:
+                    h.copy_(w, non_blocking=True)
         finished = torch.cuda.Event()
         finished.record(self.return_stream)
         caller.wait_event(finished)
         tail = torch.cuda.Event()
         tail.record(self.compute_stream)
         caller.wait_event(tail)
+        tail_copy = torch.cuda.Event()
+        tail_copy.record(self.copy_stream)
+        caller.wait_event(tail_copy)

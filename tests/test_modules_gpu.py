@@ -163,9 +163,10 @@ def _chain_layer():
     return L.spikeLayer(neuron, {"Ts": 1.0, "tSample": 300}).cuda()
 
 
+@pytest.mark.parametrize("small_bytes", [0, 100 * 1024, 1 << 30])     # all chunked / mixed / all whole-batch
 @pytest.mark.parametrize("capture", [False, True])
 @pytest.mark.parametrize("batch,chunks", [(16, 4), (7, 3), (3, 8), (5, 1)])
-def test_host_pipeline_matches_single_call(batch, chunks, capture):
+def test_host_pipeline_matches_single_call(batch, chunks, capture, small_bytes):
     """Chunked, overlapped streaming of a host batch gives the bits of one call on the whole batch."""
     from slayerpytorch_b200.hoststream import HostPipeline
     net = _chain_layer()
@@ -183,7 +184,7 @@ def test_host_pipeline_matches_single_call(batch, chunks, capture):
     y_ref, gx_ref = step(x.cuda(), up.cuda())
     assert 0.005 < y_ref.mean().item() < 0.5
     y_h, gx_h = torch.empty_like(x).pin_memory(), torch.empty_like(x).pin_memory()
-    pipe = HostPipeline("cuda", chunks=chunks, capture=capture)
+    pipe = HostPipeline("cuda", chunks=chunks, capture=capture, small_bytes=small_bytes)
     for _ in range(3):                     # later runs reuse the staging buffers (and graphs)
         y_h.fill_(-1)
         gx_h.fill_(-1)
