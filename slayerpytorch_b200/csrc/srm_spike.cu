@@ -205,7 +205,8 @@ __device__ __forceinline__ void ring_reset(float (&ring)[R])
 }
 
 // ---------------------------------------------------------------------------------------
-// cp.async path (any alignment).  V: global access width in floats.
+// cp.async path for buffers that are not 16-byte aligned.  V: global access width in floats
+// (2 or 1; T % V == 0 and bases aligned to 4*V bytes).
 // ---------------------------------------------------------------------------------------
 template <int V, int NB, int W>
 __global__ void __launch_bounds__(256)
@@ -237,29 +238,22 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
     // of the next row block - are always in flight, so a change of row block costs no memory
     // latency.  Large launches hide latency with many resident warps and use depth 2; launches
     // with only a few warps per SM use depth 4 (more shared memory per warp, fewer stalls).
-    // V == 4 uses row-skewed tiles (tile.cuh): 16-byte accesses on 32-byte boundaries for any T.
-    // Samples before a row's start are padded with -inf, which can neither spike nor be changed
-    // by a refractory tap, so the skewed lanes idle through them with their state untouched.
-    const int ntiles = V == 4 ? skew_tiles(T) : (T + kTile - 1) / kTile;
-    const unsigned phase = (unsigned)(reinterpret_cast<uintptr_t>(u) >> 2) & 7u;
+    static_assert(V == 1 || V == 2, "aligned buffers take the wide-tile or the bulk-tensor kernel");
+    const int ntiles = (T + kTile - 1) / kTile;
     const int64_t nblocks = (rows + kTile - 1) / kTile;
     const int64_t wstride = (int64_t)gridDim.x * warps_per_block;
     int64_t rb = (int64_t)blockIdx.x * warps_per_block + warp;
     if (rb >= nblocks) return;
     int64_t rb_next = rb;           // (row block, tile) of the tile to prefetch next
     int it_next = 0;
-    int skew = V == 4 ? block_skew(rb * kTile, T, phase) : 0;        // of the block being walked
-    int skew_next = skew;                                             // of the block being prefetched
     unsigned q = 0;                 // tiles walked so far: buffer = q & (depth - 1)
     const unsigned dmask = (unsigned)depth - 1u;
 
     auto prefetch = [&](float *dst) {
-        if (V == 4) tile_prefetch_skew(dst, u, rb_next * kTile, rows, it_next, T, lane, skew_next, -INFINITY);
-        else tile_prefetch<V>(dst, u, rb_next * kTile, rows, it_next * kTile, T, lane);
+        tile_prefetch<V>(dst, u, rb_next * kTile, rows, it_next * kTile, T, lane);
         if (++it_next == ntiles) {
             it_next = 0;
             rb_next += wstride;
-            if (V == 4 && rb_next < nblocks) skew_next = block_skew(rb_next * kTile, T, phase);
         }
     };
     for (int d = 0; d + 1 < depth; ++d) {
@@ -284,18 +278,12 @@ srm_get_spikes_kernel(float *s, float *u, const float *__restrict__ nu,
         else walk_tile<kTile, false, NB, W>(tile, tile_s, st, ring, lane);
         __syncwarp();
 
-        if (V == 4) {
-            tile_store_skew(tile, u, row0, rows, it, T, lane, skew);
-            tile_store_skew(tile_s, s, row0, rows, it, T, lane, skew);
-        } else {
-            tile_store<V>(tile, u, row0, rows, it * kTile, T, lane);
-            tile_store<V>(tile_s, s, row0, rows, it * kTile, T, lane);
-        }
+        tile_store<V>(tile, u, row0, rows, it * kTile, T, lane);
+        tile_store<V>(tile_s, s, row0, rows, it * kTile, T, lane);
         __syncwarp();
         if (++it == ntiles) {
             it = 0;
             rb += wstride;
-            if (V == 4 && rb < nblocks) skew = block_skew(rb * kTile, T, phase);
         }
     }
 }
