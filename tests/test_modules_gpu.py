@@ -269,3 +269,45 @@ def test_spike_delayed_matches_the_two_separate_nodes(learnable):
     assert torch.equal(xa.grad.view(torch.int32), xb.grad.view(torch.int32))
     if learnable:
         assert torch.equal(dl_a.delay.grad, dl_b.delay.grad)
+
+
+def test_num_spikes_loss_against_a_host_restatement():
+    """numSpikes on the device vs the same formula written out with NumPy in float64
+    (src/spikeLoss.py:84-104): count error inside the target region, psp of the spikes outside."""
+    from slayerpytorch_b200 import loss as ours_loss
+    from slayerpytorch_b200.layer import alpha_kernel
+    Ts, T = 1.0, 300
+    params = {"neuron": {"type": "SRMALPHA", "theta": 10, "tauSr": 10.0, "tauRef": 1.0, "scaleRef": 2,
+                         "tauRho": 1, "scaleRho": 1},
+              "simulation": {"Ts": Ts, "tSample": T, "nSample": 12},
+              "training": {"error": {"type": "NumSpikes", "tgtSpikeRegion": {"start": 40, "stop": 260},
+                                     "tgtSpikeCount": {True: 60, False: 10}}}}
+    g = torch.Generator().manual_seed(12)
+    spikes = (torch.rand(5, 10, 1, 1, T, generator=g) < 0.1).float()
+    label = torch.randint(0, 10, (5,), generator=g)
+    desired = torch.zeros(5, 10, 1, 1, 1)
+    desired[torch.arange(5), label] = 1
+    err = ours_loss.spikeLoss(params).cuda()
+    x = spikes.cuda().requires_grad_(True)
+    loss = err.numSpikes(x, desired.cuda())
+    loss.backward()
+
+    s = spikes.numpy().astype(np.float64)
+    inside = np.zeros(T)
+    inside[40:260] = 1
+    want_count = np.where(desired.numpy() == 1, 60.0, 10.0)
+    count_err = (s[..., 40:260].sum(-1, keepdims=True) * Ts - want_count) / 220
+    k = np.asarray(alpha_kernel(10.0, Ts, T), np.float64)
+    outside = s * (1 - inside)
+    psp = np.zeros_like(s)
+    for i, kv in enumerate(k):
+        psp[..., i:] += kv * outside[..., :T - i]
+    e = psp * Ts + count_err * inside
+    want = 0.5 * (e ** 2).sum() * Ts
+    assert abs(loss.item() - want) <= 1e-5 * want
+    # gradient = corr(error) everywhere (the part inside the region is a constant, not masked)
+    grad = np.zeros_like(s)
+    for i, kv in enumerate(k):
+        grad[..., :T - i] += kv * e[..., i:]
+    np.testing.assert_allclose(x.grad.cpu().numpy(), grad * Ts * Ts, rtol=2e-4, atol=1e-5)
+    assert ours_loss.spikeClassifier.getClass(x.detach()).shape == (5,)

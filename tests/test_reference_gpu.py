@@ -218,3 +218,55 @@ def test_reference_loihi_layer_on_the_new_operators(ref_py_on_ours, golden_dir):
     y = L.spikeLoihi(a)
     y.backward(torch.ones_like(y))
     assert torch.isfinite(a.grad).all() and a.grad.abs().sum() > 0
+
+
+@pytest.mark.parametrize("Ts,region", [(1.0, (0, 300)), (1.0, (50, 250)), (0.5, (10, 120))])
+def test_device_resident_losses_equal_the_reference_losses(ref_py_on_ours, Ts, region):
+    """slayerpytorch_b200.loss (no host round trip) against the reference's spikeLoss.py and
+    spikeClassifier: loss values and the gradients that reach the spikes."""
+    from slayerpytorch_b200 import loss as ours_loss
+    dev = torch.device("cuda")
+    T = int(round(300 / Ts)) if Ts == 1.0 else 300
+    params = {"neuron": {"type": "SRMALPHA", "theta": 10, "tauSr": 10.0, "tauRef": 1.0, "scaleRef": 2,
+                         "tauRho": 1, "scaleRho": 1},
+              "simulation": {"Ts": Ts, "tSample": int(T * Ts), "nSample": 12},
+              "training": {"error": {"type": "NumSpikes", "tgtSpikeRegion": {"start": region[0], "stop": region[1]},
+                                     "tgtSpikeCount": {True: 60, False: 10}}}}
+    g = torch.Generator().manual_seed(int(Ts * 10) + region[0])
+    spikes = ((torch.rand(6, 10, 1, 1, T, generator=g) < 0.08).float() / Ts).to(dev)
+    label = torch.randint(0, 10, (6,), generator=g)
+    desired = torch.zeros(6, 10, 1, 1, 1)
+    desired[torch.arange(6), label] = 1
+
+    ref = ref_py_on_ours.loss.spikeLoss(params).to(dev)
+    mine = ours_loss.spikeLoss(params).to(dev)
+    for scale in (1, 0.5):
+        a = spikes.clone().requires_grad_(True)
+        la = ref.numSpikes(a, desired, scale)
+        la.backward()
+        b = spikes.clone().requires_grad_(True)
+        lb = mine.numSpikes(b, desired.to(dev), scale)
+        lb.backward()
+        assert la.item() > 0
+        torch.testing.assert_close(lb, la, rtol=1e-6, atol=0)
+        torch.testing.assert_close(b.grad, a.grad, rtol=1e-5, atol=1e-7)
+        # a CPU one-hot works too (the reference only takes that form)
+        torch.testing.assert_close(mine.numSpikes(spikes, desired, scale), la, rtol=1e-6, atol=0)
+
+    params["training"]["error"] = {"type": "SpikeTime"}
+    ref, mine = ref_py_on_ours.loss.spikeLoss(params).to(dev), ours_loss.spikeLoss(params).to(dev)
+    target = ((torch.rand(6, 10, 1, 1, T, generator=g) < 0.05).float() / Ts).to(dev)
+    a = spikes.clone().requires_grad_(True)
+    la = ref.spikeTime(a, target)
+    la.backward()
+    b = spikes.clone().requires_grad_(True)
+    lb = mine.spikeTime(b, target)
+    lb.backward()
+    torch.testing.assert_close(lb, la, rtol=1e-6, atol=0)
+    torch.testing.assert_close(b.grad, a.grad, rtol=1e-5, atol=1e-7)
+
+    import importlib
+    ref_cls = importlib.import_module(ref_py_on_ours.loss.__name__.rsplit(".", 1)[0] + ".spikeClassifier").spikeClassifier
+    got = ours_loss.spikeClassifier.getClass(spikes)
+    assert got.is_cuda
+    assert torch.equal(got.cpu(), ref_cls.getClass(spikes))
