@@ -431,6 +431,12 @@ def time_ours(args, rank, world, device):
         "cpu_baseline": cpu,
         "per_op": op_table,
     }
+    if world == 1:
+        from slayerpytorch_b200 import loss as device_loss
+        s2, desired = loss_inputs(slayerCuda, wl, device)
+        out["loss"] = {"what": "spikeLoss.numSpikes forward + backward on the output spikes (%d x %d x %d), wall clock, "
+                               "tensors on the device, no host round trip" % (BATCH, N_OUT, T),
+                       "ms": time_num_spikes_loss(device_loss.spikeLoss(LOSS_PARAMS).to(device), s2, desired.to(device))}
     if world == 1 and not args.no_scaled:
         out["scaled"] = scaled_variant(slayerCuda, device, peak)
     return out
@@ -492,6 +498,37 @@ def scaled_variant(ops, device, peak):
             "chain_frac_of_hbm_peak": round(40 * el / (total * 1e-3) / 1e9 / peak, 4),
             "reference_sequence_ms_per_step": total_ref_seq,
             "spike_rate": rate, "per_op": res}
+
+
+# ------------------------------------------------------------------------------ loss leg
+LOSS_PARAMS = {"neuron": dict(NEURON), "simulation": dict(SIM),
+               "training": {"error": {"type": "NumSpikes", "tgtSpikeRegion": {"start": 0, "stop": T},
+                                      "tgtSpikeCount": {True: TGT_TRUE, False: TGT_FALSE}}}}
+
+
+def time_num_spikes_loss(loss_module, spikes, desired, iters=50):
+    """Wall-clock time of numSpikes forward + backward on the output layer's spikes (host
+    synchronised on both sides: what a training loop waits for)."""
+    for _ in range(5):
+        x = spikes.clone().requires_grad_(True)
+        loss_module.numSpikes(x, desired).backward()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        x = spikes.clone().requires_grad_(True)
+        loss_module.numSpikes(x, desired).backward()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / iters * 1e3
+
+
+def loss_inputs(ops, wl, device):
+    u2 = ops.conv(wl["a2"], wl["srm"], wl["Ts"])
+    s2 = ops.getSpikes(u2, wl["ref"], wl["theta"], wl["Ts"])
+    gen = torch.Generator().manual_seed(5)
+    label = torch.randint(0, N_OUT, (BATCH,), generator=gen)
+    desired = torch.zeros(BATCH, N_OUT, 1, 1, 1)
+    desired[torch.arange(BATCH), label] = 1
+    return s2, desired
 
 
 # ------------------------------------------------------------------------------- CPU legs
@@ -567,7 +604,38 @@ def time_reference(args, rank, world):
                 out["reference_cuda"] = time_reference_cuda(RefCudaOps(mod), max(5, min(args.steps, 20)))
         except Exception as e:
             out["reference_cuda"] = {"unavailable": repr(e)[:200]}
+        try:
+            out["reference_loss"] = time_reference_loss()
+        except Exception as e:
+            out["reference_loss"] = {"unavailable": repr(e)[:200]}
     return out
+
+
+def time_reference_loss():
+    """The reference's own spikeLoss.py (installed under oracle/_ref by oracle/build_ref.py),
+    unchanged, on this build's operator modules: the NumPy round trip is what is being timed."""
+    import importlib
+    import types
+    src = os.path.join(ROOT, "oracle", "_ref", "slayerSNN")
+    if not os.path.isfile(os.path.join(src, "spikeLoss.py")):
+        return {"unavailable": "reference Python package not installed under oracle/_ref"}
+    import slayerpytorch_b200
+    ops, loihi_ops = slayerpytorch_b200.load_ops()
+    sys.modules.setdefault("slayerCuda", ops)
+    sys.modules.setdefault("slayerLoihiCuda", loihi_ops)
+    pkg = types.ModuleType("slayerSNN_bench")
+    pkg.__path__ = [src]
+    sys.modules["slayerSNN_bench"] = pkg
+    import contextlib
+    import io
+    with contextlib.redirect_stdout(io.StringIO()):
+        ref_loss = importlib.import_module("slayerSNN_bench.spikeLoss")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    wl = make_workload(ops, device, seed=1002)
+    s2, desired = loss_inputs(ops, wl, device)
+    return {"what": "the reference's spikeLoss.numSpikes forward + backward on the same spikes, wall clock",
+            "ms": time_num_spikes_loss(ref_loss.spikeLoss(LOSS_PARAMS).to(device), s2, desired)}
 
 
 def time_reference_cuda(ops, steps):
