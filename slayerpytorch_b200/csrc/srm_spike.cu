@@ -116,12 +116,13 @@ __device__ __forceinline__ void fma_keep(float &v, float a, float b)
     asm("fma.rn.f32 %0, %1, %2, %0;" : "+f"(v) : "f"(a), "f"(b));
 }
 
-// Word offset of 16-byte chunk c of row r in a time tile of R steps (R = 32: 128-byte swizzle
-// of tile.cuh, R = 16: 64-byte swizzle of the bulk-tensor boxes).
+// Word offset of 16-byte chunk c of row r in a time tile of R = 32 steps: the 128-byte swizzle
+// of tile.cuh, which is also the layout a bulk tensor copy with that swizzle mode produces.
 template <int R>
 __device__ __forceinline__ int chunk_of(int r, int c)
 {
-    return R == 32 ? r * 32 + ((c ^ (r & 7)) << 2) : r * 16 + ((c ^ ((r >> 1) & 3)) << 2);
+    static_assert(R == kTile, "time tiles are 32 steps wide");
+    return tile_chunk(r, c);
 }
 
 // Walk one time tile of R steps for this lane's row: potentials are updated in place in
@@ -410,9 +411,10 @@ constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier befor
 // dynamic shared memory of a launch with `warps` warps per CTA and `ustages` stages per warp
 // mask_tiles: wide tiles whose spike bits a warp keeps (1, or all tiles of a row for the
 // delayed-output variant)
+constexpr int kRowMaskStride = kTile + 1;       // words between consecutive mask words of the whole-row bits
 static inline size_t srm_tma_smem(int warps, int ustages, int nuEff, bool taps_in_smem, int mask_tiles = 1)
 {
-    return 1024 + (size_t)warps * ((size_t)ustages * kStageBytes + (size_t)mask_tiles * 2 * kTile * sizeof(unsigned)
+    return 1024 + (size_t)warps * ((size_t)ustages * kStageBytes + (size_t)mask_tiles * 2 * kRowMaskStride * sizeof(unsigned)
                                    + ustages * sizeof(uint64_t))
          + (taps_in_smem ? (size_t)((nuEff + 3) & ~3) * sizeof(float) : 0);
 }
@@ -472,7 +474,8 @@ __device__ __forceinline__ void wide_store_spikes(const unsigned *masks, float *
 
 // Delayed spike samples of a block of 32 rows from the spike bits of the whole rows:
 // out[r, t] = value if row r spiked at t - d_r (0 <= t - d_r < T), else 0.  masks is word-major
-// ([word][row], nwords words per row, bits past T clear); lane l holds d of row l.
+// ([word][row] with kRowMaskStride words per mask word, nwords words per row, bits past T
+// clear); lane l holds d of row l.
 __device__ __forceinline__ void store_delayed_spikes(const unsigned *masks, int nwords, float *g, int64_t row0,
                                                      int64_t rows, int T, int lane, int d_lane, float value)
 {
@@ -491,8 +494,8 @@ __device__ __forceinline__ void store_delayed_spikes(const unsigned *masks, int 
             unsigned m = 0u;
             if (src > -4 && src < T) {
                 const int w = (int)(src >> 5), off = (int)(src & 31);
-                const unsigned lo = (w >= 0 && w < nwords) ? masks[w * kTile + r] : 0u;
-                const unsigned hi = (w + 1 >= 0 && w + 1 < nwords) ? masks[(w + 1) * kTile + r] : 0u;
+                const unsigned lo = (w >= 0 && w < nwords) ? masks[w * kRowMaskStride + r] : 0u;
+                const unsigned hi = (w + 1 >= 0 && w + 1 < nwords) ? masks[(w + 1) * kRowMaskStride + r] : 0u;
                 m = __funnelshift_r(lo, hi, off);
             }
             *reinterpret_cast<float4 *>(g + (row0 + r) * (int64_t)T + 4 * q) =
@@ -527,7 +530,9 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
     float *u_tiles = reinterpret_cast<float *>(base) + (size_t)warp * ustages * kWideWords;
     unsigned char *after_tiles = base + (size_t)warps_per_block * ustages * kStageBytes;
     const int ntiles = (T + kWide - 1) / kWide;
-    const int mask_words = (DELAYED ? ntiles : 1) * 2 * kTile;       // per warp; word-major: [word][row]
+    // per warp; word-major [word][row], one word of padding per mask word so that a lane group
+    // reading consecutive words of one row hits different banks
+    const int mask_words = (DELAYED ? ntiles : 1) * 2 * kRowMaskStride;
     unsigned *masks = reinterpret_cast<unsigned *>(after_tiles) + warp * mask_words;
     uint64_t *bars = reinterpret_cast<uint64_t *>(after_tiles + warps_per_block * mask_words * sizeof(unsigned))
                      + warp * ustages;
@@ -612,8 +617,8 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
             const int left = T - kWide * j;                  // > 0
             if (left < kTile) m[0] &= (1u << left) - 1u;
             if (left < kWide) m[1] &= left > kTile ? (1u << (left - kTile)) - 1u : 0u;
-            masks[(2 * j) * kTile + lane] = m[0];
-            masks[(2 * j + 1) * kTile + lane] = m[1];
+            masks[(2 * j) * kRowMaskStride + lane] = m[0];
+            masks[(2 * j + 1) * kRowMaskStride + lane] = m[1];
         } else {
             masks[lane] = m[0];
             masks[kTile + lane] = m[1];
@@ -761,7 +766,7 @@ static int launch_srm_delayed(const SrmArgs &a, const DelayArgs &da)
         return SLAYER_B200_EUNSUPPORTED;
     }
     const int sms = sm_count();
-    const size_t mask_bytes = (size_t)ntiles * 2 * kTile * sizeof(unsigned);
+    const size_t mask_bytes = (size_t)ntiles * 2 * kRowMaskStride * sizeof(unsigned);
     const int64_t warps_per_sm = ceil_div(nblocks, (int64_t)sms);
     int ustages = (int)(((208 * 1024) / warps_per_sm - (int64_t)mask_bytes) / kStageBytes);
     if (ustages > kMaxUStages) ustages = kMaxUStages;

@@ -78,25 +78,8 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
         : "memory");
 }
 
-// shared -> global box store, tracked by the issuing thread's bulk async-group
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *smem_src)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
-                 : "memory");
-}
-
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-
-// wait until all but the N most recent store groups have finished READING shared memory
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
-
-// wait until all but the N most recent store groups have completed
-template <int N>
-__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
-
-// order this thread's shared-memory writes before later asynchronous-proxy reads (bulk stores)
+// order this thread's shared-memory accesses before later asynchronous-proxy accesses to the
+// same locations (a bulk load that refills a tile this thread has just read)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 #endif
 
