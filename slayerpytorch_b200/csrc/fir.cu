@@ -32,6 +32,7 @@ constexpr int kFirWin = kFirSeg + 4;           // samples one group of four taps
 constexpr int kFirRing = kFirWin + 4;          // register ring: the window plus the quad being loaded
 constexpr int kFirPhases = kFirRing / 4;       // 6
 constexpr int kFirMaxWarps = 16;
+constexpr int kFirTileWordsPerRow = 432;  // 2 buffers x 32 rows x 432 words = 108 KB: two CTAs per SM
 
 // 128-bit load from a 32-bit shared-memory address (explicit state space: the address
 // arithmetic stays 32-bit and constant offsets fold into the instruction)
@@ -150,21 +151,50 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
     for (int i = threadIdx.x; i < KP; i += blockDim.x) fs[i] = i < K ? filt[i] : 0.0f;
 
     // asynchronous copy of one input tile: warp w fills rows w, w+nwarps, ... from contiguous
-    // global segments; samples outside the row (or rows outside the array) become zeros
-    auto fill = [&](float *xs, int64_t tile) {
+    // global segments; samples outside the row (or rows outside the array) become zeros.
+    // With 16-byte accesses a lane copies at most four chunks per row, and which of them lie
+    // inside [0, T) is the same for every row of the tile, so that is worked out once per tile
+    // and a row costs one pointer plus, per chunk, one 64-bit add and the copy itself.
+    const unsigned xbuf_saddr = (unsigned)__cvta_generic_to_shared(xbuf);
+    auto fill = [&](int buf, int64_t tile) {
+        float *xs = xbuf + buf * tile_words;
         const int64_t rb = tile / sh.ttiles;
         const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
         const int64_t row0 = rb * kFirRows;
         const int64_t nrow = rows - row0;
         const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
-        for (int r = warp; r < kFirRows; r += nwarps) {
-            const bool row_ok = r < nrow;
-            const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
-            float *dst = xs + r * sh.SX;
-            for (int p = lane * V; p < WX; p += 32 * V) {
-                const int gt = g0 + p;
-                const bool ok = row_ok && gt >= 0 && gt < T;
-                cp_async<4 * V>(dst + p, ok ? src + gt : in, ok);
+        if constexpr (V == 4) {
+            constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
+            int goff[kChunks], nbytes[kChunks];          // source offset in the row; 16, 0 (zero fill) or -1 (no chunk)
+#pragma unroll
+            for (int k = 0; k < kChunks; ++k) {
+                const int pcol = lane * 4 + 128 * k;
+                const int gt = g0 + pcol;
+                const bool ok = gt >= 0 && gt < T;
+                goff[k] = ok ? gt : 0;
+                nbytes[k] = pcol < WX ? (ok ? 16 : 0) : -1;
+            }
+            for (int r = warp; r < kFirRows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+                const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + r * sh.SX + lane * 4);
+#pragma unroll
+                for (int k = 0; k < kChunks; ++k) {
+                    if (nbytes[k] < 0) continue;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
+                                 ::"r"(dst + 512u * k), "l"(src + goff[k]), "r"(row_ok ? nbytes[k] : 0) : "memory");
+                }
+            }
+        } else {
+            for (int r = warp; r < kFirRows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+                float *dst = xs + r * sh.SX;
+                for (int pcol = lane * V; pcol < WX; pcol += 32 * V) {
+                    const int gt = g0 + pcol;
+                    const bool ok = row_ok && gt >= 0 && gt < T;
+                    cp_async<4 * V>(dst + pcol, ok ? src + gt : in, ok);
+                }
             }
         }
         cp_async_commit();
@@ -177,12 +207,12 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
     const unsigned xbuf_addr = (unsigned)__cvta_generic_to_shared(xbuf);
 
     int64_t tile = blockIdx.x;
-    if (tile < ntiles) fill(xbuf, tile);
+    if (tile < ntiles) fill(0, tile);
     for (int it = 0; tile < ntiles; tile += gridDim.x, ++it) {
         cp_async_wait<0>();
         __syncthreads();                 // this tile has landed; the other buffer is free again
         const int64_t next = tile + gridDim.x;
-        if (next < ntiles) fill(xbuf + ((it + 1) & 1) * tile_words, next);
+        if (next < ntiles) fill((it + 1) & 1, next);
 
         const int64_t rb = tile / sh.ttiles;
         const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
@@ -273,8 +303,6 @@ static inline int pad_stride(int w)       // smallest s >= w with s = 4 (mod 8)
     if ((s & 7) == 0) s += 4;
     return s;
 }
-
-constexpr int kFirTileWordsPerRow = 432;  // 2 buffers x 32 rows x 432 words = 108 KB: two CTAs per SM
 
 // Tile shape for rows of length T and K taps; returns false if the filter is too long to tile.
 static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
