@@ -428,23 +428,48 @@ struct DelayArgs {
     int64_t nNeurons;
 };
 
+// Shared-memory word offsets of a lane's 16-byte chunk in the rows it visits when it drains a
+// wide tile, two rows per pass (row = 2 * pass + rsub): the swizzle term depends on the pass
+// only through (2 * pass) & 7, so four offsets cover all sixteen passes and the row term is a
+// compile-time constant per pass.
+struct DrainLane {
+    int c16, rsub;
+    int sw[4];                  // word offset inside the half for pass & 3 = 0..3, without the row term
+    __device__ __forceinline__ explicit DrainLane(int lane)
+    {
+        c16 = lane & 15;
+        rsub = lane >> 4;
+        const int cq = c16 & 7;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sw[k] = (c16 >> 3) * kTileWords + rsub * kTile + ((cq ^ ((2 * k + rsub) & 7)) << 2);
+    }
+    // word offset of the chunk in row 2 * pass + rsub (pass is a compile-time constant at the call)
+    __device__ __forceinline__ int word(int pass) const { return 2 * pass * kTile + sw[pass & 3]; }
+};
+
 // Potentials of an unskewed wide tile starting at time t0 (T % 4 == 0).
 __device__ __forceinline__ void wide_store(const float *tile, float *g, int64_t row0, int64_t rows,
                                            int t0, int T, int lane)
 {
-    const int c16 = lane & 15;
-    const int rsub = lane >> 4;
-    const int t = t0 + c16 * 4;
+    const DrainLane dl(lane);
+    const int t = t0 + dl.c16 * 4;
     if (t >= T) return;
-    const float *half = tile + (c16 >> 3) * kTileWords;
-    const int c = (c16 & 7) * 4;
     const int64_t nrow = rows - row0;
-    float *dst = g + row0 * (int64_t)T + t;
+    float *dst = g + (row0 + dl.rsub) * (int64_t)T + t;
+    const int64_t pitch = 2 * (int64_t)T;
+    if (nrow >= kTile) {
 #pragma unroll
-    for (int i = 0; i < kTile / 2; ++i) {
-        const int r = i * 2 + rsub;
-        if (r < nrow)
-            *reinterpret_cast<float4 *>(dst + r * (int64_t)T) = *reinterpret_cast<const float4 *>(half + tile_word(r, c));
+        for (int i = 0; i < kTile / 2; ++i) {
+            *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(tile + dl.word(i));
+            dst += pitch;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kTile / 2; ++i) {
+            if (i * 2 + dl.rsub < nrow)
+                *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(tile + dl.word(i));
+            dst += pitch;
+        }
     }
 }
 
@@ -456,19 +481,21 @@ __device__ __forceinline__ void wide_store_spikes(const unsigned *masks, float *
     const int rsub = lane >> 4;
     const int t = t0 + c16 * 4;
     if (t >= T) return;
-    const unsigned *half = masks + (c16 >> 3) * kTile;
+    const unsigned *half = masks + (c16 >> 3) * kTile + rsub;
     const int sh = (c16 & 7) * 4;
     const int64_t nrow = rows - row0;
-    float *dst = g + row0 * (int64_t)T + t;
+    float *dst = g + (row0 + rsub) * (int64_t)T + t;
+    const int64_t pitch = 2 * (int64_t)T;
+    const bool full = nrow >= kTile;
 #pragma unroll
     for (int i = 0; i < kTile / 2; ++i) {
-        const int r = i * 2 + rsub;
-        if (r < nrow) {
-            const unsigned m = half[r] >> sh;
-            *reinterpret_cast<float4 *>(dst + r * (int64_t)T) =
+        if (full || i * 2 + rsub < nrow) {
+            const unsigned m = half[2 * i] >> sh;
+            *reinterpret_cast<float4 *>(dst) =
                 make_float4((m & 1u) ? value : 0.0f, (m & 2u) ? value : 0.0f,
                             (m & 4u) ? value : 0.0f, (m & 8u) ? value : 0.0f);
         }
+        dst += pitch;
     }
 }
 
