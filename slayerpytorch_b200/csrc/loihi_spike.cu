@@ -129,9 +129,7 @@ loihi_get_spikes_kernel(float *s, float *v, float *u, const float *w,
             __syncwarp();
 
             if (V == 4) {
-                tile_store_skew(tile_u, u, row0, rows, it, T, lane, skew);
-                tile_store_skew(tile_v, v, row0, rows, it, T, lane, skew);
-                tile_store_skew(tile_s, s, row0, rows, it, T, lane, skew);
+                tile_store3_skew(tile_u, tile_v, tile_s, u, v, s, row0, rows, it, T, lane, skew);
             } else {
                 tile_store<V>(tile_u, u, row0, rows, t0, T, lane);
                 tile_store<V>(tile_v, v, row0, rows, t0, T, lane);

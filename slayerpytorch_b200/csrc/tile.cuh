@@ -182,6 +182,44 @@ __device__ __forceinline__ void tile_store_skew(const float *tile, float *g, int
     }
 }
 
+// Three tiles of the same rows and steps to three arrays of the same shape: the row, its skew,
+// the bounds and the offset are worked out once per pass and shared by the three stores.
+__device__ __forceinline__ void tile_store3_skew(const float *tile_a, const float *tile_b, const float *tile_c,
+                                                 float *ga, float *gb, float *gc, int64_t row0, int64_t rows,
+                                                 int j, int T, int lane, int skew0)
+{
+    const int c = (lane & 7) * 4;
+    const int rsub = lane >> 3;
+    const int64_t nrow = rows - row0;
+#pragma unroll
+    for (int i = 0; i < kTile / 4; ++i) {
+        const int r = i * 4 + rsub;
+        const int t = kTile * j - row_skew(skew0, r, T) + c;
+        if (r >= nrow || t >= T || t + 4 <= 0) continue;
+        const int w = tile_word(r, c);
+        const int64_t off = (row0 + r) * (int64_t)T + t;
+        const float4 va = *reinterpret_cast<const float4 *>(tile_a + w);
+        const float4 vb = *reinterpret_cast<const float4 *>(tile_b + w);
+        const float4 vc = *reinterpret_cast<const float4 *>(tile_c + w);
+        if (t >= 0 && t + 4 <= T) {
+            *reinterpret_cast<float4 *>(ga + off) = va;
+            *reinterpret_cast<float4 *>(gb + off) = vb;
+            *reinterpret_cast<float4 *>(gc + off) = vc;
+        } else {
+            const float ea[4] = {va.x, va.y, va.z, va.w};
+            const float eb[4] = {vb.x, vb.y, vb.z, vb.w};
+            const float ec[4] = {vc.x, vc.y, vc.z, vc.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (t + k >= 0 && t + k < T) {
+                    ga[off + k] = ea[k];
+                    gb[off + k] = eb[k];
+                    gc[off + k] = ec[k];
+                }
+        }
+    }
+}
+
 // number of 32-step tiles that cover a row of T samples for every skew (0..7)
 __host__ __device__ inline int skew_tiles(int T) { return (T + 7 + kTile - 1) / kTile; }
 
