@@ -164,7 +164,7 @@ def _chain_layer():
 
 
 @pytest.mark.parametrize("small_bytes", [0, 100 * 1024, 1 << 30])     # all chunked / mixed / all whole-batch
-@pytest.mark.parametrize("capture", [False, True])
+@pytest.mark.parametrize("capture", [False, True, "pipeline"])
 @pytest.mark.parametrize("batch,chunks", [(16, 4), (7, 3), (3, 8), (5, 1)])
 def test_host_pipeline_matches_single_call(batch, chunks, capture, small_bytes):
     """Chunked, overlapped streaming of a host batch gives the bits of one call on the whole batch."""
