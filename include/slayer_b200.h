@@ -155,13 +155,17 @@ int slayer_b200_srm_get_spikes_delayed(float *delayed, float *s_scratch, float *
  * code that runs where entering the CUDA allocator is not allowed (another library's callback,
  * a process whose memory footprint has been frozen).  The regular entry point obtains a small
  * status buffer with cudaMalloc the first time a device is used; this one keeps its scratch -
- * one int per block of 32 rows, in which a wait that ran out leaves its trace - in a fixed
- * 256 KB array inside the library image, resident on every GPU that loads the library until
- * the process exits.  Same arguments and results as slayer_b200_srm_get_spikes, restricted to
+ * one int per block of 32 rows: cleared when a warp starts the block, set to the number of
+ * 64-step tiles when it finishes it, or to a negative code if a bounded wait for a load ran
+ * out (slayer_b200_srm_get_spikes_noalloc_status reads it back) - in a fixed 256 KB array
+ * inside the library image, resident on every GPU that loads the library until the process
+ * exits.  Same arguments and results as slayer_b200_srm_get_spikes, restricted to
  *   - rows <= 2,097,152 (65536 blocks of 32 rows); more is rejected with SLAYER_B200_EUNSUPPORTED,
  *   - T % 4 == 0, s and u 16-byte aligned, nuSize <= 257 (else SLAYER_B200_EUNSUPPORTED).
- * The first call on each device resolves the array's device address and raises the kernel's
- * shared-memory limit; make that first call outside any stream capture.  The call itself
+ * The first call on each device resolves the array's device address and raises the
+ * shared-memory limit of every variant of the kernel (one per length class of the refractory
+ * kernel), which also loads their code; make that first call outside any stream capture and
+ * before the memory footprint is frozen.  Later calls only launch.  The call itself
  * runs no cudaMalloc / cudaFree and no allocating library routine.  All calls share the one
  * array (each launch clears the entries it uses), so calls that overlap on the GPU - two
  * streams, two host threads - race on it: issue them on one stream or serialise them.
@@ -172,6 +176,19 @@ int slayer_b200_srm_get_spikes_noalloc(float *s, float *u, const float *nu,
                                        float theta, float Ts, void *stream);
 
 /*
+ * Outcome of the most recent slayer_b200_srm_get_spikes_noalloc launch on the current device,
+ * read from that entry point's fixed array: 0 if every block of 32 rows of a [rows, T] launch
+ * was walked to its end; SLAYER_B200_EDEVICE if some block was not (a bounded wait for a load
+ * ran out, so s and u are only partly written), with the index of the first such block in
+ * *first_bad_block (may be NULL; -1 when all is well).  Pass the rows and T of that launch.
+ * Allocates nothing either: the entries are copied in pieces into a buffer on the caller's
+ * stack.  The copy waits for the device, so call it after the work, not between launches,
+ * and not while another noalloc launch is running (same array).  SLAYER_B200_EINVAL before
+ * the first noalloc call on the device.  It has no counterpart in the reference.
+ */
+int slayer_b200_srm_get_spikes_noalloc_status(int64_t rows, int64_t T, int64_t *first_bad_block);
+
+/*
  * Read and clear the device-side status word of the current device.  Kernels that wait on a
  * hardware barrier (bulk tensor copies) poll a bounded number of times; if a wait ever runs
  * out they record a non-zero code here and return instead of hanging.  *status_out is 0 when
@@ -180,6 +197,15 @@ int slayer_b200_srm_get_spikes_noalloc(float *s, float *u, const float *nu,
  * reference, whose kernels neither wait on anything nor report errors.
  */
 int slayer_b200_device_status(int *status_out);
+
+/*
+ * Exercise the give-up branch of the kernels' bounded waits without losing a copy: a one-thread
+ * kernel polls, `polls` times (1 .. 2^20), a barrier that nothing will complete, then records
+ * in the device status word the code a lost bulk copy would leave (0x5101) and returns.  It
+ * neither faults nor hangs; slayer_b200_device_status() afterwards reports and clears the code.
+ * For tests and bring-up.  It has no counterpart in the reference.
+ */
+int slayer_b200_selftest_bounded_wait(int polls, void *stream);
 
 /*
  * Enable (non-zero, the default) or disable the bulk-tensor-copy code path of the kernels

@@ -52,7 +52,7 @@ struct SrmRow {
     float nu_r[NB > 0 ? NB : 1];   // nu_r[k] = tap of a spike k+1 steps ago
     float nu0, theta, spikeVal;
     bool has_nu0;
-    bool taps_negative;      // every tap after the first has its sign bit set (ring variant is exact)
+    bool taps_negative;      // every tap after the first is finite with its sign bit set (ring variant is exact)
     const float *nu_s;
 
     __device__ __forceinline__ void init(const float *__restrict__ nu, const float *nu_smem, int nuEff,
@@ -67,7 +67,11 @@ struct SrmRow {
 #pragma unroll
         for (int k = 0; k < NB; ++k) {
             nu_r[k] = (k + 1 < nuEff) ? __ldg(nu + k + 1) : -0.0f;
-            taps_negative = taps_negative && (__float_as_uint(nu_r[k]) >> 31);
+            // sign bit set and not Inf / NaN: the ring variant multiplies every tap by a 0/1 flag,
+            // and 0 * -inf is NaN where the definition adds nothing (a tap of -inf is a legitimate
+            // way to write an absolute refractory period; it takes the bits variant)
+            const unsigned bits = __float_as_uint(nu_r[k]);
+            taps_negative = taps_negative && (bits >> 31) && ((bits & 0x7f800000u) != 0x7f800000u);
         }
 #pragma unroll
         for (int w = 0; w < W; ++w) {
@@ -590,6 +594,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
     int64_t rb_next = rb;           // (row block, tile) of the next tile to load
     int j_next = 0;
     int sg_next = 0;                // stage the next load goes to
+    int inflight = 0;               // lane 0: loads issued and not yet waited for
     int delay_steps = 0;            // DELAYED: the delay of this lane's row, in steps
     auto issue_load = [&]() {       // lane 0 only
         const bool two = kWide * j_next + kBoxT < T;           // the second box starts inside the rows
@@ -599,6 +604,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
         if (two) tma_load_2d(dst + kTileWords, &map_u, kWide * j_next + kBoxT, (int)(rb_next * kTile), bars + sg_next);
         if (++sg_next == ustages) sg_next = 0;
         if (++j_next == ntiles) { j_next = 0; rb_next += wstride; }
+        ++inflight;
     };
     if (lane == 0) {
         for (int i = 0; i + 1 < ustages; ++i)
@@ -625,9 +631,17 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
             if (lane == 0) {
                 if (PER_BLOCK) status[rb] = -kStatusSrmLoadTimeout;
                 else atomicExch(status, kStatusSrmLoadTimeout);
+                // the loads issued after the lost one may still be writing into this warp's
+                // stages: give each of them the same bounded wait before the warp leaves
+                for (int i = 1; i < inflight; ++i) {
+                    const int stage = sg + i < ustages ? sg + i : sg + i - ustages;
+                    (void)mbar_wait_bounded(bars + stage, sg + i < ustages ? parity : parity ^ 1u, kLoadPollLimit);
+                }
             }
+            __syncwarp();
             break;
         }
+        if (lane == 0) --inflight;
 
         const bool two = kWide * j + kBoxT < T;
         unsigned m[2] = {0u, 0u};
@@ -848,13 +862,39 @@ static __device__ __align__(256) int g_noalloc_block_status[kNoAllocMaxRowBlocks
 struct NoAllocDevice {
     bool ready;
     int *scratch;            // device address of g_noalloc_block_status on this device
-    bool smem_set[13];       // per kernel instantiation: shared-memory limit raised
 };
 static NoAllocDevice g_noalloc_dev[64];
 static std::mutex g_noalloc_mu;
 
+// Raise the shared-memory limit of one instantiation to the largest request any of its launches
+// can make (8 warps, 257 taps).  Setting the attribute also loads the kernel's code onto the
+// device, so after the set-up no later call has anything left to load.
 template <int NB, int W>
-static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev, int slot)
+static cudaError_t noalloc_prepare_one()
+{
+    const int most = (int)srm_tma_smem(8, kUStages, 260, true);
+    return cudaFuncSetAttribute(srm_get_spikes_tma_kernel<NB, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+}
+
+static cudaError_t noalloc_prepare_all()
+{
+    cudaError_t e;
+    if ((e = noalloc_prepare_one<2, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<4, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<6, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<8, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<10, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<12, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<16, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<24, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<32, 1>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<0, 2>()) != cudaSuccess) return e;
+    if ((e = noalloc_prepare_one<0, 4>()) != cudaSuccess) return e;
+    return noalloc_prepare_one<0, 8>();
+}
+
+template <int NB, int W>
+static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
     CUtensorMap map_u;
@@ -866,16 +906,6 @@ static int launch_srm_noalloc(const SrmArgs &a, NoAllocDevice &dev, int slot)
     spike_launch_shape(nblocks, (size_t)kUStages * kStageBytes + 512, warps, grid);
     const size_t smem = srm_tma_smem(warps, kUStages, a.nuEff, NB == 0);
     auto kern = srm_get_spikes_tma_kernel<NB, W, true>;
-    if (!dev.smem_set[slot]) {
-        // the largest request any launch of this instantiation can make (8 warps, 257 taps)
-        const int most = (int)srm_tma_smem(8, kUStages, 260, true);
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
-        if (e != cudaSuccess) {
-            set_error("srm_get_spikes_noalloc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-            return SLAYER_B200_ECUDA;
-        }
-        dev.smem_set[slot] = true;
-    }
     kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
                                                          a.spikeVal, dev.scratch, kUStages, DelayArgs{});
     return check_launch("srm_get_spikes_noalloc kernel launch");
@@ -922,24 +952,72 @@ extern "C" int slayer_b200_srm_get_spikes_noalloc(float *s, float *u, const floa
             set_error("srm_get_spikes_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
             return SLAYER_B200_ECUDA;
         }
+        e = noalloc_prepare_all();
+        if (e != cudaSuccess) {
+            set_error("srm_get_spikes_noalloc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+            return SLAYER_B200_ECUDA;
+        }
         dev.scratch = ptr;
         dev.ready = true;
     }
 
     const SrmArgs a = {s, u, nu, rows, (int)nuEff, (int)T, theta, 1.0f / Ts, (cudaStream_t)stream_, true};
     const int window = a.nuEff > 1 ? a.nuEff - 1 : 0;
-    if (window <= 2) return launch_srm_noalloc<2, 1>(a, dev, 0);
-    if (window <= 4) return launch_srm_noalloc<4, 1>(a, dev, 1);
-    if (window <= 6) return launch_srm_noalloc<6, 1>(a, dev, 2);
-    if (window <= 8) return launch_srm_noalloc<8, 1>(a, dev, 3);
-    if (window <= 10) return launch_srm_noalloc<10, 1>(a, dev, 4);
-    if (window <= 12) return launch_srm_noalloc<12, 1>(a, dev, 5);
-    if (window <= 16) return launch_srm_noalloc<16, 1>(a, dev, 6);
-    if (window <= 24) return launch_srm_noalloc<24, 1>(a, dev, 7);
-    if (window <= 32) return launch_srm_noalloc<32, 1>(a, dev, 8);
-    if (window <= 64) return launch_srm_noalloc<0, 2>(a, dev, 9);
-    if (window <= 128) return launch_srm_noalloc<0, 4>(a, dev, 10);
-    return launch_srm_noalloc<0, 8>(a, dev, 11);
+    if (window <= 2) return launch_srm_noalloc<2, 1>(a, dev);
+    if (window <= 4) return launch_srm_noalloc<4, 1>(a, dev);
+    if (window <= 6) return launch_srm_noalloc<6, 1>(a, dev);
+    if (window <= 8) return launch_srm_noalloc<8, 1>(a, dev);
+    if (window <= 10) return launch_srm_noalloc<10, 1>(a, dev);
+    if (window <= 12) return launch_srm_noalloc<12, 1>(a, dev);
+    if (window <= 16) return launch_srm_noalloc<16, 1>(a, dev);
+    if (window <= 24) return launch_srm_noalloc<24, 1>(a, dev);
+    if (window <= 32) return launch_srm_noalloc<32, 1>(a, dev);
+    if (window <= 64) return launch_srm_noalloc<0, 2>(a, dev);
+    if (window <= 128) return launch_srm_noalloc<0, 4>(a, dev);
+    return launch_srm_noalloc<0, 8>(a, dev);
+}
+
+extern "C" int slayer_b200_srm_get_spikes_noalloc_status(int64_t rows, int64_t T, int64_t *first_bad_block)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(rows >= 0 && T >= 0, "srm_get_spikes_noalloc_status: negative size");
+    if (first_bad_block) *first_bad_block = -1;
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    const int64_t nblocks = ceil_div(rows, kTile);
+    SB200_REQUIRE(nblocks <= kNoAllocMaxRowBlocks, "srm_get_spikes_noalloc_status: %lld rows exceed the %lld the array covers",
+                  (long long)rows, (long long)kNoAllocMaxRowBlocks * kTile);
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) {
+        set_error("srm_get_spikes_noalloc_status: no usable current device");
+        return SLAYER_B200_ECUDA;
+    }
+    const int *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (g_noalloc_dev[d].ready) scratch = g_noalloc_dev[d].scratch;
+    }
+    SB200_REQUIRE(scratch != nullptr, "srm_get_spikes_noalloc_status: slayer_b200_srm_get_spikes_noalloc has not run on this device");
+    const int want = (int)ceil_div(T, (int64_t)kWide);        // wide tiles per row block
+    int chunk[1024];                                           // on the stack: nothing is allocated
+    for (int64_t b0 = 0; b0 < nblocks; b0 += 1024) {
+        const int64_t n = nblocks - b0 < 1024 ? nblocks - b0 : 1024;
+        cudaError_t e = cudaMemcpy(chunk, scratch + b0, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) {
+            set_error("srm_get_spikes_noalloc_status: %s", cudaGetErrorString(e));
+            return SLAYER_B200_ECUDA;
+        }
+        for (int64_t i = 0; i < n; ++i) {
+            if (chunk[i] != want) {
+                if (first_bad_block) *first_bad_block = b0 + i;
+                set_error("srm_get_spikes_noalloc_status: row block %lld %s (entry %d, expected %d)", (long long)(b0 + i),
+                          chunk[i] == -kStatusSrmLoadTimeout ? "gave up waiting for a load" : "did not finish",
+                          chunk[i], want);
+                return SLAYER_B200_EDEVICE;
+            }
+        }
+    }
+    return SLAYER_B200_OK;
 }
 
 extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,

@@ -61,6 +61,21 @@ int *device_status_word()
     return g_status[dev];
 }
 
+// One thread waits, a bounded number of polls, for a barrier phase that nothing will ever
+// complete (it expects 16 bytes that no copy sends), then records the code a lost bulk copy
+// would record and returns.  No copy is in flight and nothing faults or spins without limit:
+// this is how the give-up branch of the bounded waits is exercised on real hardware.
+__global__ void bounded_wait_selftest_kernel(int *status, int polls)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x != 0) return;
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+    mbar_expect_tx(&bar, 16);
+    if (!mbar_wait_bounded(&bar, 0u, polls)) atomicExch(status, kStatusSrmLoadTimeout);
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
+}
+
 static std::atomic<int> g_use_tma{1};
 
 bool tma_enabled() { return g_use_tma.load() != 0; }
@@ -85,4 +100,15 @@ extern "C" int slayer_b200_device_status(int *status_out)
     if (e != cudaSuccess) { set_error("device_status: %s", cudaGetErrorString(e)); return SLAYER_B200_ECUDA; }
     *status_out = value;
     return SLAYER_B200_OK;
+}
+
+extern "C" int slayer_b200_selftest_bounded_wait(int polls, void *stream)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(polls >= 1 && polls <= (1 << 20), "selftest_bounded_wait: polls must be in [1, 2^20]");
+    int *word = device_status_word();
+    if (!word) { set_error("selftest_bounded_wait: no status word on this device"); return SLAYER_B200_ECUDA; }
+    bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(word, polls);
+    return check_launch("selftest_bounded_wait kernel launch");
 }

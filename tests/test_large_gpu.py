@@ -104,3 +104,108 @@ def test_loihi_beyond_2_to_31_elements(big):
     outs = lc.getSpikes(w, 0, 5120, 1024, 128, 1)
     for got, want in zip(outs, co.loihi_get_spikes(pick(w, big), 0, 5120, 1024, 128, 1)):
         np.testing.assert_array_equal(pick(got, big), want)
+
+
+# ------------------------------------------ the largest layers of the CNN and Loihi workloads
+def sampled(t, rows, T, idx):
+    return t.view(rows, T)[idx].cpu().numpy()
+
+
+def test_cnn_first_layer_shape_rows_match_oracle():
+    """The first spiking layer of the SRM CNN workload at full size (128 x 16 x 32 x 32 neurons =
+    2,097,152 rows x 300 steps, 2.5 GB per tensor): getSpikes, then psp on the spike tensor,
+    the surrogate gradient and corr, checked on 1200 random rows against the oracle."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 30e9:
+        pytest.skip("needs about 20 GB of free device memory")
+    sc, _ = slayerpytorch_b200.load_ops()
+    dev = torch.device("cuda")
+    N, C, H, W, T = 128, 16, 32, 32, 300
+    rows = N * C * H * W
+    g = torch.Generator(device=dev).manual_seed(1003)
+    srm = torch.tensor(alpha_kernel(10.0, 1.0, 300), dtype=torch.float32, device=dev)
+    ref = torch.tensor(alpha_kernel(1.0, 1.0, 300, mult=-20.0), dtype=torch.float32, device=dev)
+    # membrane potential of a convolution layer fed with psp of 5 % input spikes: smooth, a few
+    # percent of the samples above threshold
+    a = torch.empty(N, C, H, W, T, device=dev).normal_(generator=g).mul_(2.5)
+    m = torch.empty_like(a).uniform_(generator=g)
+    a.mul_((m < 0.25).float())
+    del m
+    u = sc.conv(a, srm, 1.0)
+    idx_np = np.sort(np.random.RandomState(3).choice(rows, 1200, replace=False))
+    idx_np[:3], idx_np[-3:] = (0, 1, 31), (rows - 33, rows - 32, rows - 1)
+    idx = torch.from_numpy(idx_np).to(dev)
+    k, r = srm.cpu().numpy(), ref.cpu().numpy()
+    co.set_ftz(True)
+    try:
+        u0 = sampled(u, rows, T, idx)
+        np.testing.assert_array_equal(u0, co.conv(sampled(a, rows, T, idx), k, 1.0))
+        del a
+        s = sc.getSpikes(u, ref, 10.0, 1.0)
+        s_w, u_w = co.srm_get_spikes(u0, r, 10.0, 1.0)
+        assert 0.002 < s_w.mean() < 0.3
+        np.testing.assert_array_equal(sampled(s, rows, T, idx), s_w)
+        np.testing.assert_array_equal(sampled(u, rows, T, idx), u_w)
+        assert torch.all((s == 0) | (s == 1.0))
+        p = sc.conv(s, srm, 1.0)                          # psp of a spike tensor (mostly zeros)
+        np.testing.assert_array_equal(sampled(p, rows, T, idx), co.conv(s_w, k, 1.0))
+        del p
+        gout = torch.empty(N, C, H, W, T, device=dev).normal_(generator=g)
+        gu = sc.spikeGrad(gout, u, 10.0, 10.0, 1.0)
+        want = co.spike_grad(sampled(gout, rows, T, idx), u_w, 10.0, 10.0, 1.0)
+        np.testing.assert_allclose(sampled(gu, rows, T, idx), want, rtol=1e-5, atol=1e-37)
+        del gout
+        c = sc.corr(gu, srm, 1.0)
+        np.testing.assert_array_equal(sampled(c, rows, T, idx), co.corr(sampled(gu, rows, T, idx), k, 1.0))
+    finally:
+        co.set_ftz(False)
+        torch.cuda.empty_cache()
+
+
+def test_loihi_first_layer_shape_rows_match_oracle():
+    """The first layer of the Loihi workload at full size (64 x 16 x 32 x 32 neurons = 1,048,576
+    rows x 1450 steps, 6.1 GB per tensor, rows not 16-byte aligned): all three outputs exact on
+    1000 random rows, then the unit delay, the surrogate gradient on the voltage and corr with
+    the 110-tap Loihi response."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 60e9:
+        pytest.skip("needs about 45 GB of free device memory")
+    sc, lc = slayerpytorch_b200.load_ops()
+    from slayerpytorch_b200.layer import loihi_psp_kernel
+    dev = torch.device("cuda")
+    N, C, H, W, T = 64, 16, 32, 32, 1450
+    rows = N * C * H * W
+    g = torch.Generator(device=dev).manual_seed(1005)
+    # weighted input of a 5x5x2 convolution with integer weights over 2 % input spikes
+    w = torch.randint(-128, 128, (N, C, H, W, T), device=dev, generator=g).float()
+    m = torch.empty_like(w).uniform_(generator=g)
+    w.mul_((m < 0.1).float())
+    del m
+    idx_np = np.sort(np.random.RandomState(5).choice(rows, 1000, replace=False))
+    idx_np[:3], idx_np[-3:] = (0, 1, 31), (rows - 33, rows - 32, rows - 1)
+    idx = torch.from_numpy(idx_np).to(dev)
+    s, v, u = lc.getSpikes(w, 0, 5120, 1024, 128, 1)
+    want = co.loihi_get_spikes(sampled(w, rows, T, idx), 0, 5120, 1024, 128, 1)
+    del w
+    for got, b, name in zip((s, v, u), want, ("spike", "voltage", "current")):
+        np.testing.assert_array_equal(sampled(got, rows, T, idx), b, err_msg=name)
+    assert 0.001 < want[0].mean() < 0.6
+    del u
+    d = sc.shift(s, 1.0, 1.0)
+    assert torch.equal(d[..., 1:], s[..., :-1]) and not d[..., 0].any()
+    del d, s
+    k = torch.tensor(loihi_psp_kernel({"iDecay": 1024, "vDecay": 128, "wgtExp": 0}), dtype=torch.float32, device=dev)
+    assert k.numel() == 110
+    gout = torch.empty(N, C, H, W, T, device=dev).normal_(generator=g)
+    gu = sc.spikeGrad(gout, v, 5120.0, 5120.0, 1.0 / 195.0)
+    np.testing.assert_allclose(sampled(gu, rows, T, idx),
+                               co.spike_grad(sampled(gout, rows, T, idx), want[1], 5120.0, 5120.0, 1.0 / 195.0),
+                               rtol=1e-5, atol=1e-37)
+    del gout, v
+    co.set_ftz(True)
+    try:
+        c = sc.corr(gu, k, 1.0)
+        np.testing.assert_array_equal(sampled(c, rows, T, idx), co.corr(sampled(gu, rows, T, idx), k.cpu().numpy(), 1.0))
+    finally:
+        co.set_ftz(False)
+        torch.cuda.empty_cache()

@@ -191,6 +191,52 @@ def test_srm_edge_values():
             assert_same_floats(G.host(ud), u_want)
 
 
+def test_srm_minus_infinity_tap_is_an_absolute_refractory_period():
+    """A tap of -inf (or a NaN tap) must only act after a spike (src/cuda/spikeKernels.h:22-33):
+    rows that never spike keep their potential bit for bit, rows that spike read -inf (resp.
+    NaN) for exactly the steps the tap covers."""
+    rng = np.random.RandomState(321)
+    for T in (100, 300, 301):
+        u = (rng.randn(2, 20, 1, 1, T) * 6).astype(np.float32)
+        u[0, 0] = -5.0                                           # never spikes
+        u[0, 1, 0, 0, :] = 11.0                                  # would spike at every step
+        for nu in (np.array([0.0, -np.inf, -np.inf, -20.0, -3.0], np.float32),
+                   np.array([-0.0, -30.0, -np.inf], np.float32),
+                   np.array([0.0, -5.0, np.nan, -1.0], np.float32)):
+            ud = G.dev(u)
+            s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
+            s_want, u_want = co.srm_get_spikes(u, nu, 10.0, 1.0)
+            np.testing.assert_array_equal(s, s_want)
+            assert_same_floats(G.host(ud), u_want)
+            assert np.array_equal(G.host(ud)[0, 0], u[0, 0]) and s.sum() > 0
+
+
+@pytest.mark.parametrize("off", [1, 2, 3])
+@pytest.mark.parametrize("T,nus", [(300, 11), (64, 2), (301, 11), (1450, 34), (130, 110)])
+def test_srm_get_spikes_unaligned_buffers(off, T, nus):
+    """Bases 4, 8 and 12 bytes off a 16-byte boundary: the 8- and 4-byte cp.async kernels."""
+    rng = np.random.RandomState(off * 100 + T + nus)
+    rows = 70
+    flat_u = (rng.randn(rows * T + 3) * 8).astype(np.float32)
+    nu = (-np.abs(rng.randn(nus)) * 6).astype(np.float32)
+    base_u = G.dev(flat_u)
+    base_s = torch.full((rows * T + 3,), float("nan"), device="cuda")
+    ud = base_u[off:off + rows * T].view(2, 35, 1, 1, T)
+    sd = base_s[off:off + rows * T].view(2, 35, 1, 1, T)
+    assert ud.data_ptr() % 16 == 4 * off
+    from slayerpytorch_b200 import capi
+    capi.call("slayer_b200_srm_get_spikes", G.ptr(sd), G.ptr(ud), G.ptr(G.dev(nu)), rows, nus, T, 10.0, 1.0, G.stream())
+    u = flat_u[off:off + rows * T].reshape(2, 35, 1, 1, T)
+    s_want, u_want = co.srm_get_spikes(u, nu, 10.0, 1.0)
+    np.testing.assert_array_equal(G.host(sd), s_want)
+    assert_same_floats(G.host(ud), u_want)
+    assert s_want.sum() > 0
+    # nothing outside the views was touched
+    assert torch.isnan(base_s[:off]).all() and torch.isnan(base_s[off + rows * T:]).all()
+    np.testing.assert_array_equal(G.host(base_u)[:off], flat_u[:off])
+    np.testing.assert_array_equal(G.host(base_u)[off + rows * T:], flat_u[off + rows * T:])
+
+
 def test_srm_trace_of_reference_fixture(golden_dir):
     """test/test_slayer002.py:153-167 on the MATLAB trace, now on the GPU."""
     srm = np.load(golden_dir + "/srm_kat.npz")
@@ -226,6 +272,41 @@ def test_loihi_wraparound_negative_currents_and_fractions():
     want = co.loihi_get_spikes(w, 1, 5120, 10, 3, 2)
     for a, b in zip(got, want):
         np.testing.assert_array_equal(G.host(a), b)
+
+
+@pytest.mark.parametrize("off", [1, 2, 3])
+@pytest.mark.parametrize("T", [300, 1450, 33])
+def test_loihi_get_spikes_unaligned_buffers(off, T):
+    """Bases off a 16-byte boundary: the 8- and 4-byte tile kernels (T even/odd, offsets 4/8/12)."""
+    rng = np.random.RandomState(off * 10 + T)
+    rows = 45
+    w = (np.round((rng.rand(rows * T + 3) - 0.5) * 90) * (rng.rand(rows * T + 3) < 0.3)).astype(np.float32)
+    base_w = G.dev(w)
+    outs = [torch.full((rows * T + 3,), float("nan"), device="cuda") for _ in range(3)]
+    wd = base_w[off:off + rows * T].view(rows, T)
+    views = [o[off:off + rows * T].view(rows, T) for o in outs]
+    from slayerpytorch_b200 import capi
+    capi.call("slayer_b200_loihi_get_spikes", G.ptr(views[0]), G.ptr(views[1]), G.ptr(views[2]), G.ptr(wd),
+              rows, T, 0, 5120, 1024, 128, 2, G.stream())
+    want = co.loihi_get_spikes(w[off:off + rows * T].reshape(rows, T), 0, 5120, 1024, 128, 2)
+    for got, b, o in zip(views, want, outs):
+        np.testing.assert_array_equal(G.host(got), b)
+        assert torch.isnan(o[:off]).all() and torch.isnan(o[off + rows * T:]).all()
+    assert want[0].sum() > 0
+
+
+@pytest.mark.parametrize("theta", [0x7fffffff, 0x80000000, 0xffffff00])
+def test_loihi_threshold_at_and_above_2_to_31(theta):
+    """theta is unsigned in the signature and compared as a signed int (spikeLoihiKernels.h:64):
+    from 2^31 on it is negative, so a voltage of zero is above threshold."""
+    rng = np.random.RandomState(theta % 1000)
+    for T in (64, 301):
+        w = (np.round((rng.rand(40, T) - 0.5) * 60) * (rng.rand(40, T) < 0.3)).astype(np.float32)
+        got = G.c_loihi(G.dev(w), 0, theta, 1024, 128, 2)
+        want = co.loihi_get_spikes(w, 0, theta, 1024, 128, 2)
+        for a, b, name in zip(got, want, ("spike", "voltage", "current")):
+            np.testing.assert_array_equal(G.host(a), b, err_msg=name)
+        assert (want[0].sum() > 0) == (theta >= 0x80000000)
 
 
 def test_loihi_reference_numpy_model_fixture(golden_dir):
@@ -488,4 +569,21 @@ def test_srm_bulk_tensor_and_cp_async_paths_agree(T, nus):
 
 def test_device_status_word_is_clear_after_the_suite_so_far():
     from slayerpytorch_b200 import capi
+    assert capi.device_status() == 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable():
+    """The give-up branch of the bounded barrier waits, made to run out on purpose: a one-thread
+    kernel polls a barrier that nothing completes 1000 times, records the status code and
+    returns.  The code is read and cleared by device_status, and the next launch is clean."""
+    from slayerpytorch_b200 import capi
+    assert capi.device_status() == 0
+    capi.call("slayer_b200_selftest_bounded_wait", 1000, G.stream())
+    assert capi.device_status() == 0x5101
+    assert capi.device_status() == 0                     # reading cleared it
+    rng = np.random.RandomState(3)
+    u, nu = srm_case(rng, (2, 3, 1, 7, 300), 11)
+    ud = G.dev(u)
+    s = G.host(G.c_srm(ud, G.dev(nu), 10.0, 1.0))
+    np.testing.assert_array_equal(s, co.srm_get_spikes(u, nu, 10.0, 1.0)[0])
     assert capi.device_status() == 0

@@ -270,3 +270,58 @@ def test_device_resident_losses_equal_the_reference_losses(ref_py_on_ours, Ts, r
     got = ours_loss.spikeClassifier.getClass(spikes)
     assert got.is_cuda
     assert torch.equal(got.cpu(), ref_cls.getClass(spikes))
+
+
+def test_long_sequence_delay_network_through_the_reference_delay_layer(ours, ref_ops):
+    """The long-sequence network 200-256-200 (T = 2000, Ts = 1, learnable delays U(0, 10) ms
+    after both layers, one input spike per neuron at a random time, spikeTime loss against 2 %
+    target trains; topology of example/01_Oxford/oxfordTrain.py:33-49) run twice through the
+    reference's UNCHANGED slayer.py / spikeLoss.py - _pspFunction, _spikeFunction, _delayLayer
+    and _delayFunction (src/slayer.py:817-957) - once bound to the new operators and once bound
+    to the reference's own CUDA binary.  Spikes must be identical, every gradient within 1e-5."""
+    with contextlib.redirect_stdout(io.StringIO()):
+        on_new = refshim.load_reference_python(ours[0], ours[1], "slayerSNN_cfg4_new")
+        on_ref = refshim.load_reference_python(ref_ops[0], ref_ops[1], "slayerSNN_cfg4_ref")
+    if on_new is None or on_ref is None:
+        pytest.skip("reference Python package not installed (oracle/build_ref.py)")
+    assert on_new.slayer.slayerCuda is ours[0] and on_ref.slayer.slayerCuda is ref_ops[0]
+    dev = torch.device("cuda")
+    params = {"neuron": {"type": "SRMALPHA", "theta": 10, "tauSr": 1.0, "tauRef": 1.0, "scaleRef": 2,
+                         "tauRho": 1, "scaleRho": 1},
+              "simulation": {"Ts": 1.0, "tSample": 2000, "nSample": 1},
+              "training": {"error": {"type": "SpikeTime"}}}
+    N, T = 8, 2000
+    g = torch.Generator().manual_seed(1004)
+    x = torch.zeros(N, 200, 1, 1, T)
+    when = torch.randint(0, 1000, (N, 200), generator=g)
+    x.view(N, 200, T).scatter_(2, when.unsqueeze(-1), 1.0)
+    target = (torch.rand(N, 200, 1, 1, T, generator=g) < 0.02).float()
+    w1 = torch.randn(256, 200, 1, 1, 1, generator=g) * 4
+    w2 = torch.randn(200, 256, 1, 1, 1, generator=g) * 1.5
+    d1 = torch.rand(256, 1, 1, generator=g) * 10
+    d2 = torch.rand(200, 1, 1, generator=g) * 10
+
+    results = []
+    for mods in (on_new, on_ref):
+        S = mods.slayer
+        L = S.spikeLayer(dict(params["neuron"]), dict(params["simulation"])).to(dev)
+        fc1, fc2 = L.dense(200, 256).to(dev), L.dense(256, 200).to(dev)
+        dl1, dl2 = L.delay(256).to(dev), L.delay(200).to(dev)
+        with torch.no_grad():
+            fc1.weight.copy_(w1)
+            fc2.weight.copy_(w2)
+            dl1.delay.copy_(d1)
+            dl2.delay.copy_(d2)
+        h = dl1(L.spike(L.psp(fc1(x.to(dev)))))
+        out = dl2(L.spike(L.psp(fc2(h))))
+        loss = mods.loss.spikeLoss(params).to(dev).spikeTime(out, target.to(dev))
+        loss.backward()
+        results.append(dict(h=h.detach(), out=out.detach(), loss=loss.detach(),
+                            gw1=fc1.weight.grad, gw2=fc2.weight.grad, gd1=dl1.delay.grad, gd2=dl2.delay.grad))
+    new, ref = results
+    assert torch.equal(new["h"], ref["h"]) and torch.equal(new["out"], ref["out"])
+    assert 0.001 < new["h"].mean() < 0.5 and new["out"].sum() > 0
+    for k in ("loss", "gw1", "gw2", "gd1", "gd2"):
+        scale = ref[k].abs().max().item()
+        assert scale > 0, k
+        torch.testing.assert_close(new[k], ref[k], rtol=REL, atol=REL * scale, msg=lambda m, k=k: k + ": " + m)
