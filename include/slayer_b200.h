@@ -215,6 +215,13 @@ int slayer_b200_selftest_bounded_wait(int polls, void *stream);
  */
 int slayer_b200_set_tma(int enable);
 
+/*
+ * Enable (non-zero, the default) or disable the packed form of the conv / corr kernel (two
+ * rows per lane, two-wide fp32 FMAs); returns the previous setting.  Disabled, the scalar
+ * kernel runs, which computes the same bits.  It has no counterpart in the reference.
+ */
+int slayer_b200_set_fir_packed(int enable);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,7 @@ SYMBOLS = {
     "slayer_b200_delay_grad": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "slayer_b200_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "slayer_b200_set_tma": (_int, [_int]),
+    "slayer_b200_set_fir_packed": (_int, [_int]),
 }
 
 _lib = None
@@ -77,6 +78,11 @@ def device_status():
     value = ctypes.c_int(0)
     check(load().slayer_b200_device_status(ctypes.byref(value)), "slayer_b200_device_status")
     return value.value
+
+
+def set_fir_packed(enable):
+    """Enable/disable the packed conv / corr kernel; returns the previous setting."""
+    return bool(load().slayer_b200_set_fir_packed(1 if enable else 0))
 
 
 def set_tma(enable):

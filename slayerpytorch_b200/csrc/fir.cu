@@ -6,6 +6,10 @@
 // output loop, so results are reproducible bit for bit whatever the tiling.  Samples outside
 // the row enter the chain as +0, which leaves the accumulator unchanged for finite taps.
 //
+// Two kernels compute the same bits.  fir2_kernel (further down, the default) packs two rows
+// per lane into two-wide FMAs; fir_kernel, described next, is the scalar form and the fallback
+// (slayer_b200_set_fir_packed(0) selects it).
+//
 // Cost: 8 algorithmic bytes and 2K flops per element.  For K above ~47 taps the fp32 FMA
 // pipes, not HBM, bound the kernel, so the design goal is to keep those pipes fed:
 //   - persistent CTAs walk [32 rows x nseg*16 samples] tiles; the input tile (plus a halo of
@@ -21,6 +25,8 @@
 //   - results go from registers straight to global memory (64 contiguous bytes per thread).
 // The row stride of the tile is = 4 (mod 8) words, which makes the per-row 128-bit loads of a
 // warp conflict free.
+#include <atomic>
+
 #include "common.cuh"
 #include "tile.cuh"
 
@@ -274,6 +280,238 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
     cp_async_wait<0>();
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Packed variant: two rows per lane, two fp32 FMAs per instruction.
+//
+// fma.rn.ftz.f32x2 performs two independent single-precision fused multiply-adds on the halves
+// of 64-bit registers; each half rounds exactly like the scalar instruction, so results keep
+// their bits.  The FMA pipe does the same number of lane-operations per clock either way, but
+// the packed form needs half the issue slots, which leaves room for the shared-memory loads
+// and address arithmetic that otherwise compete with the FMAs for issue.  Every operand has to
+// be a register pair, so the data is arranged to make the pairs natural:
+//   - a lane owns TWO rows (2l, 2l+1 of a 64-row tile); the tile in shared memory interleaves
+//     the two rows sample by sample (A0 B0 A1 B1 ...), so one 128-bit load yields two ready
+//     (A_t, B_t) pairs and the sliding window is a ring of pairs;
+//   - taps sit in shared memory duplicated (f0 f0 f1 f1 ...), one 128-bit broadcast load
+//     yields two (f, f) pairs;
+//   - accumulators are pairs (outA[m], outB[m]).
+// No re-pairing moves are needed.  The interleave is produced by the tile fill itself: 4-byte
+// cp.async copies, 32 consecutive samples of one row per warp instruction (coalesced 128 bytes
+// of global memory), which also makes the fill indifferent to the alignment of the input.
+// One CTA per SM (two buffers of up to 64 rows x 428 samples), warps take 16-sample segments.
+// ---------------------------------------------------------------------------------------
+typedef unsigned long long f2;
+
+constexpr int kFir2Rows = 64;
+constexpr int kFir2MaxSamples = 428;     // staged samples per row: 2 buffers x 32 pairs x 2 x 428 words fit one SM
+
+__device__ __forceinline__ void ld2p(unsigned saddr, f2 &a, f2 &b)
+{
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(saddr));
+}
+
+__device__ __forceinline__ void fma2_acc(f2 &acc, f2 a, f2 b)
+{
+    asm("fma.rn.ftz.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
+__device__ __forceinline__ void unpack2(f2 v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+template <int DIR, int PH, int NT>
+__device__ __forceinline__ void fir2_group(f2 (&acc)[kFirSeg], const f2 (&w)[kFirRing], const f2 (&f)[4])
+{
+#pragma unroll
+    for (int ii = 0; ii < NT; ++ii) {
+#pragma unroll
+        for (int m = 0; m < kFirSeg; ++m)
+            fma2_acc(acc[m], w[win_reg<DIR, PH>(DIR < 0 ? m + 4 - ii : m + ii)], f[ii]);
+    }
+}
+
+template <int DIR, int PH>
+__device__ __forceinline__ void fir2_group_n(f2 (&acc)[kFirSeg], const f2 (&w)[kFirRing], const f2 (&f)[4], int ntaps)
+{
+    switch (ntaps) {
+        case 1: fir2_group<DIR, PH, 1>(acc, w, f); break;
+        case 2: fir2_group<DIR, PH, 2>(acc, w, f); break;
+        case 3: fir2_group<DIR, PH, 3>(acc, w, f); break;
+        default: fir2_group<DIR, PH, 4>(acc, w, f); break;
+    }
+}
+
+// One group of four taps in phase PH; before its arithmetic it starts the loads of the next
+// group: four sample pairs into the free ring quad, four tap pairs into the idle tap quad.
+template <int DIR, int PH>
+__device__ __forceinline__ void fir2_step(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing], f2 (&f)[2][4],
+                                          unsigned fp_next, unsigned xp)
+{
+    constexpr int base = win_reg<DIR, PH>(DIR < 0 ? -4 + kFirRing : kFirWin);
+    ld2p(xp, w[base], w[base + 1]);
+    ld2p(xp + 16, w[base + 2], w[base + 3]);
+    ld2p(fp_next, f[(PH + 1) & 1][0], f[(PH + 1) & 1][1]);
+    ld2p(fp_next + 16, f[(PH + 1) & 1][2], f[(PH + 1) & 1][3]);
+    fir2_group<DIR, PH, 4>(acc, w, f[PH & 1]);
+}
+
+template <int DIR, int PH>
+__device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing], f2 (&f)[2][4],
+                                          unsigned fp_next, unsigned xp, int left, int tail)
+{
+    if (left == 0) {
+        if (tail) fir2_group_n<DIR, PH>(acc, w, f[PH & 1], tail);
+        return;
+    }
+    fir2_step<DIR, PH>(acc, w, f, fp_next, xp);
+    if constexpr (PH + 1 < kFirPhases)
+        fir2_rest<DIR, PH + 1>(acc, w, f, fp_next + 32, xp + (DIR < 0 ? 0u - 32u : 32u), left - 1, tail);
+}
+
+// V: width of the global stores in floats (4, 2 or 1; T % V == 0 and `out` aligned to 4*V bytes).
+template <int DIR, int V>
+__global__ void __launch_bounds__(kFirMaxWarps * 32, 1)
+fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
+            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int Tt = sh.nseg * kFirSeg;
+    const int WX = Tt + sh.halo;
+    const int KP = ((K + 3) & ~3) + 4;       // taps, zero padded; one spare quad for the look-ahead load
+    float *fs = smem;                        // 2 * KP words: every tap twice
+    float *xbuf = fs + 2 * KP;               // 2 x [32 row pairs x SX], SX = words per row pair
+    const int tile_words = (kFir2Rows / 2) * sh.SX;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+
+    for (int i = threadIdx.x; i < KP; i += blockDim.x) {
+        const float v = i < K ? filt[i] : 0.0f;
+        fs[2 * i] = v;
+        fs[2 * i + 1] = v;
+    }
+
+    // asynchronous copy of one input tile, 4 bytes per lane per copy: warp w fills rows w,
+    // w+nwarps, ...; a warp instruction covers 32 consecutive samples of one row.  Samples
+    // outside the row (or rows outside the array) become zeros.  Which of a lane's columns lie
+    // inside [0, T) is the same for every row of the tile and is worked out once per tile.
+    const unsigned xbuf_saddr = (unsigned)__cvta_generic_to_shared(xbuf);
+    auto fill = [&](int buf, int64_t tile) {
+        const int64_t rb = tile / sh.ttiles;
+        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        const int64_t row0 = rb * kFir2Rows;
+        const int64_t nrow = rows - row0;
+        const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
+        constexpr int kCols = (kFir2MaxSamples + 31) / 32;     // 14
+        int goff[kCols], nbytes[kCols];
+#pragma unroll
+        for (int k = 0; k < kCols; ++k) {
+            const int pcol = lane + 32 * k;
+            const int gt = g0 + pcol;
+            const bool ok = gt >= 0 && gt < T;
+            goff[k] = ok ? gt : 0;
+            nbytes[k] = pcol < WX ? (ok ? 4 : 0) : -1;
+        }
+        for (int r = warp; r < kFir2Rows; r += nwarps) {
+            const bool row_ok = r < nrow;
+            const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+            const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + (r >> 1) * sh.SX + (r & 1) + 2 * lane);
+#pragma unroll
+            for (int k = 0; k < kCols; ++k) {
+                if (nbytes[k] < 0) continue;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n"
+                             ::"r"(dst + 256u * k), "l"(src + goff[k]), "r"(row_ok ? nbytes[k] : 0) : "memory");
+            }
+        }
+        cp_async_commit();
+    };
+
+    const int groups = K >> 2;          // full groups of 4 taps
+    const int tail = K & 3;
+    constexpr unsigned step = DIR < 0 ? 0u - 32u : 32u;   // bytes the window moves per group (mod 2^32)
+    const unsigned fs_addr = (unsigned)__cvta_generic_to_shared(fs);
+
+    int64_t tile = blockIdx.x;
+    if (tile < ntiles) fill(0, tile);
+    for (int it = 0; tile < ntiles; tile += gridDim.x, ++it) {
+        cp_async_wait<0>();
+        __syncthreads();                 // this tile has landed; the other buffer is free again
+        const int64_t next = tile + gridDim.x;
+        if (next < ntiles) fill((it + 1) & 1, next);
+
+        const int64_t rb = tile / sh.ttiles;
+        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        const int64_t rowA = rb * kFir2Rows + 2 * lane;
+        // byte address of tile position 0 of this lane's row pair
+        const unsigned xrow = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + lane * sh.SX + 2 * (DIR < 0 ? sh.halo : 0));
+
+        for (int seg = warp; seg < sh.nseg; seg += nwarps) {
+            const int tb = seg * kFirSeg;
+            if (t0 + tb >= T) break;    // whole segment beyond the row end (warp-uniform)
+            f2 acc[kFirSeg];
+#pragma unroll
+            for (int m = 0; m < kFirSeg; ++m) acc[m] = 0ull;
+
+            // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
+            f2 w[kFirRing];
+            const unsigned x0 = xrow + 8u * (unsigned)tb - (DIR < 0 ? 32u : 0u);
+#pragma unroll
+            for (int q = 0; q < kFirWin / 2; ++q) ld2p(x0 + 16 * q, w[2 * q], w[2 * q + 1]);
+            unsigned xp = DIR < 0 ? x0 - 32 : x0 + 8 * kFirWin;    // next four sample pairs to fetch
+            unsigned fp = fs_addr;
+            f2 f[2][4];
+            ld2p(fp, f[0][0], f[0][1]);
+            ld2p(fp + 16, f[0][2], f[0][3]);
+            int g = 0;
+            for (; g + kFirPhases <= groups; g += kFirPhases) {
+                fir2_step<DIR, 0>(acc, w, f, fp + 32, xp);
+                fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step);
+                fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step);
+                fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step);
+                fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step);
+                fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step);
+                xp += kFirPhases * step;
+                fp += 32 * kFirPhases;
+            }
+            fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, groups - g, tail);
+
+            float oa[kFirSeg], ob[kFirSeg];
+#pragma unroll
+            for (int m = 0; m < kFirSeg; ++m) {
+                unpack2(acc[m], oa[m], ob[m]);
+                oa[m] *= Ts;
+                ob[m] *= Ts;
+            }
+            const int left = T - (t0 + tb);          // > 0, multiple of V
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int64_t row = rowA + h;
+                if (row >= rows) continue;
+                const float *o = h ? ob : oa;
+                float *dst = out + row * (int64_t)T + t0 + tb;
+                if (V == 4) {
+#pragma unroll
+                    for (int q = 0; q < kFirSeg / 4; ++q)
+                        if (4 * q < left)
+                            *reinterpret_cast<float4 *>(dst + 4 * q) = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                } else if (V == 2) {
+#pragma unroll
+                    for (int q = 0; q < kFirSeg / 2; ++q)
+                        if (2 * q < left) *reinterpret_cast<float2 *>(dst + 2 * q) = make_float2(o[2 * q], o[2 * q + 1]);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < kFirSeg; ++q)
+                        if (q < left) dst[q] = o[q];
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
 // Thread-per-output restatement for filters too long for the shared-memory tile.
 template <int DIR>
 __global__ void __launch_bounds__(256)
@@ -343,6 +581,74 @@ static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
     return true;
 }
 
+// Tile shape of the packed kernel (64-row tiles, one CTA per SM); false if the filter is too long.
+static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
+{
+    sh.halo = (int)(((K + 3) & ~3LL) + 8);     // taps rounded up plus two quads of look-ahead
+    const int room = kFir2MaxSamples - 2 - sh.halo;           // samples left for outputs (2 = stride padding)
+    const int nseg_max = room / kFirSeg;
+    if (nseg_max < 1) return false;
+    const int64_t segs = ceil_div(T, kFirSeg);
+    sh.ttiles = (int)ceil_div(segs, nseg_max);
+    // few rows: cut time finer so that every SM gets a tile (the halo is re-read from L2)
+    const int64_t row_blocks = ceil_div(rows, kFir2Rows);
+    const int64_t want = (int64_t)sm_count();
+    if (row_blocks * sh.ttiles < want) {
+        int64_t tt = ceil_div(want, row_blocks);
+        if (tt > segs) tt = segs;
+        if (tt > sh.ttiles) sh.ttiles = (int)tt;
+    }
+    sh.nseg = (int)ceil_div(segs, sh.ttiles);
+    sh.ttiles = (int)ceil_div(segs, sh.nseg);
+    // words per row pair: two rows interleaved, = 4 (mod 8) so that the 128-bit loads of a
+    // quarter warp fall into distinct bank groups
+    sh.SX = pad_stride(2 * (sh.nseg * kFirSeg + sh.halo));
+    // Warps per CTA: warp w runs on scheduler w % 4 and takes segments w, w+nw, ...; pick the
+    // multiple of four whose busiest scheduler has the least work, preferring fewer warps.
+    if (sh.nseg <= 8) {
+        sh.nwarps = sh.nseg;
+        return true;
+    }
+    int best_load = 1 << 30;
+    sh.nwarps = 8;
+    const int candidates[3] = {8, 12, 16};
+    for (int nw : candidates) {
+        int load[4] = {0, 0, 0, 0};
+        for (int w = 0; w < nw; ++w) load[w & 3] += (sh.nseg - w + nw - 1) / nw;
+        int worst = load[0];
+        for (int k = 1; k < 4; ++k) worst = load[k] > worst ? load[k] : worst;
+        if (worst < best_load) { best_load = worst; sh.nwarps = nw; }
+    }
+    return true;
+}
+
+static std::atomic<int> g_fir_packed{1};
+
+template <int DIR>
+static int launch_fir2(float *out, const float *in, const float *filt,
+                       int64_t rows, int64_t T, int64_t Keff, float Ts, cudaStream_t stream, bool &taken)
+{
+    FirShape sh;
+    taken = fir2_shape(rows, T, Keff, sh);
+    if (!taken) return SLAYER_B200_OK;
+    const int64_t ntiles = ceil_div(rows, kFir2Rows) * sh.ttiles;
+    const size_t smem = sizeof(float) * (2 * ((size_t)((Keff + 3) & ~3LL) + 4) + 2 * (size_t)(kFir2Rows / 2) * sh.SX);
+    const int vw = tile_vec_width(T, {out});
+    auto kern = vw == 4 ? fir2_kernel<DIR, 4> : (vw == 2 ? fir2_kernel<DIR, 2> : fir2_kernel<DIR, 1>);
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
+    // CTAs per SM: bounded by shared memory and by registers (128 per thread at most)
+    int64_t by_smem = (int64_t)(226 * 1024 / (smem + 1024));
+    int64_t by_regs = 65536 / (128 * 32 * (int64_t)sh.nwarps);
+    int64_t ctas_per_sm = by_smem < by_regs ? by_smem : by_regs;
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    int64_t grid = ctas_per_sm * (int64_t)sm_count();
+    if (grid > ntiles) grid = ntiles;
+    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles);
+    return check_launch("fir (packed) kernel launch");
+}
+
 template <int DIR>
 static int launch_fir(float *out, const float *in, const float *filt,
                       int64_t rows, int64_t T, int64_t K, float Ts, cudaStream_t stream)
@@ -354,6 +660,11 @@ static int launch_fir(float *out, const float *in, const float *filt,
         return SLAYER_B200_OK;
     }
     const int64_t Keff = K < T ? K : T;              // taps beyond the row length never contribute
+    if (g_fir_packed.load() != 0) {
+        bool taken = false;
+        const int rc = launch_fir2<DIR>(out, in, filt, rows, T, Keff, Ts, stream, taken);
+        if (taken) return rc;
+    }
     FirShape sh;
     const bool tiled = fir_shape(rows, T, Keff, sh);
     const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
@@ -390,6 +701,11 @@ static int check_fir_args(const char *name, float *out, const float *in, const f
 }
 
 }  // namespace sb200
+
+extern "C" int slayer_b200_set_fir_packed(int enable)
+{
+    return sb200::g_fir_packed.exchange(enable ? 1 : 0);
+}
 
 extern "C" int slayer_b200_conv(float *out, const float *in, const float *filter,
                                 int64_t rows, int64_t T, int64_t K, float Ts, void *stream)

@@ -33,9 +33,13 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--density", type=float, default=0.3, help="fraction of non-zero input samples")
     ap.add_argument("--neurons", type=int, default=512, help="rows per batch sample (length of the shift table)")
+    ap.add_argument("--scalar-fir", action="store_true", help="conv/corr: the scalar kernel instead of the packed one")
     args = ap.parse_args(argv)
 
     sc, lc = slayerpytorch_b200.load_ops()
+    if args.scalar_fir:
+        from slayerpytorch_b200 import capi
+        capi.set_fir_packed(False)
     dev = torch.device("cuda")
     gen = torch.Generator(device=dev).manual_seed(1)
     neurons = min(args.neurons, args.rows)

@@ -78,9 +78,19 @@ def test_shift_unaligned_buffers_take_the_scalar_path():
 
 
 # --------------------------------------------------------------------------- conv / corr
+@pytest.fixture(params=["packed", "scalar"])
+def fir_variant(request):
+    """conv / corr have two kernels that must give the same bits: the packed one (two rows per
+    lane, two-wide FMAs; the default) and the scalar one."""
+    from slayerpytorch_b200 import capi
+    before = capi.set_fir_packed(request.param == "packed")
+    yield request.param
+    capi.set_fir_packed(before)
+
+
 @pytest.mark.parametrize("T", [1, 5, 64, 300, 301, 500, 1450, 2000])
 @pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 11, 12, 13, 77, 110, 160])
-def test_conv_corr_bit_exact(T, K):
+def test_conv_corr_bit_exact(T, K, fir_variant):
     rng = np.random.RandomState(1000 * T + K)
     rows = 37 if T < 1000 else 33
     x = (rng.rand(rows, T) < 0.2).astype(np.float32) * rng.randn(rows, T).astype(np.float32)
@@ -91,7 +101,7 @@ def test_conv_corr_bit_exact(T, K):
         assert_close_or_equal(G.host(G.c_conv(xd, fd, Ts, corr=True)), co.corr(x, f, Ts))
 
 
-def test_conv_delay_gradient_filter():
+def test_conv_delay_gradient_filter(fir_variant):
     """K = 2 difference filter of the delay gradient (src/slayer.py:950-953): (x[t-1]-x[t])/Ts."""
     rng = np.random.RandomState(3)
     x = rng.randn(2, 5, 1, 1, 300).astype(np.float32)
@@ -104,7 +114,7 @@ def test_conv_delay_gradient_filter():
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)
 
 
-def test_conv_spike_input_and_psp_kernel(golden_dir):
+def test_conv_spike_input_and_psp_kernel(golden_dir, fir_variant):
     g = np.load(golden_dir + "/ref_python.npz")
     for tag, kern in (("psp_Ts1", "srm_Ts1_srmKernel"), ("psp_kat", "srm_kat_srmKernel")):
         x, y, Ts = g[tag + "_in"], g[tag + "_out"], float(g[tag + "_Ts"])
@@ -113,25 +123,37 @@ def test_conv_spike_input_and_psp_kernel(golden_dir):
         assert_close_or_equal(got, co.conv(x, g[kern], Ts))
 
 
-def test_conv_many_rows_and_row_remainders():
+def test_conv_many_rows_and_row_remainders(fir_variant):
     rng = np.random.RandomState(5)
     f = rng.randn(77).astype(np.float32)
     fd = G.dev(f)
-    for rows in (1, 31, 32, 33, 1000):
+    for rows in (1, 2, 31, 32, 33, 63, 64, 65, 127, 1000):
         x = rng.randn(rows, 300).astype(np.float32)
         assert_close_or_equal(G.host(G.c_conv(G.dev(x), fd, 1.0)), co.conv(x, f, 1.0))
         assert_close_or_equal(G.host(G.c_conv(G.dev(x), fd, 1.0, corr=True)), co.corr(x, f, 1.0))
 
 
-def test_conv_unaligned_buffer():
+def test_conv_unaligned_buffer(fir_variant):
     rng = np.random.RandomState(8)
-    flat = rng.randn(9 * 300 + 1).astype(np.float32)
     f = rng.randn(11).astype(np.float32)
-    xd = G.dev(flat)[1:].view(9, 300)
-    assert_close_or_equal(G.host(G.c_conv(xd, G.dev(f), 1.0)), co.conv(flat[1:].reshape(9, 300), f, 1.0))
+    for rows, T in ((9, 300), (70, 302), (5, 77)):
+        flat = rng.randn(rows * T + 3).astype(np.float32)
+        base = G.dev(flat)
+        for off in (1, 2, 3):
+            xd = base[off:off + rows * T].view(rows, T)
+            want = co.conv(flat[off:off + rows * T].reshape(rows, T), f, 1.0)
+            assert_close_or_equal(G.host(G.c_conv(xd, G.dev(f), 1.0)), want)
+            # input aligned, output not
+            out = torch.full((rows * T + 3,), float("nan"), device="cuda")
+            ov = out[off:off + rows * T].view(rows, T)
+            xa = G.dev(flat[off:off + rows * T].reshape(rows, T))
+            from slayerpytorch_b200 import capi
+            capi.call("slayer_b200_conv", G.ptr(ov), G.ptr(xa), G.ptr(G.dev(f)), rows, T, f.size, 1.0, G.stream())
+            assert_close_or_equal(G.host(ov), want)
+            assert torch.isnan(out[:off]).all() and torch.isnan(out[off + rows * T:]).all()
 
 
-def test_conv_very_long_filter_fallback():
+def test_conv_very_long_filter_fallback(fir_variant):
     rng = np.random.RandomState(9)
     x = rng.randn(3, 2500).astype(np.float32)
     f = (rng.randn(2300) * 0.05).astype(np.float32)
