@@ -222,6 +222,15 @@ int slayer_b200_set_tma(int enable);
  */
 int slayer_b200_set_fir_packed(int enable);
 
+/*
+ * Enable (non-zero, the default) or disable the zero-skipping path of the packed conv / corr
+ * kernel; returns the previous setting.  Enabled, the kernel looks at its input tiles and, where
+ * most sample positions are zero in all 64 rows of a tile (spike tensors), only visits the
+ * positions that are not; the results are the same bits (a zero sample leaves every sum it
+ * enters unchanged).  It has no counterpart in the reference.
+ */
+int slayer_b200_set_fir_skip_zeros(int enable);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,6 +36,7 @@ SYMBOLS = {
     "slayer_b200_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "slayer_b200_set_tma": (_int, [_int]),
     "slayer_b200_set_fir_packed": (_int, [_int]),
+    "slayer_b200_set_fir_skip_zeros": (_int, [_int]),
 }
 
 _lib = None
@@ -83,6 +84,11 @@ def device_status():
 def set_fir_packed(enable):
     """Enable/disable the packed conv / corr kernel; returns the previous setting."""
     return bool(load().slayer_b200_set_fir_packed(1 if enable else 0))
+
+
+def set_fir_skip_zeros(enable):
+    """Enable/disable the zero-skipping path of the packed conv / corr kernel; returns the previous setting."""
+    return bool(load().slayer_b200_set_fir_skip_zeros(1 if enable else 0))
 
 
 def set_tma(enable):

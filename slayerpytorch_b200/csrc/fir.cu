@@ -281,6 +281,8 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
 }
 
 
+typedef unsigned long long f2;      // two packed fp32 values
+
 // ---------------------------------------------------------------------------------------
 // Packed variant: two rows per lane, two fp32 FMAs per instruction.
 //
@@ -301,10 +303,19 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
 // of global memory), which also makes the fill indifferent to the alignment of the input.
 // One CTA per SM (two buffers of up to 64 rows x 428 samples), warps take 16-sample segments.
 // ---------------------------------------------------------------------------------------
-typedef unsigned long long f2;
-
 constexpr int kFir2Rows = 64;
-constexpr int kFir2MaxSamples = 428;     // staged samples per row: 2 buffers x 32 pairs x 2 x 428 words fit one SM
+constexpr int kFir2MaxSamples = 424;     // staged samples per row: 2 buffers x 32 pairs x 2 x 424 words fit one SM
+constexpr int kFir2MaskWords = 16;       // one bit per staged sample position (>= kFir2MaxSamples / 32, padded)
+constexpr int kFir2ScanEvery = 8;        // dense mode: look at every 8th tile for zeros
+constexpr int kFir2SparsePercent = 45;   // a tile runs the zero-skipping path below this share of live positions
+
+// 64-bit load of one (row A, row B) sample pair
+__device__ __forceinline__ f2 ld1p(unsigned saddr)
+{
+    f2 v;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(saddr));
+    return v;
+}
 
 __device__ __forceinline__ void ld2p(unsigned saddr, f2 &a, f2 &b)
 {
@@ -370,18 +381,77 @@ __device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing],
         fir2_rest<DIR, PH + 1>(acc, w, f, fp_next + 32, xp + (DIR < 0 ? 0u - 32u : 32u), left - 1, tail);
 }
 
+
+// Zero-skipping form of one 16-output segment.  Spike tensors are mostly zeros, and a zero
+// sample leaves every accumulator it is multiplied into unchanged, so only the sample positions
+// where at least one of the warp's 64 rows is non-zero need any arithmetic.  `colmask` holds one
+// bit per staged sample position of the tile (bit set = some row is non-zero there).  The live
+// positions of the segment's window are visited in the order that keeps every output's chain in
+// ascending tap order (conv: newest sample first; corr: oldest first); each costs 16 packed FMAs
+// with the 16 consecutive taps that connect it to the segment's outputs.  Taps outside [0, K)
+// are skipped by predicate, not multiplied as zeros, so non-finite samples behave as in the
+// dense form.  pos0 = tile position of the window's first sample.
+template <int DIR>
+__device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const unsigned *colmask, unsigned xrow_tile0,
+                                                    unsigned fsA_addr, unsigned fsB_addr, int pos0, int K)
+{
+    // window: positions pos0 .. pos0 + K + 14 (K - 1 past samples + 16 outputs)
+    const int npos = K + kFirSeg - 1;
+    // conv walks positions downwards from the last one, corr upwards from the first one
+    for (int done = 0; done < npos;) {
+        // next live position at or after `done` in walking order
+        const int p = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;
+        const int word = p >> 5, bit = p & 31;
+        unsigned m = colmask[word];
+        int skip;
+        if (DIR < 0) {
+            m &= bit == 31 ? 0xffffffffu : ((2u << bit) - 1u);         // bits 0 .. bit
+            skip = m ? bit - (31 - __clz(m)) : bit + 1;                // positions to step over
+        } else {
+            m &= 0xffffffffu << bit;                                   // bits bit .. 31
+            skip = m ? (__ffs(m) - 1) - bit : 32 - bit;
+        }
+        done += skip;
+        if (!m || done >= npos) continue;
+        const int q = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;  // the live position
+        ++done;
+        const f2 x = ld1p(xrow_tile0 + 8u * (unsigned)q);
+        // conv: output m takes tap (pos0 + K - 1 + m) - q;  corr: tap q - pos0 - m
+        const int a = DIR < 0 ? pos0 + K - 1 - q : q - pos0 - (kFirSeg - 1);      // lowest tap index of the 16
+        const int n0 = a + kFirSeg;                                               // index into the padded table (>= 1)
+        const unsigned tp = ((n0 & 1) ? fsB_addr + 8u * (unsigned)(n0 - 1) : fsA_addr + 8u * (unsigned)n0);
+        f2 f[kFirSeg];
+#pragma unroll
+        for (int k = 0; k < kFirSeg / 2; ++k) ld2p(tp + 16 * k, f[2 * k], f[2 * k + 1]);
+        if (a >= 0 && a + kFirSeg <= K) {
+#pragma unroll
+            for (int mm = 0; mm < kFirSeg; ++mm) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
+        } else {
+#pragma unroll
+            for (int mm = 0; mm < kFirSeg; ++mm) {
+                const int tap = a + (DIR < 0 ? mm : kFirSeg - 1 - mm);
+                if (tap >= 0 && tap < K) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
+            }
+        }
+    }
+}
+
 // V: width of the global stores in floats (4, 2 or 1; T % V == 0 and `out` aligned to 4*V bytes).
 template <int DIR, int V>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, 1)
 fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles)
+            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, bool sparse_ok)
 {
     extern __shared__ __align__(16) float smem[];
     const int Tt = sh.nseg * kFirSeg;
     const int WX = Tt + sh.halo;
     const int KP = ((K + 3) & ~3) + 4;       // taps, zero padded; one spare quad for the look-ahead load
+    const int KS = ((K + 3) & ~3) + 2 * kFirSeg;   // taps with 16 zeros in front and at least 16 behind (sparse path)
     float *fs = smem;                        // 2 * KP words: every tap twice
-    float *xbuf = fs + 2 * KP;               // 2 x [32 row pairs x SX], SX = words per row pair
+    float *fsA = fs + 2 * KP;                // 2 * KS words: padded taps, every tap twice
+    float *fsB = fsA + 2 * KS;               // the same, one tap further on (16-byte alignment for odd starts)
+    unsigned *colmask = reinterpret_cast<unsigned *>(fsB + 2 * KS);     // kFir2MaskWords words
+    float *xbuf = reinterpret_cast<float *>(colmask + kFir2MaskWords);  // 2 x [32 row pairs x SX], SX = words per row pair
     const int tile_words = (kFir2Rows / 2) * sh.SX;
 
     const int lane = threadIdx.x & 31;
@@ -392,6 +462,14 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
         const float v = i < K ? filt[i] : 0.0f;
         fs[2 * i] = v;
         fs[2 * i + 1] = v;
+    }
+    for (int n = threadIdx.x; n < KS; n += blockDim.x) {       // padded tap n = tap n - 16
+        const float a = (n >= kFirSeg && n - kFirSeg < K) ? filt[n - kFirSeg] : 0.0f;
+        const float b = (n + 1 >= kFirSeg && n + 1 - kFirSeg < K) ? filt[n + 1 - kFirSeg] : 0.0f;
+        fsA[2 * n] = a;
+        fsA[2 * n + 1] = a;
+        fsB[2 * n] = b;
+        fsB[2 * n + 1] = b;
     }
 
     // asynchronous copy of one input tile, 4 bytes per lane per copy: warp w fills rows w,
@@ -433,6 +511,11 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
     const int tail = K & 3;
     constexpr unsigned step = DIR < 0 ? 0u - 32u : 32u;   // bytes the window moves per group (mod 2^32)
     const unsigned fs_addr = (unsigned)__cvta_generic_to_shared(fs);
+    const unsigned fsA_addr = (unsigned)__cvta_generic_to_shared(fsA);
+    const unsigned fsB_addr = (unsigned)__cvta_generic_to_shared(fsB);
+    const int mask_words = (WX + 31) >> 5;
+    const bool may_skip = sparse_ok && K >= 8;
+    bool sparse = false;                 // the previous scanned tile was mostly zeros (same value in every thread)
 
     int64_t tile = blockIdx.x;
     if (tile < ntiles) fill(0, tile);
@@ -446,7 +529,34 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
         const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
         const int64_t rowA = rb * kFir2Rows + 2 * lane;
         // byte address of tile position 0 of this lane's row pair
-        const unsigned xrow = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + lane * sh.SX + 2 * (DIR < 0 ? sh.halo : 0));
+        const unsigned xtile0 = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + lane * sh.SX);
+        const unsigned xrow = xtile0 + 8u * (unsigned)(DIR < 0 ? sh.halo : 0);
+
+        // Which sample positions hold a non-zero in any of the 64 rows?  Looked at for every tile
+        // while tiles are sparse, else for one tile in kFir2ScanEvery.  Lane = position, loop over
+        // the row pairs: the OR of the magnitude bits of both rows, one ballot per 32 positions.
+        if (may_skip && (sparse || (it % kFir2ScanEvery) == 0)) {
+            for (int wd = warp; wd < mask_words; wd += nwarps) {
+                const int pos = 32 * wd + lane;
+                unsigned bits = 0u;
+                if (pos < WX) {
+                    const unsigned col = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words) + 8u * (unsigned)pos;
+#pragma unroll 8
+                    for (int pr = 0; pr < kFir2Rows / 2; ++pr) {
+                        const f2 v = ld1p(col + 4u * (unsigned)(pr * sh.SX));
+                        bits |= (unsigned)v | (unsigned)(v >> 32);
+                    }
+                }
+                const unsigned live = __ballot_sync(0xffffffffu, (bits & 0x7fffffffu) != 0u);
+                if (lane == 0) colmask[wd] = live;
+            }
+            __syncthreads();
+            int live = 0;
+            for (int wd = 0; wd < mask_words; ++wd) live += __popc(colmask[wd]);
+            sparse = live * 100 < kFir2SparsePercent * WX;
+        } else if (may_skip) {
+            sparse = false;
+        }
 
         for (int seg = warp; seg < sh.nseg; seg += nwarps) {
             const int tb = seg * kFirSeg;
@@ -455,28 +565,35 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
 #pragma unroll
             for (int m = 0; m < kFirSeg; ++m) acc[m] = 0ull;
 
-            // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
-            f2 w[kFirRing];
-            const unsigned x0 = xrow + 8u * (unsigned)tb - (DIR < 0 ? 32u : 0u);
+            if (sparse) {
+                // window of the segment in tile positions: conv starts K - 1 samples before the
+                // first output (tile position halo + tb), corr at the first output
+                fir2_sparse_segment<DIR>(acc, colmask, xtile0, fsA_addr, fsB_addr,
+                                         DIR < 0 ? sh.halo + tb - (K - 1) : tb, K);
+            } else {
+                // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
+                f2 w[kFirRing];
+                const unsigned x0 = xrow + 8u * (unsigned)tb - (DIR < 0 ? 32u : 0u);
 #pragma unroll
-            for (int q = 0; q < kFirWin / 2; ++q) ld2p(x0 + 16 * q, w[2 * q], w[2 * q + 1]);
-            unsigned xp = DIR < 0 ? x0 - 32 : x0 + 8 * kFirWin;    // next four sample pairs to fetch
-            unsigned fp = fs_addr;
-            f2 f[2][4];
-            ld2p(fp, f[0][0], f[0][1]);
-            ld2p(fp + 16, f[0][2], f[0][3]);
-            int g = 0;
-            for (; g + kFirPhases <= groups; g += kFirPhases) {
-                fir2_step<DIR, 0>(acc, w, f, fp + 32, xp);
-                fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step);
-                fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step);
-                fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step);
-                fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step);
-                fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step);
-                xp += kFirPhases * step;
-                fp += 32 * kFirPhases;
+                for (int q = 0; q < kFirWin / 2; ++q) ld2p(x0 + 16 * q, w[2 * q], w[2 * q + 1]);
+                unsigned xp = DIR < 0 ? x0 - 32 : x0 + 8 * kFirWin;    // next four sample pairs to fetch
+                unsigned fp = fs_addr;
+                f2 f[2][4];
+                ld2p(fp, f[0][0], f[0][1]);
+                ld2p(fp + 16, f[0][2], f[0][3]);
+                int g = 0;
+                for (; g + kFirPhases <= groups; g += kFirPhases) {
+                    fir2_step<DIR, 0>(acc, w, f, fp + 32, xp);
+                    fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step);
+                    fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step);
+                    fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step);
+                    fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step);
+                    fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step);
+                    xp += kFirPhases * step;
+                    fp += 32 * kFirPhases;
+                }
+                fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, groups - g, tail);
             }
-            fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, groups - g, tail);
 
             float oa[kFirSeg], ob[kFirSeg];
 #pragma unroll
@@ -623,6 +740,7 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
 }
 
 static std::atomic<int> g_fir_packed{1};
+static std::atomic<int> g_fir_skip_zeros{1};
 
 template <int DIR>
 static int launch_fir2(float *out, const float *in, const float *filt,
@@ -632,7 +750,8 @@ static int launch_fir2(float *out, const float *in, const float *filt,
     taken = fir2_shape(rows, T, Keff, sh);
     if (!taken) return SLAYER_B200_OK;
     const int64_t ntiles = ceil_div(rows, kFir2Rows) * sh.ttiles;
-    const size_t smem = sizeof(float) * (2 * ((size_t)((Keff + 3) & ~3LL) + 4) + 2 * (size_t)(kFir2Rows / 2) * sh.SX);
+    const size_t kp = (size_t)((Keff + 3) & ~3LL);
+    const size_t smem = sizeof(float) * (2 * (kp + 4) + 4 * (kp + 2 * kFirSeg) + kFir2MaskWords + 2 * (size_t)(kFir2Rows / 2) * sh.SX);
     const int vw = tile_vec_width(T, {out});
     auto kern = vw == 4 ? fir2_kernel<DIR, 4> : (vw == 2 ? fir2_kernel<DIR, 2> : fir2_kernel<DIR, 1>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);
@@ -645,7 +764,8 @@ static int launch_fir2(float *out, const float *in, const float *filt,
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     int64_t grid = ctas_per_sm * (int64_t)sm_count();
     if (grid > ntiles) grid = ntiles;
-    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles);
+    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles,
+                                                           g_fir_skip_zeros.load() != 0);
     return check_launch("fir (packed) kernel launch");
 }
 
@@ -705,6 +825,11 @@ static int check_fir_args(const char *name, float *out, const float *in, const f
 extern "C" int slayer_b200_set_fir_packed(int enable)
 {
     return sb200::g_fir_packed.exchange(enable ? 1 : 0);
+}
+
+extern "C" int slayer_b200_set_fir_skip_zeros(int enable)
+{
+    return sb200::g_fir_skip_zeros.exchange(enable ? 1 : 0);
 }
 
 extern "C" int slayer_b200_conv(float *out, const float *in, const float *filter,

@@ -65,10 +65,16 @@ class spikeLoss(torch.nn.Module):
 
 
 class spikeClassifier:
-    """Class label = the output neuron with the most spikes (src/spikeClassifier.py:9-20); the
-    result stays on the device of ``spike``."""
+    """Class label = the output neuron with the most spikes (src/spikeClassifier.py:9-20).
+
+    As in the reference the labels come back as a CPU tensor, so that the reference's training
+    scripts, which compare them with the CPU labels of a DataLoader
+    (``torch.sum(getClass(output) == label)``), run unchanged; the counting itself stays on the
+    device and only one index per sample crosses.  ``host=False`` keeps the result on the device
+    of ``spike`` (no synchronisation)."""
 
     @staticmethod
-    def getClass(spike):
+    def getClass(spike, host=True):
         numSpikes = torch.sum(spike, 4, keepdim=True)
-        return torch.max(numSpikes.reshape((numSpikes.shape[0], -1)), 1)[1]
+        labels = torch.max(numSpikes.reshape((numSpikes.shape[0], -1)), 1)[1]
+        return labels.cpu() if host else labels

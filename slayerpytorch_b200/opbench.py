@@ -34,12 +34,17 @@ def main(argv=None):
     ap.add_argument("--density", type=float, default=0.3, help="fraction of non-zero input samples")
     ap.add_argument("--neurons", type=int, default=512, help="rows per batch sample (length of the shift table)")
     ap.add_argument("--scalar-fir", action="store_true", help="conv/corr: the scalar kernel instead of the packed one")
+    ap.add_argument("--no-skip-zeros", action="store_true", help="conv/corr: packed kernel without its zero-skipping path")
+    ap.add_argument("--spikes", action="store_true", help="conv/corr: the input is a 0/1 spike tensor of the given density")
     args = ap.parse_args(argv)
 
     sc, lc = slayerpytorch_b200.load_ops()
     if args.scalar_fir:
         from slayerpytorch_b200 import capi
         capi.set_fir_packed(False)
+    if args.no_skip_zeros:
+        from slayerpytorch_b200 import capi
+        capi.set_fir_skip_zeros(False)
     dev = torch.device("cuda")
     gen = torch.Generator(device=dev).manual_seed(1)
     neurons = min(args.neurons, args.rows)
@@ -59,6 +64,8 @@ def main(argv=None):
          * (torch.rand(shape, device=dev, generator=gen) < args.density)).float()
     extra = {}
     restore = None
+    if args.spikes:
+        a = (torch.rand(shape, device=dev, generator=gen) < args.density).float()
     if args.op in ("conv", "corr"):
         fn = (lambda: sc.conv(a, filt, 1.0)) if args.op == "conv" else (lambda: sc.corr(a, filt, 1.0))
         extra["taps"] = int(filt.numel())

@@ -153,6 +153,52 @@ def test_conv_unaligned_buffer(fir_variant):
             assert torch.isnan(out[:off]).all() and torch.isnan(out[off + rows * T:]).all()
 
 
+@pytest.mark.parametrize("density", [0.0, 0.002, 0.01, 0.05])
+@pytest.mark.parametrize("T,K", [(300, 77), (304, 8), (1450, 110), (40, 77)])
+def test_conv_corr_on_spike_tensors_skip_zeros(density, T, K):
+    """Mostly-zero inputs take the zero-skipping path of the packed kernel (one CTA walks several
+    tiles here, so the per-tile switch between the two paths is exercised too); with the path
+    switched off the dense path runs.  Both must give the oracle's bits."""
+    from slayerpytorch_b200 import capi
+    rng = np.random.RandomState(int(density * 1e4) + T + K)
+    rows = 20000 if T <= 304 else 4200
+    x = (rng.rand(rows, T) < density).astype(np.float32)
+    x[rows // 3:rows // 3 + 700] = rng.randn(700, T).astype(np.float32)      # a dense stretch in the middle
+    x[5, 7 % T] = -0.0
+    f = rng.randn(K).astype(np.float32)
+    xd, fd = G.dev(x), G.dev(f)
+    want_conv, want_corr = co.conv(x, f, 1.0), co.corr(x, f, 1.0)
+    try:
+        for skip in (True, False):
+            capi.set_fir_skip_zeros(skip)
+            assert_close_or_equal(G.host(G.c_conv(xd, fd, 1.0)), want_conv)
+            assert_close_or_equal(G.host(G.c_conv(xd, fd, 1.0, corr=True)), want_corr)
+    finally:
+        capi.set_fir_skip_zeros(True)
+
+
+def test_conv_skip_zeros_with_non_finite_samples():
+    """An Inf or NaN sample only reaches the outputs within K taps of it, on both paths."""
+    from slayerpytorch_b200 import capi
+    rng = np.random.RandomState(11)
+    x = (rng.rand(256, 300) < 0.004).astype(np.float32)
+    x[3, 100], x[70, 5], x[200, 299], x[201, 0] = np.inf, np.nan, -np.inf, np.inf
+    f = rng.randn(77).astype(np.float32)
+    xd, fd = G.dev(x), G.dev(f)
+    got = {}
+    try:
+        for skip in (True, False):
+            capi.set_fir_skip_zeros(skip)
+            got[skip] = (G.host(G.c_conv(xd, fd, 1.0)), G.host(G.c_conv(xd, fd, 1.0, corr=True)))
+    finally:
+        capi.set_fir_skip_zeros(True)
+    for a, b in zip(got[True], got[False]):
+        np.testing.assert_array_equal(a, b)                  # NaN == NaN in this comparison
+    conv = got[True][0]
+    assert np.isfinite(conv[3, :100]).all() and not np.isfinite(conv[3, 100:177]).any() and np.isfinite(conv[3, 177:]).all()
+    np.testing.assert_array_equal(conv[4], co.conv(x[4:5], f, 1.0)[0])
+
+
 def test_conv_very_long_filter_fallback(fir_variant):
     rng = np.random.RandomState(9)
     x = rng.randn(3, 2500).astype(np.float32)

@@ -268,8 +268,12 @@ def test_device_resident_losses_equal_the_reference_losses(ref_py_on_ours, Ts, r
     import importlib
     ref_cls = importlib.import_module(ref_py_on_ours.loss.__name__.rsplit(".", 1)[0] + ".spikeClassifier").spikeClassifier
     got = ours_loss.spikeClassifier.getClass(spikes)
-    assert got.is_cuda
-    assert torch.equal(got.cpu(), ref_cls.getClass(spikes))
+    want = ref_cls.getClass(spikes)
+    assert not got.is_cuda and torch.equal(got, want)
+    # the accuracy line of the reference's training scripts (example/02_NMNIST_MLP/nmnistMLP.py:120)
+    assert int(torch.sum(got == label)) == int(torch.sum(want == label))
+    on_dev = ours_loss.spikeClassifier.getClass(spikes, host=False)
+    assert on_dev.is_cuda and torch.equal(on_dev.cpu(), want)
 
 
 def test_long_sequence_delay_network_through_the_reference_delay_layer(ours, ref_ops):
