@@ -150,6 +150,35 @@ int slayer_b200_srm_get_spikes_delayed(float *delayed, float *s_scratch, float *
                                        float theta, float Ts, void *stream);
 
 /*
+ * Bit-packed spike tensors.  A spike tensor holds two values, 0 and 1/Ts; packed, a row of T
+ * samples is ceil(T / 32) uint32 words, bit i of word w = "sample 32 w + i is a spike" (bits
+ * past T are zero): 1/32 of the bytes the fp32 form of the reference's interface moves
+ * (getSpikesKernel writes fp32 samples, src/cuda/spikeKernels.h:18-27).  pack_spikes sets a bit
+ * where s is non-zero; unpack_spikes writes `value` where a bit is set and 0 elsewhere.
+ */
+int slayer_b200_pack_spikes(uint32_t *bits, const float *s, int64_t rows, int64_t T, void *stream);
+int slayer_b200_unpack_spikes(float *s, const uint32_t *bits, int64_t rows, int64_t T, float value, void *stream);
+
+/*
+ * slayer_b200_srm_get_spikes with the spikes written in the bit-packed form above (the updated
+ * potential u is the same fp32 tensor).  Same spike positions and same u as getSpikes<float>(),
+ * src/cuda/spikeKernels.h:9-38, :54-60; 8 + 1/8 instead of 12 bytes per element.  Needs
+ * T % 4 == 0, u 16-byte aligned and nuSize <= 257; otherwise SLAYER_B200_EUNSUPPORTED (run
+ * slayer_b200_srm_get_spikes and slayer_b200_pack_spikes instead).
+ */
+int slayer_b200_srm_get_spikes_packed(uint32_t *bits, float *u, const float *nu,
+                                      int64_t rows, int64_t nuSize, int64_t T, float theta, void *stream);
+
+/*
+ * slayer_b200_conv on a bit-packed spike tensor: out = conv(unpack(bits, spike_value), filter),
+ * the same bits as the two calls (conv<float>(), src/cuda/convKernels.h:10-35, applied to the
+ * spike tensor as spikeLayer.psp does, src/slayer.py:130-142); 4 + 1/8 instead of 8 bytes per
+ * element.  SLAYER_B200_EUNSUPPORTED for filters too long for the tiled kernel.
+ */
+int slayer_b200_conv_packed(float *out, const uint32_t *bits, const float *filter,
+                            int64_t rows, int64_t T, int64_t K, float spike_value, float Ts, void *stream);
+
+/*
  * slayer_b200_srm_get_spikes without any memory allocation, for callers that cannot allocate
  * device memory: an application that has already given all device memory to its own pool, or
  * code that runs where entering the CUDA allocator is not allowed (another library's callback,
@@ -216,15 +245,16 @@ int slayer_b200_selftest_bounded_wait(int polls, void *stream);
 int slayer_b200_set_tma(int enable);
 
 /*
- * Enable (non-zero, the default) or disable the packed form of the conv / corr kernel (two
- * rows per lane, two-wide fp32 FMAs); returns the previous setting.  Disabled, the scalar
- * kernel runs, which computes the same bits.  It has no counterpart in the reference.
+ * Enable (non-zero) or disable (zero, the default) the packed form of the conv / corr kernel
+ * (two rows per lane, two-wide fp32 FMAs, zero skipping); returns the previous setting.
+ * Disabled, the scalar kernel runs; both compute the same bits.  It has no counterpart in the
+ * reference.
  */
 int slayer_b200_set_fir_packed(int enable);
 
 /*
  * Enable (non-zero, the default) or disable the zero-skipping path of the packed conv / corr
- * kernel; returns the previous setting.  Enabled, the kernel looks at its input tiles and, where
+ * kernel (it only matters where that kernel runs); returns the previous setting.  Enabled, the kernel looks at its input tiles and, where
  * most sample positions are zero in all 64 rows of a tile (spike tensors), only visits the
  * positions that are not; the results are the same bits (a zero sample leaves every sum it
  * enters unchanged).  It has no counterpart in the reference.

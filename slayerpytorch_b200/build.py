@@ -35,6 +35,7 @@ CUDA_SOURCES = {
     "loihi_spike.cu": [],
     "spike_grad.cu": [],
     "delay_grad.cu": [],
+    "packed.cu": [],
     "tma.cu": [],
 }
 HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", os.path.join(INCLUDE, "slayer_b200.h")]

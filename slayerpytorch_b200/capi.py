@@ -28,6 +28,10 @@ SYMBOLS = {
     "slayer_b200_srm_get_spikes_noalloc": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_srm_get_spikes_noalloc_status": (_int, [_i64, _i64, ctypes.POINTER(_i64)]),
     "slayer_b200_selftest_bounded_wait": (_int, [_int, _p]),
+    "slayer_b200_pack_spikes": (_int, [_p, _p, _i64, _i64, _p]),
+    "slayer_b200_unpack_spikes": (_int, [_p, _p, _i64, _i64, _f, _p]),
+    "slayer_b200_srm_get_spikes_packed": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
+    "slayer_b200_conv_packed": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_loihi_get_spikes": (_int, [_p, _p, _p, _p, _i64, _i64, _u32, _u32, _u32, _u32, _u32, _p]),
     "slayer_b200_spike_grad": (_int, [_p, _p, _p, _i64, _f, _f, _f, _p]),
     "slayer_b200_srm_get_spikes_delayed": (_int, [_p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i64, _f, _f, _p]),

@@ -8,7 +8,8 @@
 //   - the per-neuron shift covers the whole batch in one launch;
 //   - dtype is checked explicitly;
 //   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift,
-//     getSpikesDelayed and delayGrad.
+//     getSpikesDelayed, delayGrad, and the bit-packed spike operators packSpikes, unpackSpikes,
+//     getSpikesPacked and convPacked (packed tensors are int32, [..., ceil(T / 32)]).
 #include "bindings_common.h"
 
 using namespace sb200py;
@@ -214,6 +215,105 @@ static torch::Tensor delayGradCuda(torch::Tensor gradOut, torch::Tensor output, 
     return result;
 }
 
+// ---------------------------------------------------------------- bit-packed spike tensors
+static std::vector<int64_t> packed_shape(const torch::Tensor &like)
+{
+    auto shape = like.sizes().vec();
+    shape.back() = (shape.back() + 31) / 32;
+    return shape;
+}
+
+static void check_packed(const torch::Tensor &bits, const char *name)
+{
+    TORCH_CHECK(bits.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(bits.is_contiguous(), name, " must be contiguous");
+    TORCH_CHECK(bits.scalar_type() == torch::kInt32, name, " must be an int32 tensor");
+}
+
+// bit i of word w of a row = (spikes[..., 32 w + i] != 0)
+static torch::Tensor packSpikesCuda(torch::Tensor spikes)
+{
+    check_input(spikes, "spikes");
+    TORCH_CHECK(spikes.dim() >= 1, "packSpikes expects a tensor with a time dimension");
+    c10::cuda::CUDAGuard guard(spikes.device());
+    auto bits = torch::empty(packed_shape(spikes), spikes.options().dtype(torch::kInt32));
+    const int64_t T = spikes.size(-1);
+    const int64_t rows = T ? spikes.numel() / T : 0;
+    check_rc(slayer_b200_pack_spikes(reinterpret_cast<uint32_t *>(bits.data_ptr<int32_t>()), spikes.data_ptr<float>(),
+                                     rows, T, current_stream()),
+             "packSpikes");
+    return bits;
+}
+
+// fp32 view of a packed spike tensor: `value` where a bit is set, 0 elsewhere; T = row length
+static torch::Tensor unpackSpikesCuda(torch::Tensor bits, int64_t T, float value)
+{
+    check_packed(bits, "bits");
+    TORCH_CHECK(bits.dim() >= 1 && bits.size(-1) == (T + 31) / 32, "unpackSpikes: the last dimension must be ceil(T / 32)");
+    c10::cuda::CUDAGuard guard(bits.device());
+    auto shape = bits.sizes().vec();
+    shape.back() = T;
+    auto spikes = torch::empty(shape, bits.options().dtype(torch::kFloat32));
+    const int64_t words = bits.size(-1);
+    const int64_t rows = words ? bits.numel() / words : 0;
+    check_rc(slayer_b200_unpack_spikes(spikes.data_ptr<float>(), reinterpret_cast<const uint32_t *>(bits.data_ptr<int32_t>()),
+                                       rows, T, value, current_stream()),
+             "unpackSpikes");
+    return spikes;
+}
+
+// getSpikes with the spikes returned packed; d_u is updated in place like getSpikes does
+static torch::Tensor getSpikesPackedCuda(torch::Tensor d_u, const torch::Tensor &d_nu, const float theta, const float Ts)
+{
+    check_input(d_u, "d_u");
+    check_input(d_nu, "d_nu");
+    check_device(d_u, d_nu, "d_u", "d_nu");
+    TORCH_CHECK_INDEX(d_u.dim() >= 4, "getSpikesPacked expects a tensor with at least 4 dimensions (NCHWT), got ", d_u.dim());
+    c10::cuda::CUDAGuard guard(d_u.device());
+    auto bits = torch::empty(packed_shape(d_u), d_u.options().dtype(torch::kInt32));
+    const int64_t Ns = d_u.size(-1);
+    const int64_t rows = Ns ? d_u.numel() / Ns : 0;
+    const int64_t nuSize = d_nu.dim() ? d_nu.size(-1) : 1;
+    uint32_t *words = reinterpret_cast<uint32_t *>(bits.data_ptr<int32_t>());
+    int rc = slayer_b200_srm_get_spikes_packed(words, d_u.data_ptr<float>(), d_nu.data_ptr<float>(), rows, nuSize, Ns, theta,
+                                               current_stream());
+    if (rc == SLAYER_B200_EUNSUPPORTED) {       // sizes the packed kernel does not take: the two steps
+        auto d_s = torch::empty_like(d_u);
+        check_rc(slayer_b200_srm_get_spikes(d_s.data_ptr<float>(), d_u.data_ptr<float>(), d_nu.data_ptr<float>(),
+                                            rows, nuSize, Ns, theta, Ts, current_stream()),
+                 "getSpikesPacked");
+        rc = slayer_b200_pack_spikes(words, d_s.data_ptr<float>(), rows, Ns, current_stream());
+    }
+    check_rc(rc, "getSpikesPacked");
+    return bits;
+}
+
+// conv(unpackSpikes(bits, T, value), filter, Ts) without the fp32 spike tensor
+static torch::Tensor convPackedCuda(torch::Tensor bits, int64_t T, torch::Tensor filter, float Ts, float value)
+{
+    check_packed(bits, "bits");
+    check_input(filter, "filter");
+    TORCH_CHECK(bits.device().index() == filter.device().index(), "bits and filter must be in same CUDA device");
+    TORCH_CHECK(bits.dim() >= 1 && bits.size(-1) == (T + 31) / 32, "convPacked: the last dimension must be ceil(T / 32)");
+    c10::cuda::CUDAGuard guard(bits.device());
+    auto shape = bits.sizes().vec();
+    shape.back() = T;
+    auto output = torch::empty(shape, bits.options().dtype(torch::kFloat32));
+    const int64_t words = bits.size(-1);
+    const int64_t rows = words ? bits.numel() / words : 0;
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(bits.data_ptr<int32_t>());
+    int rc = slayer_b200_conv_packed(output.data_ptr<float>(), w, filter.data_ptr<float>(), rows, T, filter.numel(), value, Ts,
+                                     current_stream());
+    if (rc == SLAYER_B200_EUNSUPPORTED) {       // very long filter: the two steps
+        auto spikes = torch::empty_like(output);
+        check_rc(slayer_b200_unpack_spikes(spikes.data_ptr<float>(), w, rows, T, value, current_stream()), "convPacked");
+        rc = slayer_b200_conv(output.data_ptr<float>(), spikes.data_ptr<float>(), filter.data_ptr<float>(), rows, T,
+                              filter.numel(), Ts, current_stream());
+    }
+    check_rc(rc, "convPacked");
+    return output;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
     m.def("getSpikes", &getSpikesCuda, "Get spikes (CUDA)");
@@ -229,5 +329,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("spikeGrad_", &spikeGradInplaceCuda, "In-place variant of spikeGrad (overwrites gradOutput)");
     m.def("spikeGradShift", &spikeGradShiftCuda, "Surrogate gradient of the time-shifted gradient in one pass (CUDA)");
     m.def("delayGrad", &delayGradCuda, "Ts * sum over batch and time of gradOutput * d(output)/dt per neuron (CUDA)");
+    m.def("packSpikes", &packSpikesCuda, "Spike tensor -> bit-packed int32 words, ceil(T / 32) per row (CUDA)");
+    m.def("unpackSpikes", &unpackSpikesCuda, "Bit-packed spike tensor -> fp32 (value where a bit is set) (CUDA)");
+    m.def("getSpikesPacked", &getSpikesPackedCuda, "Get spikes, returned bit-packed (CUDA)");
+    m.def("convPacked", &convPackedCuda, "Convolution in time of a bit-packed spike tensor (CUDA)");
     m.attr("backend") = "slayer_b200";
 }

@@ -6,9 +6,10 @@
 // output loop, so results are reproducible bit for bit whatever the tiling.  Samples outside
 // the row enter the chain as +0, which leaves the accumulator unchanged for finite taps.
 //
-// Two kernels compute the same bits.  fir2_kernel (further down, the default) packs two rows
-// per lane into two-wide FMAs; fir_kernel, described next, is the scalar form and the fallback
-// (slayer_b200_set_fir_packed(0) selects it).
+// Two kernels compute the same bits.  fir_kernel, described next, is the scalar form and the
+// default.  fir2_kernel (further down) packs two rows per lane into two-wide FMAs, skips the
+// zeros of spike tensors and can read bit-packed spike tensors; slayer_b200_set_fir_packed(1)
+// selects it for conv / corr, and slayer_b200_conv_packed always runs it.
 //
 // Cost: 8 algorithmic bytes and 2K flops per element.  For K above ~47 taps the fp32 FMA
 // pipes, not HBM, bound the kernel, so the design goal is to keep those pipes fed:
@@ -289,32 +290,48 @@ typedef unsigned long long f2;      // two packed fp32 values
 // fma.rn.ftz.f32x2 performs two independent single-precision fused multiply-adds on the halves
 // of 64-bit registers; each half rounds exactly like the scalar instruction, so results keep
 // their bits.  The FMA pipe does the same number of lane-operations per clock either way, but
-// the packed form needs half the issue slots, which leaves room for the shared-memory loads
-// and address arithmetic that otherwise compete with the FMAs for issue.  Every operand has to
-// be a register pair, so the data is arranged to make the pairs natural:
-//   - a lane owns TWO rows (2l, 2l+1 of a 64-row tile); the tile in shared memory interleaves
-//     the two rows sample by sample (A0 B0 A1 B1 ...), so one 128-bit load yields two ready
-//     (A_t, B_t) pairs and the sliding window is a ring of pairs;
+// the packed form needs half the issue slots, which leaves room for the shared-memory loads,
+// the register moves and the address arithmetic that otherwise compete with the FMAs for issue.
+// Every operand has to be a register pair:
+//   - a lane owns TWO rows (l and l + 32 of a 64-row tile); the sliding window is a ring of
+//     (row A, row B) sample pairs, refilled per group of four taps by one 128-bit load from each
+//     row and four register-pair moves;
 //   - taps sit in shared memory duplicated (f0 f0 f1 f1 ...), one 128-bit broadcast load
 //     yields two (f, f) pairs;
 //   - accumulators are pairs (outA[m], outB[m]).
-// No re-pairing moves are needed.  The interleave is produced by the tile fill itself: 4-byte
-// cp.async copies, 32 consecutive samples of one row per warp instruction (coalesced 128 bytes
-// of global memory), which also makes the fill indifferent to the alignment of the input.
+// The tile in shared memory has the layout of the scalar kernel (one row after the other, row
+// stride = 4 mod 8 words, filled by 16-byte cp.async), with 64 rows instead of 32.
 // One CTA per SM (two buffers of up to 64 rows x 428 samples), warps take 16-sample segments.
 // ---------------------------------------------------------------------------------------
 constexpr int kFir2Rows = 64;
-constexpr int kFir2MaxSamples = 424;     // staged samples per row: 2 buffers x 32 pairs x 2 x 424 words fit one SM
+constexpr int kFir2MaxSamples = 428;     // staged samples per row: 2 buffers x 64 rows x 428 words fit one SM
 constexpr int kFir2MaskWords = 16;       // one bit per staged sample position (>= kFir2MaxSamples / 32, padded)
 constexpr int kFir2ScanEvery = 8;        // dense mode: look at every 8th tile for zeros
 constexpr int kFir2SparsePercent = 45;   // a tile runs the zero-skipping path below this share of live positions
 
-// 64-bit load of one (row A, row B) sample pair
-__device__ __forceinline__ f2 ld1p(unsigned saddr)
+__device__ __forceinline__ f2 pack2(float lo, float hi)
 {
-    f2 v;
-    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(saddr));
+    f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ float ld1(unsigned saddr)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr));
     return v;
+}
+
+// four (row A, row B) sample pairs from the two rows of a lane: xa = address in row A, the
+// same samples of row B lie `rowb` bytes further on
+__device__ __forceinline__ void ld4p(unsigned xa, unsigned rowb, f2 &p0, f2 &p1, f2 &p2, f2 &p3)
+{
+    const float4 a = ld4(xa), b = ld4(xa + rowb);
+    p0 = pack2(a.x, b.x);
+    p1 = pack2(a.y, b.y);
+    p2 = pack2(a.z, b.z);
+    p3 = pack2(a.w, b.w);
 }
 
 __device__ __forceinline__ void ld2p(unsigned saddr, f2 &a, f2 &b)
@@ -358,11 +375,10 @@ __device__ __forceinline__ void fir2_group_n(f2 (&acc)[kFirSeg], const f2 (&w)[k
 // group: four sample pairs into the free ring quad, four tap pairs into the idle tap quad.
 template <int DIR, int PH>
 __device__ __forceinline__ void fir2_step(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing], f2 (&f)[2][4],
-                                          unsigned fp_next, unsigned xp)
+                                          unsigned fp_next, unsigned xp, unsigned rowb)
 {
     constexpr int base = win_reg<DIR, PH>(DIR < 0 ? -4 + kFirRing : kFirWin);
-    ld2p(xp, w[base], w[base + 1]);
-    ld2p(xp + 16, w[base + 2], w[base + 3]);
+    ld4p(xp, rowb, w[base], w[base + 1], w[base + 2], w[base + 3]);
     ld2p(fp_next, f[(PH + 1) & 1][0], f[(PH + 1) & 1][1]);
     ld2p(fp_next + 16, f[(PH + 1) & 1][2], f[(PH + 1) & 1][3]);
     fir2_group<DIR, PH, 4>(acc, w, f[PH & 1]);
@@ -370,15 +386,15 @@ __device__ __forceinline__ void fir2_step(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing],
 
 template <int DIR, int PH>
 __device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing], f2 (&f)[2][4],
-                                          unsigned fp_next, unsigned xp, int left, int tail)
+                                          unsigned fp_next, unsigned xp, unsigned rowb, int left, int tail)
 {
     if (left == 0) {
         if (tail) fir2_group_n<DIR, PH>(acc, w, f[PH & 1], tail);
         return;
     }
-    fir2_step<DIR, PH>(acc, w, f, fp_next, xp);
+    fir2_step<DIR, PH>(acc, w, f, fp_next, xp, rowb);
     if constexpr (PH + 1 < kFirPhases)
-        fir2_rest<DIR, PH + 1>(acc, w, f, fp_next + 32, xp + (DIR < 0 ? 0u - 32u : 32u), left - 1, tail);
+        fir2_rest<DIR, PH + 1>(acc, w, f, fp_next + 32, xp + (DIR < 0 ? 0u - 16u : 16u), rowb, left - 1, tail);
 }
 
 
@@ -392,7 +408,7 @@ __device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing],
 // are skipped by predicate, not multiplied as zeros, so non-finite samples behave as in the
 // dense form.  pos0 = tile position of the window's first sample.
 template <int DIR>
-__device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const unsigned *colmask, unsigned xrow_tile0,
+__device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const unsigned *colmask, unsigned xrow_tile0, unsigned rowb,
                                                     unsigned fsA_addr, unsigned fsB_addr, int pos0, int K)
 {
     // window: positions pos0 .. pos0 + K + 14 (K - 1 past samples + 16 outputs)
@@ -415,7 +431,7 @@ __device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const un
         if (!m || done >= npos) continue;
         const int q = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;  // the live position
         ++done;
-        const f2 x = ld1p(xrow_tile0 + 8u * (unsigned)q);
+        const f2 x = pack2(ld1(xrow_tile0 + 4u * (unsigned)q), ld1(xrow_tile0 + rowb + 4u * (unsigned)q));
         // conv: output m takes tap (pos0 + K - 1 + m) - q;  corr: tap q - pos0 - m
         const int a = DIR < 0 ? pos0 + K - 1 - q : q - pos0 - (kFirSeg - 1);      // lowest tap index of the 16
         const int n0 = a + kFirSeg;                                               // index into the padded table (>= 1)
@@ -436,11 +452,14 @@ __device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const un
     }
 }
 
-// V: width of the global stores in floats (4, 2 or 1; T % V == 0 and `out` aligned to 4*V bytes).
-template <int DIR, int V>
+// V: width of the global accesses in floats (4, 2 or 1; T % V == 0 and both `in` (unless PK) and
+// `out` aligned to 4*V bytes).
+// PK: the input is a bit-packed spike tensor (`in` points to 32-bit words, ceil(T / 32) per row,
+// bit i of word w = sample 32 w + i is `spike_value`, else 0); the tile fill expands the bits.
+template <int DIR, int V, bool PK = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, 1)
 fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, bool sparse_ok)
+            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, bool sparse_ok, float spike_value)
 {
     extern __shared__ __align__(16) float smem[];
     const int Tt = sh.nseg * kFirSeg;
@@ -451,8 +470,9 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
     float *fsA = fs + 2 * KP;                // 2 * KS words: padded taps, every tap twice
     float *fsB = fsA + 2 * KS;               // the same, one tap further on (16-byte alignment for odd starts)
     unsigned *colmask = reinterpret_cast<unsigned *>(fsB + 2 * KS);     // kFir2MaskWords words
-    float *xbuf = reinterpret_cast<float *>(colmask + kFir2MaskWords);  // 2 x [32 row pairs x SX], SX = words per row pair
-    const int tile_words = (kFir2Rows / 2) * sh.SX;
+    float *xbuf = reinterpret_cast<float *>(colmask + kFir2MaskWords);  // 2 x [64 rows x SX]
+    const int tile_words = kFir2Rows * sh.SX;
+    const unsigned rowb = 4u * (unsigned)(32 * sh.SX);      // bytes from a lane's row A to its row B
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -472,10 +492,10 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
         fsB[2 * n + 1] = b;
     }
 
-    // asynchronous copy of one input tile, 4 bytes per lane per copy: warp w fills rows w,
-    // w+nwarps, ...; a warp instruction covers 32 consecutive samples of one row.  Samples
-    // outside the row (or rows outside the array) become zeros.  Which of a lane's columns lie
-    // inside [0, T) is the same for every row of the tile and is worked out once per tile.
+    // asynchronous copy of one input tile: warp w fills rows w, w+nwarps, ... from contiguous
+    // global segments; samples outside the row (or rows outside the array) become zeros.  With
+    // 16-byte accesses a lane copies at most four chunks per row, and which of them lie inside
+    // [0, T) is the same for every row of the tile, so that is worked out once per tile.
     const unsigned xbuf_saddr = (unsigned)__cvta_generic_to_shared(xbuf);
     auto fill = [&](int buf, int64_t tile) {
         const int64_t rb = tile / sh.ttiles;
@@ -483,25 +503,60 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
         const int64_t row0 = rb * kFir2Rows;
         const int64_t nrow = rows - row0;
         const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
-        constexpr int kCols = (kFir2MaxSamples + 31) / 32;     // 14
-        int goff[kCols], nbytes[kCols];
+        if constexpr (PK) {
+            // packed input: a lane fetches the word that holds its sample (neighbouring lanes share
+            // it) and stores the expanded sample; ordinary stores, ordered by the tile barrier
+            constexpr int kCols = (kFir2MaxSamples + 31) / 32;     // 14
+            const unsigned *words_in = reinterpret_cast<const unsigned *>(in);
+            const int words = (T + 31) >> 5;
+            for (int r = warp; r < kFir2Rows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const unsigned *src = words_in + (row0 + (row_ok ? r : 0)) * (int64_t)words;
+                float *dst = xbuf + buf * tile_words + r * sh.SX + lane;
+                unsigned wv[kCols];
 #pragma unroll
-        for (int k = 0; k < kCols; ++k) {
-            const int pcol = lane + 32 * k;
-            const int gt = g0 + pcol;
-            const bool ok = gt >= 0 && gt < T;
-            goff[k] = ok ? gt : 0;
-            nbytes[k] = pcol < WX ? (ok ? 4 : 0) : -1;
-        }
-        for (int r = warp; r < kFir2Rows; r += nwarps) {
-            const bool row_ok = r < nrow;
-            const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
-            const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + (r >> 1) * sh.SX + (r & 1) + 2 * lane);
+                for (int k = 0; k < kCols; ++k) {
+                    const int gt = g0 + lane + 32 * k;
+                    const bool ok = row_ok && lane + 32 * k < WX && gt >= 0 && gt < T;
+                    wv[k] = ok ? (__ldg(src + (gt >> 5)) >> (gt & 31)) & 1u : 0u;
+                }
 #pragma unroll
-            for (int k = 0; k < kCols; ++k) {
-                if (nbytes[k] < 0) continue;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n"
-                             ::"r"(dst + 256u * k), "l"(src + goff[k]), "r"(row_ok ? nbytes[k] : 0) : "memory");
+                for (int k = 0; k < kCols; ++k)
+                    if (lane + 32 * k < WX) dst[32 * k] = wv[k] ? spike_value : 0.0f;
+            }
+        } else if constexpr (V == 4) {
+            constexpr int kChunks = (kFir2MaxSamples + 127) / 128;     // 4
+            int goff[kChunks], nbytes[kChunks];          // source offset in the row; 16, 0 (zero fill) or -1 (no chunk)
+#pragma unroll
+            for (int k = 0; k < kChunks; ++k) {
+                const int pcol = lane * 4 + 128 * k;
+                const int gt = g0 + pcol;
+                const bool ok = gt >= 0 && gt < T;
+                goff[k] = ok ? gt : 0;
+                nbytes[k] = pcol < WX ? (ok ? 16 : 0) : -1;
+            }
+            for (int r = warp; r < kFir2Rows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+                const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + r * sh.SX + lane * 4);
+#pragma unroll
+                for (int k = 0; k < kChunks; ++k) {
+                    if (nbytes[k] < 0) continue;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
+                                 ::"r"(dst + 512u * k), "l"(src + goff[k]), "r"(row_ok ? nbytes[k] : 0) : "memory");
+                }
+            }
+        } else {
+            float *xs = xbuf + buf * tile_words;
+            for (int r = warp; r < kFir2Rows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+                float *dst = xs + r * sh.SX;
+                for (int pcol = lane * V; pcol < WX; pcol += 32 * V) {
+                    const int gt = g0 + pcol;
+                    const bool ok = row_ok && gt >= 0 && gt < T;
+                    cp_async<4 * V>(dst + pcol, ok ? src + gt : in, ok);
+                }
             }
         }
         cp_async_commit();
@@ -509,13 +564,13 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
 
     const int groups = K >> 2;          // full groups of 4 taps
     const int tail = K & 3;
-    constexpr unsigned step = DIR < 0 ? 0u - 32u : 32u;   // bytes the window moves per group (mod 2^32)
+    constexpr unsigned step = DIR < 0 ? 0u - 16u : 16u;   // bytes the window moves per group (mod 2^32)
     const unsigned fs_addr = (unsigned)__cvta_generic_to_shared(fs);
     const unsigned fsA_addr = (unsigned)__cvta_generic_to_shared(fsA);
     const unsigned fsB_addr = (unsigned)__cvta_generic_to_shared(fsB);
     const int mask_words = (WX + 31) >> 5;
     const bool may_skip = sparse_ok && K >= 8;
-    bool sparse = false;                 // the previous scanned tile was mostly zeros (same value in every thread)
+    bool sparse = false;                 // the last tile looked at was mostly zeros (same value in every thread)
 
     int64_t tile = blockIdx.x;
     if (tile < ntiles) fill(0, tile);
@@ -527,25 +582,22 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
 
         const int64_t rb = tile / sh.ttiles;
         const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
-        const int64_t rowA = rb * kFir2Rows + 2 * lane;
-        // byte address of tile position 0 of this lane's row pair
+        const int64_t rowA = rb * kFir2Rows + lane;
+        // byte address of tile position 0 of this lane's row A
         const unsigned xtile0 = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + lane * sh.SX);
-        const unsigned xrow = xtile0 + 8u * (unsigned)(DIR < 0 ? sh.halo : 0);
+        const unsigned xrow = xtile0 + 4u * (unsigned)(DIR < 0 ? sh.halo : 0);
 
         // Which sample positions hold a non-zero in any of the 64 rows?  Looked at for every tile
         // while tiles are sparse, else for one tile in kFir2ScanEvery.  Lane = position, loop over
-        // the row pairs: the OR of the magnitude bits of both rows, one ballot per 32 positions.
+        // the rows: the OR of the magnitude bits, one ballot per 32 positions.
         if (may_skip && (sparse || (it % kFir2ScanEvery) == 0)) {
             for (int wd = warp; wd < mask_words; wd += nwarps) {
                 const int pos = 32 * wd + lane;
                 unsigned bits = 0u;
                 if (pos < WX) {
-                    const unsigned col = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words) + 8u * (unsigned)pos;
+                    const unsigned col = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + pos);
 #pragma unroll 8
-                    for (int pr = 0; pr < kFir2Rows / 2; ++pr) {
-                        const f2 v = ld1p(col + 4u * (unsigned)(pr * sh.SX));
-                        bits |= (unsigned)v | (unsigned)(v >> 32);
-                    }
+                    for (int r = 0; r < kFir2Rows; ++r) bits |= __float_as_uint(ld1(col + 4u * (unsigned)(r * sh.SX)));
                 }
                 const unsigned live = __ballot_sync(0xffffffffu, (bits & 0x7fffffffu) != 0u);
                 if (lane == 0) colmask[wd] = live;
@@ -568,31 +620,31 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
             if (sparse) {
                 // window of the segment in tile positions: conv starts K - 1 samples before the
                 // first output (tile position halo + tb), corr at the first output
-                fir2_sparse_segment<DIR>(acc, colmask, xtile0, fsA_addr, fsB_addr,
+                fir2_sparse_segment<DIR>(acc, colmask, xtile0, rowb, fsA_addr, fsB_addr,
                                          DIR < 0 ? sh.halo + tb - (K - 1) : tb, K);
             } else {
                 // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
                 f2 w[kFirRing];
-                const unsigned x0 = xrow + 8u * (unsigned)tb - (DIR < 0 ? 32u : 0u);
+                const unsigned x0 = xrow + 4u * (unsigned)tb - (DIR < 0 ? 16u : 0u);
 #pragma unroll
-                for (int q = 0; q < kFirWin / 2; ++q) ld2p(x0 + 16 * q, w[2 * q], w[2 * q + 1]);
-                unsigned xp = DIR < 0 ? x0 - 32 : x0 + 8 * kFirWin;    // next four sample pairs to fetch
+                for (int q = 0; q < kFirWin / 4; ++q) ld4p(x0 + 16 * q, rowb, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                unsigned xp = DIR < 0 ? x0 - 16 : x0 + 4 * kFirWin;    // next four samples to fetch
                 unsigned fp = fs_addr;
                 f2 f[2][4];
                 ld2p(fp, f[0][0], f[0][1]);
                 ld2p(fp + 16, f[0][2], f[0][3]);
                 int g = 0;
                 for (; g + kFirPhases <= groups; g += kFirPhases) {
-                    fir2_step<DIR, 0>(acc, w, f, fp + 32, xp);
-                    fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step);
-                    fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step);
-                    fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step);
-                    fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step);
-                    fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step);
+                    fir2_step<DIR, 0>(acc, w, f, fp + 32, xp, rowb);
+                    fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step, rowb);
+                    fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step, rowb);
+                    fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step, rowb);
+                    fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step, rowb);
+                    fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step, rowb);
                     xp += kFirPhases * step;
                     fp += 32 * kFirPhases;
                 }
-                fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, groups - g, tail);
+                fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, rowb, groups - g, tail);
             }
 
             float oa[kFirSeg], ob[kFirSeg];
@@ -605,7 +657,7 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
             const int left = T - (t0 + tb);          // > 0, multiple of V
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int64_t row = rowA + h;
+                const int64_t row = rowA + 32 * h;
                 if (row >= rows) continue;
                 const float *o = h ? ob : oa;
                 float *dst = out + row * (int64_t)T + t0 + tb;
@@ -702,7 +754,7 @@ static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
 static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
 {
     sh.halo = (int)(((K + 3) & ~3LL) + 8);     // taps rounded up plus two quads of look-ahead
-    const int room = kFir2MaxSamples - 2 - sh.halo;           // samples left for outputs (2 = stride padding)
+    const int room = kFir2MaxSamples - 4 - sh.halo;           // samples left for outputs (4 = stride padding)
     const int nseg_max = room / kFirSeg;
     if (nseg_max < 1) return false;
     const int64_t segs = ceil_div(T, kFirSeg);
@@ -717,9 +769,7 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
     }
     sh.nseg = (int)ceil_div(segs, sh.ttiles);
     sh.ttiles = (int)ceil_div(segs, sh.nseg);
-    // words per row pair: two rows interleaved, = 4 (mod 8) so that the 128-bit loads of a
-    // quarter warp fall into distinct bank groups
-    sh.SX = pad_stride(2 * (sh.nseg * kFirSeg + sh.halo));
+    sh.SX = pad_stride(sh.nseg * kFirSeg + sh.halo);
     // Warps per CTA: warp w runs on scheduler w % 4 and takes segments w, w+nw, ...; pick the
     // multiple of four whose busiest scheduler has the least work, preferring fewer warps.
     if (sh.nseg <= 8) {
@@ -739,21 +789,22 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
     return true;
 }
 
-static std::atomic<int> g_fir_packed{1};
+static std::atomic<int> g_fir_packed{0};
 static std::atomic<int> g_fir_skip_zeros{1};
 
-template <int DIR>
+template <int DIR, bool PK = false>
 static int launch_fir2(float *out, const float *in, const float *filt,
-                       int64_t rows, int64_t T, int64_t Keff, float Ts, cudaStream_t stream, bool &taken)
+                       int64_t rows, int64_t T, int64_t Keff, float Ts, cudaStream_t stream, bool &taken,
+                       float spike_value = 0.0f)
 {
     FirShape sh;
     taken = fir2_shape(rows, T, Keff, sh);
     if (!taken) return SLAYER_B200_OK;
     const int64_t ntiles = ceil_div(rows, kFir2Rows) * sh.ttiles;
     const size_t kp = (size_t)((Keff + 3) & ~3LL);
-    const size_t smem = sizeof(float) * (2 * (kp + 4) + 4 * (kp + 2 * kFirSeg) + kFir2MaskWords + 2 * (size_t)(kFir2Rows / 2) * sh.SX);
-    const int vw = tile_vec_width(T, {out});
-    auto kern = vw == 4 ? fir2_kernel<DIR, 4> : (vw == 2 ? fir2_kernel<DIR, 2> : fir2_kernel<DIR, 1>);
+    const size_t smem = sizeof(float) * (2 * (kp + 4) + 4 * (kp + 2 * kFirSeg) + kFir2MaskWords + 2 * (size_t)kFir2Rows * sh.SX);
+    const int vw = PK ? tile_vec_width(T, {out}) : tile_vec_width(T, {out, in});
+    auto kern = vw == 4 ? fir2_kernel<DIR, 4, PK> : (vw == 2 ? fir2_kernel<DIR, 2, PK> : fir2_kernel<DIR, 1, PK>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
     // CTAs per SM: bounded by shared memory and by registers (128 per thread at most)
@@ -765,7 +816,7 @@ static int launch_fir2(float *out, const float *in, const float *filt,
     int64_t grid = ctas_per_sm * (int64_t)sm_count();
     if (grid > ntiles) grid = ntiles;
     kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles,
-                                                           g_fir_skip_zeros.load() != 0);
+                                                           g_fir_skip_zeros.load() != 0, spike_value);
     return check_launch("fir (packed) kernel launch");
 }
 
@@ -840,6 +891,31 @@ extern "C" int slayer_b200_conv(float *out, const float *in, const float *filter
     int rc = check_fir_args("conv", out, in, filter, rows, T, K);
     if (rc) return rc;
     return launch_fir<-1>(out, in, filter, rows, T, K, Ts, (cudaStream_t)stream);
+}
+
+extern "C" int slayer_b200_conv_packed(float *out, const uint32_t *bits, const float *filter,
+                                       int64_t rows, int64_t T, int64_t K, float spike_value, float Ts, void *stream)
+{
+    using namespace sb200;
+    clear_error();
+    int rc = check_fir_args("conv_packed", out, reinterpret_cast<const float *>(bits), filter, rows, T, K);
+    if (rc) return rc;
+    SB200_REQUIRE((reinterpret_cast<uintptr_t>(bits) & 3u) == 0, "conv_packed: bits must be 4-byte aligned");
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    if (K == 0) {
+        cudaError_t e = cudaMemsetAsync(out, 0, (size_t)rows * T * sizeof(float), (cudaStream_t)stream);
+        if (e != cudaSuccess) { set_error("conv_packed: memset failed: %s", cudaGetErrorString(e)); return SLAYER_B200_ECUDA; }
+        return SLAYER_B200_OK;
+    }
+    bool taken = false;
+    rc = launch_fir2<-1, true>(out, reinterpret_cast<const float *>(bits), filter, rows, T, K < T ? K : T, Ts,
+                               (cudaStream_t)stream, taken, spike_value);
+    if (!taken) {
+        set_error("conv_packed: a filter of %lld taps is too long for the tiled kernel; unpack the spikes and call "
+                  "slayer_b200_conv", (long long)K);
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    return rc;
 }
 
 extern "C" int slayer_b200_corr(float *out, const float *in, const float *filter,

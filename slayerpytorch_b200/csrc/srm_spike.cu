@@ -546,7 +546,12 @@ __device__ __forceinline__ void store_delayed_spikes(const unsigned *masks, int 
 // The warp keeps the spike bits of the whole row (T / 32 words per row) in shared memory and
 // writes the shifted samples when it has walked the row, so any delay - positive, negative,
 // beyond the row - costs the same and the undelayed spikes never reach global memory.
-template <int NB, int W, bool PER_BLOCK = false, bool DELAYED = false>
+//
+// PACKED: the spikes leave as bits, not as fp32 samples: `s` then points to 32-bit words,
+// ceil(T / 32) per row, bit i of word w = "spiked at step 32 w + i" (bits past T are zero).  The
+// warp already holds exactly these words after walking a tile, so each lane stores the two words
+// of its row; the spike output shrinks from 4 bytes to 1/8 byte per element.
+template <int NB, int W, bool PER_BLOCK = false, bool DELAYED = false, bool PACKED = false>
 __global__ void __launch_bounds__(256)
 srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__restrict__ s, float *u,
                           const float *__restrict__ nu, int64_t rows, int nuEff, int T,
@@ -653,11 +658,22 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
             if (h == 0) m[0] = mh;
             else m[1] = mh;
         }
-        if (DELAYED) {
-            // keep the bits of the whole row; bits of steps past the row end must read as zero
+        if (DELAYED || PACKED) {
+            // bits of steps past the row end must read as zero
             const int left = T - kWide * j;                  // > 0
             if (left < kTile) m[0] &= (1u << left) - 1u;
             if (left < kWide) m[1] &= left > kTile ? (1u << (left - kTile)) - 1u : 0u;
+        }
+        if (PACKED) {
+            const int64_t row = rb * kTile + lane;
+            const int words = (T + 31) >> 5;
+            if (row < rows) {
+                unsigned *dst = reinterpret_cast<unsigned *>(s) + row * words + 2 * j;
+                dst[0] = m[0];
+                if (2 * j + 1 < words) dst[1] = m[1];
+            }
+        } else if (DELAYED) {
+            // keep the bits of the whole row
             masks[(2 * j) * kRowMaskStride + lane] = m[0];
             masks[(2 * j + 1) * kRowMaskStride + lane] = m[1];
         } else {
@@ -666,7 +682,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
         }
         __syncwarp();
         wide_store(tile, u, rb * kTile, rows, kWide * j, T, lane);
-        if (!DELAYED) wide_store_spikes(masks, s, rb * kTile, rows, kWide * j, T, lane, spikeVal);
+        if (!DELAYED && !PACKED) wide_store_spikes(masks, s, rb * kTile, rows, kWide * j, T, lane, spikeVal);
         if (DELAYED && j == ntiles - 1)
             store_delayed_spikes(masks, 2 * ntiles, da.out, rb * kTile, rows, T, lane, delay_steps, spikeVal);
         // the reads of this stage (and of the masks) precede the bulk load that refills it
@@ -838,6 +854,52 @@ static int dispatch_srm_delayed(const SrmArgs &a, const DelayArgs &da)
     if (window <= 64) return launch_srm_delayed<0, 2>(a, da);
     if (window <= 128) return launch_srm_delayed<0, 4>(a, da);
     return launch_srm_delayed<0, 8>(a, da);
+}
+
+// Spikes written as bits (slayer_b200_srm_get_spikes_packed): the bulk-tensor kernel with its
+// spike output replaced by two word stores per row and tile.
+template <int NB, int W>
+static int launch_srm_packed(const SrmArgs &a)
+{
+    const int64_t nblocks = ceil_div(a.rows, kTile);
+    CUtensorMap map_u;
+    int *status = device_status_word();
+    if (!status || a.rows * (int64_t)kTile >= (1LL << 31) ||
+        !encode_rows_tensor_map(&map_u, a.u, a.rows, a.T, kBoxT, kTile, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        set_error("srm_get_spikes_packed: cannot describe the buffers for bulk tensor copies");
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    const int sms = sm_count();
+    const int64_t warps_per_sm = ceil_div(nblocks, sms);
+    int ustages = (int)((208 * 1024) / (warps_per_sm * kStageBytes));
+    if (ustages > kMaxUStages) ustages = kMaxUStages;
+    if (ustages < kUStages) ustages = kUStages;
+    int warps, grid;
+    spike_launch_shape(nblocks, (size_t)ustages * kStageBytes + 512, warps, grid);
+    const size_t smem = srm_tma_smem(warps, ustages, a.nuEff, NB == 0);
+    auto kern = srm_get_spikes_tma_kernel<NB, W, false, false, true>;
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
+    kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(map_u, a.s, a.u, a.nu, a.rows, a.nuEff, a.T, a.theta,
+                                                         a.spikeVal, status, ustages, DelayArgs{});
+    return check_launch("srm_get_spikes_packed kernel launch");
+}
+
+static int dispatch_srm_packed(const SrmArgs &a)
+{
+    const int window = a.nuEff > 1 ? a.nuEff - 1 : 0;     // history bits needed
+    if (window <= 2) return launch_srm_packed<2, 1>(a);
+    if (window <= 4) return launch_srm_packed<4, 1>(a);
+    if (window <= 6) return launch_srm_packed<6, 1>(a);
+    if (window <= 8) return launch_srm_packed<8, 1>(a);
+    if (window <= 10) return launch_srm_packed<10, 1>(a);
+    if (window <= 12) return launch_srm_packed<12, 1>(a);
+    if (window <= 16) return launch_srm_packed<16, 1>(a);
+    if (window <= 24) return launch_srm_packed<24, 1>(a);
+    if (window <= 32) return launch_srm_packed<32, 1>(a);
+    if (window <= 64) return launch_srm_packed<0, 2>(a);
+    if (window <= 128) return launch_srm_packed<0, 4>(a);
+    return launch_srm_packed<0, 8>(a);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1048,6 +1110,26 @@ extern "C" int slayer_b200_srm_get_spikes(float *s, float *u, const float *nu,
         case 2: return dispatch_srm<2>(a);
         default: return dispatch_srm<1>(a);
     }
+}
+
+extern "C" int slayer_b200_srm_get_spikes_packed(uint32_t *bits, float *u, const float *nu,
+                                                 int64_t rows, int64_t nuSize, int64_t T, float theta, void *stream_)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(rows >= 0 && nuSize >= 0 && T >= 0, "srm_get_spikes_packed: negative size");
+    SB200_REQUIRE(T < (1LL << 31) - 64, "srm_get_spikes_packed: T=%lld too large", (long long)T);
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    SB200_REQUIRE(bits && u && (nu || nuSize == 0), "srm_get_spikes_packed: null pointer");
+    SB200_REQUIRE((void *)bits != (void *)u, "srm_get_spikes_packed: bits must not alias u");
+    const int64_t nuEff = nuSize < T ? nuSize : T;
+    if ((T & 3) || !aligned16(u) || (reinterpret_cast<uintptr_t>(bits) & 3u) || nuEff - 1 > 32 * kMaxHistWords || !tma_enabled()) {
+        set_error("srm_get_spikes_packed: needs T %% 4 == 0, a 16-byte aligned potential and at most %d taps; "
+                  "otherwise run slayer_b200_srm_get_spikes and slayer_b200_pack_spikes", 32 * kMaxHistWords + 1);
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    const SrmArgs a = {reinterpret_cast<float *>(bits), u, nu, rows, (int)nuEff, (int)T, theta, 1.0f, (cudaStream_t)stream_, true};
+    return dispatch_srm_packed(a);
 }
 
 extern "C" int slayer_b200_shift_lut(float *out, const float *in, const float *lut,

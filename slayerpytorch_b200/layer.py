@@ -106,6 +106,50 @@ class _SpikeFunction(torch.autograd.Function):
         return slayerCuda.spikeGrad(grad.contiguous(), u, ctx.theta, ctx.tau, ctx.scale), None, None, None
 
 
+class PackedSpikes:
+    """A spike tensor stored as bits: ``bits`` is int32 of shape ``[..., ceil(T / 32)]``, bit i of
+    word w = "spike at step 32 w + i"; a spike has the value ``value`` (1 / Ts).  1/32 of the
+    bytes of the fp32 form; ``dense()`` gives that form back."""
+
+    def __init__(self, bits, T, value):
+        self.bits, self.T, self.value = bits, int(T), float(value)
+
+    @property
+    def shape(self):
+        return tuple(self.bits.shape[:-1]) + (self.T,)
+
+    def dense(self):
+        return slayerCuda.unpackSpikes(self.bits, self.T, self.value)
+
+
+class _SpikePspFunction(torch.autograd.Function):
+    """psp(spike(u)) as one autograd node: the spikes go from the spike kernel to the psp filter
+    as bits (1/8 byte per element instead of two fp32 passes) and are returned packed as a second,
+    non-differentiable output.  Backward is the reference's: corr of the incoming gradient
+    (src/slayer.py:892), then the surrogate gradient on the updated potential (src/slayer.py:862).
+    Same results as _PspFunction applied to _SpikeFunction."""
+
+    @staticmethod
+    def forward(ctx, u, srmKernel, refKernel, neuron, Ts):
+        u = u.contiguous()
+        Ts = float(Ts)
+        bits = slayerCuda.getSpikesPacked(u, refKernel, neuron['theta'], Ts)
+        out = slayerCuda.convPacked(bits, u.shape[-1], srmKernel, Ts, 1.0 / Ts)
+        ctx.save_for_backward(u, srmKernel)
+        ctx.theta = float(neuron['theta'])
+        ctx.tau = float(neuron['tauRho'] * neuron['theta'])
+        ctx.scale = float(neuron['scaleRho'])
+        ctx.Ts = Ts
+        ctx.mark_non_differentiable(bits)
+        return out, bits
+
+    @staticmethod
+    def backward(ctx, grad, _grad_bits):
+        u, srmKernel = ctx.saved_tensors
+        g = slayerCuda.corr(grad.contiguous(), srmKernel, ctx.Ts)
+        return slayerCuda.spikeGrad_(g, u, ctx.theta, ctx.tau, ctx.scale), None, None, None, None
+
+
 class _DelayFunction(torch.autograd.Function):
     """Learnable per-neuron delay (src/slayer.py:930-957): forward shifts by the delay, backward
     shifts the gradient back and integrates gradient x finite-difference of the output."""
@@ -276,7 +320,18 @@ class spikeLayer(torch.nn.Module):
                                               self.simulation['tSample'], mult=mult, epsilon=eps))
 
     def psp(self, spike):
+        if isinstance(spike, PackedSpikes):      # bit-packed spikes (no gradient flows into them)
+            return slayerCuda.convPacked(spike.bits, spike.T, self.srmKernel, self.simulation['Ts'], spike.value)
         return _PspFunction.apply(spike, self.srmKernel, self.simulation['Ts'])
+
+    def spikePsp(self, membranePotential):
+        """``psp(spike(u))`` as one autograd node with the spikes kept bit-packed in between;
+        returns ``(psp output, PackedSpikes)``.  For layers of the form ``spike(W(psp(.)))``, where
+        the spikes of one layer are only ever read by the psp filter of the next.  Not part of
+        the reference's interface."""
+        Ts = self.simulation['Ts']
+        out, bits = _SpikePspFunction.apply(membranePotential, self.srmKernel, self.refKernel, self.neuron, Ts)
+        return out, PackedSpikes(bits, membranePotential.shape[-1], 1.0 / Ts)
 
     def spike(self, membranePotential):
         return _SpikeFunction.apply(membranePotential, self.refKernel, self.neuron, self.simulation['Ts'])

@@ -2,8 +2,8 @@
 
     python -m slayerpytorch_b200.opbench --op getSpikes --rows 262144 --T 300 --iters 5
 
-Operators: conv, corr, getSpikes, getSpikesDelayed, shift, shiftScalar, spikeGrad, spikeGradShift,
-delayGrad, loihi.  Prints one JSON line with
+Operators: conv, corr, convPacked, getSpikes, getSpikesPacked, getSpikesDelayed, shift, shiftScalar,
+spikeGrad, spikeGradShift, delayGrad, loihi.  Prints one JSON line with
 the average launch time, algorithmic GB/s (8 bytes per element for conv/corr/shift, 12 for
 getSpikes/spikeGrad, 16 for loihi) and elements per second.  Small enough to run under a
 profiler: every iteration is exactly one kernel launch of the operator (getSpikes works in
@@ -19,7 +19,7 @@ import slayerpytorch_b200
 from slayerpytorch_b200.layer import alpha_kernel, loihi_psp_kernel
 
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "spikeGradShift": 12, "delayGrad": 8,
-             "getSpikesDelayed": 12,
+             "getSpikesDelayed": 12, "getSpikesPacked": 8.125, "convPacked": 4.125,
              "loihi": 16}
 
 
@@ -33,15 +33,15 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--density", type=float, default=0.3, help="fraction of non-zero input samples")
     ap.add_argument("--neurons", type=int, default=512, help="rows per batch sample (length of the shift table)")
-    ap.add_argument("--scalar-fir", action="store_true", help="conv/corr: the scalar kernel instead of the packed one")
+    ap.add_argument("--packed-fir", action="store_true", help="conv/corr: the packed kernel instead of the scalar one")
     ap.add_argument("--no-skip-zeros", action="store_true", help="conv/corr: packed kernel without its zero-skipping path")
     ap.add_argument("--spikes", action="store_true", help="conv/corr: the input is a 0/1 spike tensor of the given density")
     args = ap.parse_args(argv)
 
     sc, lc = slayerpytorch_b200.load_ops()
-    if args.scalar_fir:
+    if args.packed_fir:
         from slayerpytorch_b200 import capi
-        capi.set_fir_packed(False)
+        capi.set_fir_packed(True)
     if args.no_skip_zeros:
         from slayerpytorch_b200 import capi
         capi.set_fir_skip_zeros(False)
@@ -74,6 +74,15 @@ def main(argv=None):
         u = torch.empty_like(u0)
         restore = lambda: u.copy_(u0)
         fn = lambda: sc.getSpikes(u, ref, 10.0, 1.0)
+    elif args.op == "getSpikesPacked":
+        u0 = sc.conv(a, srm, 1.0)
+        u = torch.empty_like(u0)
+        restore = lambda: u.copy_(u0)
+        fn = lambda: sc.getSpikesPacked(u, ref, 10.0, 1.0)
+    elif args.op == "convPacked":
+        bits = sc.packSpikes(a)
+        fn = lambda: sc.convPacked(bits, args.T, filt, 1.0, 1.0)
+        extra["taps"] = int(filt.numel())
     elif args.op == "getSpikesDelayed":
         u0 = sc.conv(a, srm, 1.0)
         u = torch.empty_like(u0)
@@ -114,6 +123,8 @@ def main(argv=None):
             times.append(e0.elapsed_time(e1))
     if args.op in ("getSpikes", "getSpikesDelayed"):
         extra["spike_rate"] = float(out.mean())
+    if args.op in ("conv", "corr", "convPacked"):
+        extra["input_density"] = float((a != 0).float().mean())
     if args.op == "loihi":
         extra["spike_rate"] = float(out[0].mean())
     ms = sum(times) / len(times)

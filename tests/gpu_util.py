@@ -110,3 +110,35 @@ def c_srm_delayed(u, nu, lut, theta, Ts, scalar=None, scratch=False):
         capi.call("slayer_b200_srm_get_spikes_delayed", ptr(d), ptr(sc) if scratch else None, ptr(u), ptr(nu), ptr(lut),
                   0.0, nb, rows // nb, nu.numel(), T, float(theta), float(Ts), stream())
     return d
+
+
+def words_of(T):
+    return (T + 31) // 32
+
+
+def c_pack(s):
+    rows, T = rows_T(s)
+    bits = torch.empty(s.shape[:-1] + (words_of(T),), dtype=torch.int32, device=s.device)
+    capi.call("slayer_b200_pack_spikes", ptr(bits), ptr(s), rows, T, stream())
+    return bits
+
+
+def c_unpack(bits, T, value):
+    s = torch.empty(bits.shape[:-1] + (T,), dtype=torch.float32, device=bits.device)
+    capi.call("slayer_b200_unpack_spikes", ptr(s), ptr(bits), s.numel() // T if T else 0, T, float(value), stream())
+    return s
+
+
+def c_srm_packed(u, nu, theta):
+    """In place on u; returns the packed spikes."""
+    rows, T = rows_T(u)
+    bits = torch.full(u.shape[:-1] + (words_of(T),), -1, dtype=torch.int32, device=u.device)
+    capi.call("slayer_b200_srm_get_spikes_packed", ptr(bits), ptr(u), ptr(nu), rows, nu.numel(), T, float(theta), stream())
+    return bits
+
+
+def c_conv_packed(bits, T, f, value, Ts):
+    out = torch.empty(bits.shape[:-1] + (T,), dtype=torch.float32, device=bits.device)
+    capi.call("slayer_b200_conv_packed", ptr(out), ptr(bits), ptr(f), out.numel() // T if T else 0, T, f.numel(),
+              float(value), float(Ts), stream())
+    return out

@@ -168,6 +168,7 @@ def test_conv_corr_on_spike_tensors_skip_zeros(density, T, K):
     f = rng.randn(K).astype(np.float32)
     xd, fd = G.dev(x), G.dev(f)
     want_conv, want_corr = co.conv(x, f, 1.0), co.corr(x, f, 1.0)
+    before = capi.set_fir_packed(True)
     try:
         for skip in (True, False):
             capi.set_fir_skip_zeros(skip)
@@ -175,6 +176,7 @@ def test_conv_corr_on_spike_tensors_skip_zeros(density, T, K):
             assert_close_or_equal(G.host(G.c_conv(xd, fd, 1.0, corr=True)), want_corr)
     finally:
         capi.set_fir_skip_zeros(True)
+        capi.set_fir_packed(before)
 
 
 def test_conv_skip_zeros_with_non_finite_samples():
@@ -186,12 +188,14 @@ def test_conv_skip_zeros_with_non_finite_samples():
     f = rng.randn(77).astype(np.float32)
     xd, fd = G.dev(x), G.dev(f)
     got = {}
+    before = capi.set_fir_packed(True)
     try:
         for skip in (True, False):
             capi.set_fir_skip_zeros(skip)
             got[skip] = (G.host(G.c_conv(xd, fd, 1.0)), G.host(G.c_conv(xd, fd, 1.0, corr=True)))
     finally:
         capi.set_fir_skip_zeros(True)
+        capi.set_fir_packed(before)
     for a, b in zip(got[True], got[False]):
         np.testing.assert_array_equal(a, b)                  # NaN == NaN in this comparison
     conv = got[True][0]
