@@ -179,6 +179,34 @@ int slayer_b200_conv_packed(float *out, const uint32_t *bits, const float *filte
                             int64_t rows, int64_t T, int64_t K, float spike_value, float Ts, void *stream);
 
 /*
+ * Address events -> spike tensor, on the device: event e = (x[e], y[e], p[e], t[e] in ms)
+ * lands at out[n[e], p, y, x, rint(t / samplingTime) - tStart] of a [N, C, H, W, T] tensor
+ * (rint in double precision, half to even) if every index is inside it, and is dropped
+ * otherwise.  n may be NULL (all events in sample 0) and y may be NULL (y = 0).  sum_mode = 0:
+ * the element is set to 1 / samplingTime (`out` is updated in place, `base` is not read);
+ * sum_mode != 0: the element becomes base[...] + 1 / samplingTime, once per bin however many
+ * events share it (`base` holds the tensor's original values and must not be `out`; elements no
+ * event touches are left as they are in `out`).  Events are int32 / float64 device arrays.
+ * Replaces event.toSpikeTensor, src/spikeFileIO.py:66-144 (index rounding :95-97, bounds
+ * :102-107 and :121-128, 'OR' :108-112, 'SUM' :113-117 - an indexed "+=" there, which adds once
+ * per distinct index), including its time shift tSt (:82-93; drawn on the host and passed in).
+ */
+int slayer_b200_bin_events(float *out, const float *base, const int32_t *n, const int32_t *x, const int32_t *y,
+                           const int32_t *p, const double *t, int64_t nEvents,
+                           int64_t N, int64_t C, int64_t H, int64_t W, int64_t T,
+                           double samplingTime, int64_t tStart, int sum_mode, void *stream);
+
+/*
+ * The same binning ('OR' mode) into a bit-packed spike tensor: `bits` holds ceil(T / 32) uint32
+ * words per [n, p, y, x] row and must be zeroed (or hold earlier events) before the call; bits
+ * are set with atomic OR.  Index rules as above (src/spikeFileIO.py:95-112).
+ */
+int slayer_b200_bin_events_packed(uint32_t *bits, const int32_t *n, const int32_t *x, const int32_t *y,
+                                  const int32_t *p, const double *t, int64_t nEvents,
+                                  int64_t N, int64_t C, int64_t H, int64_t W, int64_t T,
+                                  double samplingTime, int64_t tStart, void *stream);
+
+/*
  * slayer_b200_srm_get_spikes without any memory allocation, for callers that cannot allocate
  * device memory: an application that has already given all device memory to its own pool, or
  * code that runs where entering the CUDA allocator is not allowed (another library's callback,

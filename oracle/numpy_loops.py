@@ -11,6 +11,8 @@ the explicit time-loop models in the reference's own tests:
 * conv / corr:  src/cuda/convKernels.h:28-33, :55-60 (tap loop; no fused multiply-add here,
   so values agree with the C oracle to rounding, not bit for bit)
 * surrogate:    src/slayer.py:862
+* event binning: src/spikeFileIO.py:66-144 (``event.toSpikeTensor``), one Python iteration per
+  event
 """
 import numpy as np
 
@@ -129,3 +131,36 @@ def spike_grad(g, u, theta, tau, scale):
     u = np.asarray(u, np.float32)
     theta, tau, scale = np.float32(theta), np.float32(tau), np.float32(scale)
     return g * (scale / tau * np.exp(-np.abs(u - theta) / tau))
+
+
+def bin_events(tensor, x, y, p, t, sampling_time=1.0, t_start=0, mode="OR", n=None):
+    """Address events into a spike tensor, following event.toSpikeTensor
+    (src/spikeFileIO.py:66-144): indices are rounded (:95-97, :120), events with any index
+    outside the tensor are dropped (:102-107, :121-128), 'OR' sets the bin to 1/samplingTime
+    (:108-112) and 'SUM' is an indexed "+=" (:113-117), which NumPy evaluates from the original
+    tensor and assigns once per distinct index.  ``tensor`` is [C, H, W, T], or [N, C, H, W, T]
+    with a sample index ``n`` per event; ``y`` may be None (one spatial dimension: y = 0).
+    Returns a new array."""
+    base = np.array(tensor, copy=True)
+    out = np.array(tensor, copy=True)
+    batched = out.ndim == 5
+    shape = out.shape if batched else (1,) + out.shape
+    view = out.reshape(shape)
+    orig = base.reshape(shape)
+    value = out.dtype.type(1.0 / sampling_time)
+    xs = np.round(np.asarray(x)).astype(np.int64)
+    ps = np.round(np.asarray(p)).astype(np.int64)
+    ys = np.zeros_like(xs) if y is None else np.round(np.asarray(y)).astype(np.int64)
+    ts = np.round(np.asarray(t, np.float64) / sampling_time).astype(np.int64) - int(t_start)
+    ns = np.zeros_like(xs) if n is None else np.asarray(n, np.int64)
+    N, C, H, W, T = shape
+    for e in range(xs.size):
+        if not (0 <= ns[e] < N and 0 <= ps[e] < C and 0 <= ys[e] < H and 0 <= xs[e] < W and 0 <= ts[e] < T):
+            continue
+        if mode.upper() == "OR":
+            view[ns[e], ps[e], ys[e], xs[e], ts[e]] = value
+        elif mode.upper() == "SUM":
+            view[ns[e], ps[e], ys[e], xs[e], ts[e]] = orig[ns[e], ps[e], ys[e], xs[e], ts[e]] + value
+        else:
+            raise ValueError("Unsupported binningMode. It was {}".format(mode))
+    return out

@@ -36,6 +36,7 @@ CUDA_SOURCES = {
     "spike_grad.cu": [],
     "delay_grad.cu": [],
     "packed.cu": [],
+    "events.cu": [],
     "tma.cu": [],
 }
 HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", os.path.join(INCLUDE, "slayer_b200.h")]

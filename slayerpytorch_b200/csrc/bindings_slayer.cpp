@@ -8,8 +8,9 @@
 //   - the per-neuron shift covers the whole batch in one launch;
 //   - dtype is checked explicitly;
 //   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift,
-//     getSpikesDelayed, delayGrad, and the bit-packed spike operators packSpikes, unpackSpikes,
-//     getSpikesPacked and convPacked (packed tensors are int32, [..., ceil(T / 32)]).
+//     getSpikesDelayed, delayGrad, the bit-packed spike operators packSpikes, unpackSpikes,
+//     getSpikesPacked and convPacked (packed tensors are int32, [..., ceil(T / 32)]), and the
+//     event binning binEvents / binEventsPacked.
 #include "bindings_common.h"
 
 using namespace sb200py;
@@ -314,6 +315,76 @@ static torch::Tensor convPackedCuda(torch::Tensor bits, int64_t T, torch::Tensor
     return output;
 }
 
+// ------------------------------------------------------------------ address events -> tensor
+static void check_events(const torch::Tensor &v, const char *name, torch::ScalarType dtype, int64_t count, const torch::Tensor &like)
+{
+    TORCH_CHECK(v.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(v.is_contiguous(), name, " must be contiguous");
+    TORCH_CHECK(v.scalar_type() == dtype, name, " has the wrong dtype (x, y, p, n: int32; t: float64)");
+    TORCH_CHECK(v.numel() == count, name, " must have one entry per event");
+    TORCH_CHECK(v.device().index() == like.device().index(), name, " must be on the device of the tensor");
+}
+
+// Events (x, y, p, t [, n]) binned into `tensor` ([C, H, W, T], or [N, C, H, W, T] with a sample
+// index n per event): mode 0 sets bins to 1/samplingTime in place and returns `tensor`; mode 1
+// returns a new tensor with 1/samplingTime added once to every bin that receives events.
+static torch::Tensor binEventsCuda(torch::Tensor tensor, torch::Tensor x, c10::optional<torch::Tensor> y, torch::Tensor p,
+                                   torch::Tensor t, c10::optional<torch::Tensor> n, double samplingTime, int64_t tStart,
+                                   int64_t mode)
+{
+    check_input(tensor, "tensor");
+    TORCH_CHECK(tensor.dim() == 4 || tensor.dim() == 5, "binEvents expects a CHWT or NCHWT tensor");
+    TORCH_CHECK(mode == 0 || mode == 1, "mode must be 0 (OR) or 1 (SUM)");
+    const int64_t count = x.numel();
+    check_events(x, "x", torch::kInt32, count, tensor);
+    check_events(p, "p", torch::kInt32, count, tensor);
+    check_events(t, "t", torch::kFloat64, count, tensor);
+    if (y.has_value()) check_events(*y, "y", torch::kInt32, count, tensor);
+    if (n.has_value()) check_events(*n, "n", torch::kInt32, count, tensor);
+    TORCH_CHECK(tensor.dim() == 5 || !n.has_value(), "a sample index needs an NCHWT tensor");
+    c10::cuda::CUDAGuard guard(tensor.device());
+    const int d = tensor.dim() == 5 ? 1 : 0;
+    const int64_t N = d ? tensor.size(0) : 1;
+    auto out = mode == 1 ? tensor.clone() : tensor;
+    check_rc(slayer_b200_bin_events(out.data_ptr<float>(), mode == 1 ? tensor.data_ptr<float>() : nullptr,
+                                    n.has_value() ? n->data_ptr<int32_t>() : nullptr, x.data_ptr<int32_t>(),
+                                    y.has_value() ? y->data_ptr<int32_t>() : nullptr, p.data_ptr<int32_t>(), t.data_ptr<double>(),
+                                    count, N, tensor.size(d), tensor.size(d + 1), tensor.size(d + 2), tensor.size(d + 3),
+                                    samplingTime, tStart, (int)mode, current_stream()),
+             "binEvents");
+    return out;
+}
+
+// The same binning ('OR') into a bit-packed spike tensor of the given CHWT / NCHWT shape.
+static torch::Tensor binEventsPackedCuda(std::vector<int64_t> shape, torch::Tensor x, c10::optional<torch::Tensor> y,
+                                         torch::Tensor p, torch::Tensor t, c10::optional<torch::Tensor> n,
+                                         double samplingTime, int64_t tStart)
+{
+    TORCH_CHECK(shape.size() == 4 || shape.size() == 5, "binEventsPacked expects a CHWT or NCHWT shape");
+    TORCH_CHECK(x.is_cuda(), "x must be a CUDA tensor");
+    const int64_t count = x.numel();
+    check_events(x, "x", torch::kInt32, count, x);
+    check_events(p, "p", torch::kInt32, count, x);
+    check_events(t, "t", torch::kFloat64, count, x);
+    if (y.has_value()) check_events(*y, "y", torch::kInt32, count, x);
+    if (n.has_value()) check_events(*n, "n", torch::kInt32, count, x);
+    TORCH_CHECK(shape.size() == 5 || !n.has_value(), "a sample index needs an NCHWT shape");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int d = shape.size() == 5 ? 1 : 0;
+    const int64_t N = d ? shape[0] : 1;
+    const int64_t T = shape.back();
+    auto wshape = shape;
+    wshape.back() = (T + 31) / 32;
+    auto bits = torch::zeros(wshape, x.options().dtype(torch::kInt32));
+    check_rc(slayer_b200_bin_events_packed(reinterpret_cast<uint32_t *>(bits.data_ptr<int32_t>()),
+                                           n.has_value() ? n->data_ptr<int32_t>() : nullptr, x.data_ptr<int32_t>(),
+                                           y.has_value() ? y->data_ptr<int32_t>() : nullptr, p.data_ptr<int32_t>(),
+                                           t.data_ptr<double>(), count, N, shape[d], shape[d + 1], shape[d + 2], T,
+                                           samplingTime, tStart, current_stream()),
+             "binEventsPacked");
+    return bits;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
     m.def("getSpikes", &getSpikesCuda, "Get spikes (CUDA)");
@@ -333,5 +404,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("unpackSpikes", &unpackSpikesCuda, "Bit-packed spike tensor -> fp32 (value where a bit is set) (CUDA)");
     m.def("getSpikesPacked", &getSpikesPackedCuda, "Get spikes, returned bit-packed (CUDA)");
     m.def("convPacked", &convPackedCuda, "Convolution in time of a bit-packed spike tensor (CUDA)");
+    m.def("binEvents", &binEventsCuda, "Address events -> spike tensor (CUDA)");
+    m.def("binEventsPacked", &binEventsPackedCuda, "Address events -> bit-packed spike tensor (CUDA)");
     m.attr("backend") = "slayer_b200";
 }

@@ -4,7 +4,7 @@ Run once, where the reference is available:
 
     python tests/golden/make_golden.py <path-to-reference-checkout>
 
-It writes three small ``.npz`` files next to itself:
+It writes four small ``.npz`` files next to itself:
 
 ``srm_kat.npz``
     The reference's MATLAB-derived known-answer data for the 250-25-1 SRM network
@@ -22,6 +22,12 @@ It writes three small ``.npz`` files next to itself:
     src/slayerLoihi.py:66-89), the pure-PyTorch psp layer (src/slayer.py:760-791) and the
     NumPy Loihi neuron model ``Neuron.run`` (test/test_slayerLoihi002.py:30-82, extracted
     from the test file by name so that nothing else in that file is executed).
+
+``events_ref.npz``
+    Seeded synthetic address events and the spike tensors the reference's own
+    ``event.toSpikeTensor`` (src/spikeFileIO.py:66-144; the class is extracted from the file by
+    name, because the module imports matplotlib) makes of them: one- and two-dimensional
+    events, events outside the tensor, both binning modes, sampling times 1 and 0.5 ms.
 
 Only data is stored; no reference source code is copied.
 """
@@ -179,6 +185,36 @@ def ref_python(root):
     return out
 
 
+def events_ref(root):
+    event = extract_class(os.path.join(root, "src", "spikeFileIO.py"), "event")
+    rng = np.random.RandomState(77)
+    out = {}
+    cases = [("2d_or", 2, (2, 9, 11, 40), 1.0, "OR"), ("2d_sum", 2, (2, 9, 11, 40), 1.0, "SUM"),
+             ("2d_half", 2, (3, 6, 5, 64), 0.5, "OR"), ("1d_or", 1, (4, 1, 20, 33), 1.0, "OR"),
+             ("1d_sum_half", 1, (2, 1, 7, 50), 0.5, "SUM")]
+    for tag, dim, shape, Ts, mode in cases:
+        C, H, W, T = shape
+        n = 400
+        # some events fall outside the tensor in every coordinate; many share a bin
+        x = rng.randint(-1, W + 2, n)
+        y = rng.randint(-1, H + 2, n) if dim == 2 else None
+        p = rng.randint(0, C + 1, n)
+        p[0] = 0                                       # the class subtracts min(p): keep it 0
+        t = rng.rand(n) * (T + 4) * Ts - Ts
+        t[:8] = (np.arange(8) + 0.5) * Ts              # exact half bins: rounding to even
+        start = (rng.rand(*shape) < 0.1).astype(np.float32) * 3.0 if mode == "SUM" else np.zeros(shape, np.float32)
+        got = event(x.copy(), None if y is None else y.copy(), p.copy(), t.copy()).toSpikeTensor(
+            start.copy(), samplingTime=Ts, randomShift=False, binningMode=mode)
+        out[tag + "_x"], out[tag + "_p"], out[tag + "_t"] = x.astype(np.int32), p.astype(np.int32), t
+        if y is not None:
+            out[tag + "_y"] = y.astype(np.int32)
+        out[tag + "_start"], out[tag + "_out"] = start, np.asarray(got, np.float32)
+        out[tag + "_Ts"] = np.float64(Ts)
+    out["cases"] = np.array([c[0] + ":" + c[4] for c in cases])
+    np.savez_compressed(os.path.join(HERE, "events_ref.npz"), **out)
+    return out
+
+
 def main(argv):
     if len(argv) < 2:
         print(__doc__)
@@ -187,7 +223,8 @@ def main(argv):
     a = srm_kat(root)
     b = loihi_kat(root)
     c = ref_python(root)
-    for name, d in (("srm_kat", a), ("loihi_kat", b), ("ref_python", c)):
+    d = events_ref(root)
+    for name, d in (("srm_kat", a), ("loihi_kat", b), ("ref_python", c), ("events_ref", d)):
         size = os.path.getsize(os.path.join(HERE, name + ".npz"))
         print("%s.npz: %d arrays, %d bytes" % (name, len(d), size))
     return 0

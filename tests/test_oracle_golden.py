@@ -253,3 +253,16 @@ def test_srm_c_vs_numpy_random():
         b = nl.srm_get_spikes(u, nu, 10.0, 1.0)
         np.testing.assert_array_equal(a[0], b[0])
         np.testing.assert_array_equal(a[1], b[1])
+
+
+def test_event_binning_oracle_equals_the_reference_function(golden_dir):
+    """oracle.numpy_loops.bin_events against spike tensors made by the reference's own
+    event.toSpikeTensor (src/spikeFileIO.py:66-144) from seeded synthetic events."""
+    from oracle import numpy_loops as nl
+    g = np.load(golden_dir + "/events_ref.npz")
+    assert len(g["cases"]) >= 5
+    for case in g["cases"]:
+        tag, mode = str(case).split(":")
+        y = g[tag + "_y"] if tag + "_y" in g else None
+        got = nl.bin_events(g[tag + "_start"], g[tag + "_x"], y, g[tag + "_p"], g[tag + "_t"], float(g[tag + "_Ts"]), 0, mode)
+        np.testing.assert_array_equal(got, g[tag + "_out"], err_msg=tag)
