@@ -207,6 +207,23 @@ int slayer_b200_bin_events_packed(uint32_t *bits, const int32_t *n, const int32_
                                   double samplingTime, int64_t tStart, void *stream);
 
 /*
+ * Spike-count loss, value and gradient in one pass.  For output spikes s[rows, T] (rows = batch
+ * x classes), a target region [start, stop) in time steps (resolved like a Python slice of a
+ * row) and a desired spike count per row:
+ *   c[row]   = float( (double(Ts * sum_{t in region} s[t]) - desired_count[row]) / (stop - start) * scale )
+ *   e[t]     = conv(s outside the region, filter)[t] + (t in region ? c[row] : 0)
+ *   row_sq[row] = sum_t e[t]^2 (double)           loss = Ts / 2 * sum(row_sq)   (left to the caller)
+ *   grad[row, t] = corr(Ts * e, filter)[t]        = d loss / d s
+ * conv / corr as slayer_b200_conv / _corr (same chains, x Ts).  Replaces spikeLoss.numSpikes,
+ * src/spikeLoss.py:85-104 (host NumPy for the counts and masks, then psp and a tensor sum), and
+ * the backward pass autograd derives from it (psp backward = corr, src/slayer.py:892).
+ * SLAYER_B200_EUNSUPPORTED for rows too long for the kernel's shared memory.
+ */
+int slayer_b200_num_spikes_loss(float *grad, double *row_sq, const float *s, const float *desired_count,
+                                const float *filter, int64_t rows, int64_t T, int64_t K,
+                                int64_t start, int64_t stop, float Ts, float scale, void *stream);
+
+/*
  * slayer_b200_srm_get_spikes without any memory allocation, for callers that cannot allocate
  * device memory: an application that has already given all device memory to its own pool, or
  * code that runs where entering the CUDA allocator is not allowed (another library's callback,

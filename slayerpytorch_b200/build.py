@@ -37,6 +37,7 @@ CUDA_SOURCES = {
     "delay_grad.cu": [],
     "packed.cu": [],
     "events.cu": [],
+    "loss.cu": ["-ftz=true"],
     "tma.cu": [],
 }
 HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", os.path.join(INCLUDE, "slayer_b200.h")]

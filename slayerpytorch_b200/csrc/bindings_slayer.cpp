@@ -315,6 +315,31 @@ static torch::Tensor convPackedCuda(torch::Tensor bits, int64_t T, torch::Tensor
     return output;
 }
 
+// ------------------------------------------------------------------------ spike-count loss
+// Returns (sum over rows and time of e^2 as a float64 0-dim tensor, d loss / d spikes for a unit
+// upstream gradient); the caller scales by Ts / 2.  desiredCount: one value per [batch, class] row.
+static std::vector<torch::Tensor> numSpikesLossCuda(torch::Tensor spikes, torch::Tensor desiredCount, torch::Tensor filter,
+                                                    int64_t start, int64_t stop, float Ts, float scale)
+{
+    check_input(spikes, "spikes");
+    check_input(desiredCount, "desiredCount");
+    check_input(filter, "filter");
+    check_device(spikes, desiredCount, "spikes", "desiredCount");
+    check_device(spikes, filter, "spikes", "filter");
+    TORCH_CHECK(spikes.dim() >= 2, "numSpikesLoss expects [batch, ..., time] spikes");
+    const int64_t T = spikes.size(-1);
+    const int64_t rows = T ? spikes.numel() / T : 0;
+    TORCH_CHECK(desiredCount.numel() == rows, "desiredCount must hold one value per row of spikes");
+    c10::cuda::CUDAGuard guard(spikes.device());
+    auto grad = torch::empty_like(spikes);
+    auto row_sq = torch::empty({rows}, spikes.options().dtype(torch::kFloat64));
+    check_rc(slayer_b200_num_spikes_loss(grad.data_ptr<float>(), row_sq.data_ptr<double>(), spikes.data_ptr<float>(),
+                                         desiredCount.data_ptr<float>(), filter.data_ptr<float>(), rows, T, filter.numel(),
+                                         start, stop, Ts, scale, current_stream()),
+             "numSpikesLoss");
+    return {row_sq.sum(), grad};
+}
+
 // ------------------------------------------------------------------ address events -> tensor
 static void check_events(const torch::Tensor &v, const char *name, torch::ScalarType dtype, int64_t count, const torch::Tensor &like)
 {
@@ -404,6 +429,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("unpackSpikes", &unpackSpikesCuda, "Bit-packed spike tensor -> fp32 (value where a bit is set) (CUDA)");
     m.def("getSpikesPacked", &getSpikesPackedCuda, "Get spikes, returned bit-packed (CUDA)");
     m.def("convPacked", &convPackedCuda, "Convolution in time of a bit-packed spike tensor (CUDA)");
+    m.def("numSpikesLoss", &numSpikesLossCuda, "Spike-count loss: sum of squared errors and gradient in one pass (CUDA)");
     m.def("binEvents", &binEventsCuda, "Address events -> spike tensor (CUDA)");
     m.def("binEventsPacked", &binEventsPackedCuda, "Address events -> bit-packed spike tensor (CUDA)");
     m.attr("backend") = "slayer_b200";

@@ -290,48 +290,44 @@ typedef unsigned long long f2;      // two packed fp32 values
 // fma.rn.ftz.f32x2 performs two independent single-precision fused multiply-adds on the halves
 // of 64-bit registers; each half rounds exactly like the scalar instruction, so results keep
 // their bits.  The FMA pipe does the same number of lane-operations per clock either way, but
-// the packed form needs half the issue slots, which leaves room for the shared-memory loads,
-// the register moves and the address arithmetic that otherwise compete with the FMAs for issue.
-// Every operand has to be a register pair:
-//   - a lane owns TWO rows (l and l + 32 of a 64-row tile); the sliding window is a ring of
-//     (row A, row B) sample pairs, refilled per group of four taps by one 128-bit load from each
-//     row and four register-pair moves;
+// the packed form needs half the issue slots, which leaves room for the shared-memory loads and
+// the address arithmetic that otherwise compete with the FMAs for issue.  Every operand has to
+// be a register pair, and a pair that has to be put together from two registers costs moves
+// that eat the gain, so the data is arranged to make the pairs natural:
+//   - a lane owns TWO rows (2l and 2l+1 of a 64-row tile); the tile the arithmetic reads
+//     interleaves the two rows sample by sample (A0 B0 A1 B1 ...), so one 128-bit load yields
+//     two ready (A_t, B_t) pairs and the sliding window is a ring of pairs;
 //   - taps sit in shared memory duplicated (f0 f0 f1 f1 ...), one 128-bit broadcast load
 //     yields two (f, f) pairs;
 //   - accumulators are pairs (outA[m], outB[m]).
-// The tile in shared memory has the layout of the scalar kernel (one row after the other, row
-// stride = 4 mod 8 words, filled by 16-byte cp.async), with 64 rows instead of 32.
-// One CTA per SM (two buffers of up to 64 rows x 428 samples), warps take 16-sample segments.
+// Global memory cannot be copied into the interleaved form efficiently (it would take 4-byte
+// copies), so a tile takes two steps: 16-byte cp.async copies land the next tile in a staging
+// buffer with plain rows while the current tile is being computed, and a short pass of all
+// warps re-packs staging -> interleaved (two 128-bit loads, two 128-bit stores per 8 samples)
+// between two barriers.  The same pass notes which sample positions hold a non-zero in any of
+// the 64 rows (see the zero-skipping segment below).  A bit-packed input is staged as words
+// and expanded by the re-pack pass.
+// One CTA per SM (staging + interleaved tile of up to 64 rows x 428 samples), warps take
+// 16-sample segments.
 // ---------------------------------------------------------------------------------------
 constexpr int kFir2Rows = 64;
 constexpr int kFir2MaxSamples = 428;     // staged samples per row: 2 buffers x 64 rows x 428 words fit one SM
 constexpr int kFir2MaskWords = 16;       // one bit per staged sample position (>= kFir2MaxSamples / 32, padded)
+constexpr int kFir2StageWords = 16;      // packed input: staged words per row (covers 428 samples at any bit offset)
 constexpr int kFir2ScanEvery = 8;        // dense mode: look at every 8th tile for zeros
 constexpr int kFir2SparsePercent = 45;   // a tile runs the zero-skipping path below this share of live positions
 
-__device__ __forceinline__ f2 pack2(float lo, float hi)
+// 64-bit load of one (row A, row B) sample pair
+__device__ __forceinline__ f2 ld1p(unsigned saddr)
 {
-    f2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-
-__device__ __forceinline__ float ld1(unsigned saddr)
-{
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr));
+    f2 v;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(saddr));
     return v;
 }
 
-// four (row A, row B) sample pairs from the two rows of a lane: xa = address in row A, the
-// same samples of row B lie `rowb` bytes further on
-__device__ __forceinline__ void ld4p(unsigned xa, unsigned rowb, f2 &p0, f2 &p1, f2 &p2, f2 &p3)
+__device__ __forceinline__ void st4(unsigned saddr, float a, float b, float c, float d)
 {
-    const float4 a = ld4(xa), b = ld4(xa + rowb);
-    p0 = pack2(a.x, b.x);
-    p1 = pack2(a.y, b.y);
-    p2 = pack2(a.z, b.z);
-    p3 = pack2(a.w, b.w);
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 __device__ __forceinline__ void ld2p(unsigned saddr, f2 &a, f2 &b)
@@ -375,10 +371,11 @@ __device__ __forceinline__ void fir2_group_n(f2 (&acc)[kFirSeg], const f2 (&w)[k
 // group: four sample pairs into the free ring quad, four tap pairs into the idle tap quad.
 template <int DIR, int PH>
 __device__ __forceinline__ void fir2_step(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing], f2 (&f)[2][4],
-                                          unsigned fp_next, unsigned xp, unsigned rowb)
+                                          unsigned fp_next, unsigned xp)
 {
     constexpr int base = win_reg<DIR, PH>(DIR < 0 ? -4 + kFirRing : kFirWin);
-    ld4p(xp, rowb, w[base], w[base + 1], w[base + 2], w[base + 3]);
+    ld2p(xp, w[base], w[base + 1]);
+    ld2p(xp + 16, w[base + 2], w[base + 3]);
     ld2p(fp_next, f[(PH + 1) & 1][0], f[(PH + 1) & 1][1]);
     ld2p(fp_next + 16, f[(PH + 1) & 1][2], f[(PH + 1) & 1][3]);
     fir2_group<DIR, PH, 4>(acc, w, f[PH & 1]);
@@ -386,15 +383,15 @@ __device__ __forceinline__ void fir2_step(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing],
 
 template <int DIR, int PH>
 __device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing], f2 (&f)[2][4],
-                                          unsigned fp_next, unsigned xp, unsigned rowb, int left, int tail)
+                                          unsigned fp_next, unsigned xp, int left, int tail)
 {
     if (left == 0) {
         if (tail) fir2_group_n<DIR, PH>(acc, w, f[PH & 1], tail);
         return;
     }
-    fir2_step<DIR, PH>(acc, w, f, fp_next, xp, rowb);
+    fir2_step<DIR, PH>(acc, w, f, fp_next, xp);
     if constexpr (PH + 1 < kFirPhases)
-        fir2_rest<DIR, PH + 1>(acc, w, f, fp_next + 32, xp + (DIR < 0 ? 0u - 16u : 16u), rowb, left - 1, tail);
+        fir2_rest<DIR, PH + 1>(acc, w, f, fp_next + 32, xp + (DIR < 0 ? 0u - 32u : 32u), left - 1, tail);
 }
 
 
@@ -404,24 +401,24 @@ __device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing],
 // bit per staged sample position of the tile (bit set = some row is non-zero there).  The live
 // positions of the segment's window are visited in the order that keeps every output's chain in
 // ascending tap order (conv: newest sample first; corr: oldest first); each costs 16 packed FMAs
-// with the 16 consecutive taps that connect it to the segment's outputs.  Taps outside [0, K)
-// are skipped by predicate, not multiplied as zeros, so non-finite samples behave as in the
-// dense form.  pos0 = tile position of the window's first sample.
+// with the 16 consecutive taps that connect it to the segment's outputs, read from a copy of the
+// taps with 16 zeros in front and behind: a tap outside [0, K) multiplies the sample by zero,
+// which changes nothing for finite samples (tiles that hold an Inf or NaN take the dense form).
+// pos0 = tile position of the window's first sample.
 template <int DIR>
-__device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const unsigned *colmask, unsigned xrow_tile0, unsigned rowb,
+__device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const unsigned *colmask, unsigned xrow_tile0,
                                                     unsigned fsA_addr, unsigned fsB_addr, int pos0, int K)
 {
     // window: positions pos0 .. pos0 + K + 14 (K - 1 past samples + 16 outputs)
     const int npos = K + kFirSeg - 1;
     // conv walks positions downwards from the last one, corr upwards from the first one
     for (int done = 0; done < npos;) {
-        // next live position at or after `done` in walking order
         const int p = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;
         const int word = p >> 5, bit = p & 31;
         unsigned m = colmask[word];
         int skip;
         if (DIR < 0) {
-            m &= bit == 31 ? 0xffffffffu : ((2u << bit) - 1u);         // bits 0 .. bit
+            m &= (2u << bit) - 1u;                                     // bits 0 .. bit
             skip = m ? bit - (31 - __clz(m)) : bit + 1;                // positions to step over
         } else {
             m &= 0xffffffffu << bit;                                   // bits bit .. 31
@@ -431,7 +428,7 @@ __device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const un
         if (!m || done >= npos) continue;
         const int q = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;  // the live position
         ++done;
-        const f2 x = pack2(ld1(xrow_tile0 + 4u * (unsigned)q), ld1(xrow_tile0 + rowb + 4u * (unsigned)q));
+        const f2 x = ld1p(xrow_tile0 + 8u * (unsigned)q);
         // conv: output m takes tap (pos0 + K - 1 + m) - q;  corr: tap q - pos0 - m
         const int a = DIR < 0 ? pos0 + K - 1 - q : q - pos0 - (kFirSeg - 1);      // lowest tap index of the 16
         const int n0 = a + kFirSeg;                                               // index into the padded table (>= 1)
@@ -439,23 +436,16 @@ __device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const un
         f2 f[kFirSeg];
 #pragma unroll
         for (int k = 0; k < kFirSeg / 2; ++k) ld2p(tp + 16 * k, f[2 * k], f[2 * k + 1]);
-        if (a >= 0 && a + kFirSeg <= K) {
 #pragma unroll
-            for (int mm = 0; mm < kFirSeg; ++mm) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
-        } else {
-#pragma unroll
-            for (int mm = 0; mm < kFirSeg; ++mm) {
-                const int tap = a + (DIR < 0 ? mm : kFirSeg - 1 - mm);
-                if (tap >= 0 && tap < K) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
-            }
-        }
+        for (int mm = 0; mm < kFirSeg; ++mm) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
     }
 }
 
 // V: width of the global accesses in floats (4, 2 or 1; T % V == 0 and both `in` (unless PK) and
 // `out` aligned to 4*V bytes).
 // PK: the input is a bit-packed spike tensor (`in` points to 32-bit words, ceil(T / 32) per row,
-// bit i of word w = sample 32 w + i is `spike_value`, else 0); the tile fill expands the bits.
+// bit i of word w = sample 32 w + i is `spike_value`, else 0); the words are staged and the
+// re-pack pass expands them.
 template <int DIR, int V, bool PK = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, 1)
 fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
@@ -466,13 +456,14 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
     const int WX = Tt + sh.halo;
     const int KP = ((K + 3) & ~3) + 4;       // taps, zero padded; one spare quad for the look-ahead load
     const int KS = ((K + 3) & ~3) + 2 * kFirSeg;   // taps with 16 zeros in front and at least 16 behind (sparse path)
+    const int SXs = PK ? kFir2StageWords : ((WX + 3) & ~3);     // staging: words per row
     float *fs = smem;                        // 2 * KP words: every tap twice
     float *fsA = fs + 2 * KP;                // 2 * KS words: padded taps, every tap twice
     float *fsB = fsA + 2 * KS;               // the same, one tap further on (16-byte alignment for odd starts)
-    unsigned *colmask = reinterpret_cast<unsigned *>(fsB + 2 * KS);     // kFir2MaskWords words
-    float *xbuf = reinterpret_cast<float *>(colmask + kFir2MaskWords);  // 2 x [64 rows x SX]
-    const int tile_words = kFir2Rows * sh.SX;
-    const unsigned rowb = 4u * (unsigned)(32 * sh.SX);      // bytes from a lane's row A to its row B
+    unsigned *colmask = reinterpret_cast<unsigned *>(fsB + 2 * KS);     // 2 x kFir2MaskWords words, then 2 flags (+2 pad)
+    unsigned *nonfinite = colmask + 2 * kFir2MaskWords;
+    float *stage = reinterpret_cast<float *>(nonfinite + 4);            // [64 rows x SXs]
+    float *xbuf = stage + kFir2Rows * SXs;                              // [32 row pairs x SX], interleaved
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -491,38 +482,36 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
         fsB[2 * n] = b;
         fsB[2 * n + 1] = b;
     }
+    for (int i = threadIdx.x; i < 2 * kFir2MaskWords + 4; i += blockDim.x) colmask[i] = 0u;
 
-    // asynchronous copy of one input tile: warp w fills rows w, w+nwarps, ... from contiguous
-    // global segments; samples outside the row (or rows outside the array) become zeros.  With
-    // 16-byte accesses a lane copies at most four chunks per row, and which of them lie inside
-    // [0, T) is the same for every row of the tile, so that is worked out once per tile.
+    // asynchronous copy of one input tile into the staging buffer: warp w fills rows w,
+    // w+nwarps, ... from contiguous global segments; samples outside the row (or rows outside
+    // the array) become zeros.  With 16-byte accesses a lane copies at most four chunks per row,
+    // and which of them lie inside [0, T) is the same for every row of the tile.
+    const unsigned stage_saddr = (unsigned)__cvta_generic_to_shared(stage);
     const unsigned xbuf_saddr = (unsigned)__cvta_generic_to_shared(xbuf);
-    auto fill = [&](int buf, int64_t tile) {
+    auto tile_origin = [&](int64_t tile, int64_t &row0, int &t0) {
         const int64_t rb = tile / sh.ttiles;
-        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
-        const int64_t row0 = rb * kFir2Rows;
+        t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        row0 = rb * kFir2Rows;
+    };
+    auto fill = [&](int64_t tile) {
+        int64_t row0;
+        int t0;
+        tile_origin(tile, row0, t0);
         const int64_t nrow = rows - row0;
         const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
         if constexpr (PK) {
-            // packed input: a lane fetches the word that holds its sample (neighbouring lanes share
-            // it) and stores the expanded sample; ordinary stores, ordered by the tile barrier
-            constexpr int kCols = (kFir2MaxSamples + 31) / 32;     // 14
+            // the words that hold samples g0 .. g0 + WX - 1 of each row, word index w_lo + lane
             const unsigned *words_in = reinterpret_cast<const unsigned *>(in);
             const int words = (T + 31) >> 5;
-            for (int r = warp; r < kFir2Rows; r += nwarps) {
-                const bool row_ok = r < nrow;
-                const unsigned *src = words_in + (row0 + (row_ok ? r : 0)) * (int64_t)words;
-                float *dst = xbuf + buf * tile_words + r * sh.SX + lane;
-                unsigned wv[kCols];
-#pragma unroll
-                for (int k = 0; k < kCols; ++k) {
-                    const int gt = g0 + lane + 32 * k;
-                    const bool ok = row_ok && lane + 32 * k < WX && gt >= 0 && gt < T;
-                    wv[k] = ok ? (__ldg(src + (gt >> 5)) >> (gt & 31)) & 1u : 0u;
+            const int wi = (g0 >> 5) + lane;             // arithmetic shift: floor for negative g0
+            const bool word_ok = lane < kFir2StageWords && wi >= 0 && wi < words;
+            if (lane < kFir2StageWords) {
+                for (int r = warp; r < kFir2Rows; r += nwarps) {
+                    const bool ok = word_ok && r < nrow;
+                    cp_async<4>(stage + r * kFir2StageWords + lane, ok ? words_in + (row0 + r) * (int64_t)words + wi : words_in, ok);
                 }
-#pragma unroll
-                for (int k = 0; k < kCols; ++k)
-                    if (lane + 32 * k < WX) dst[32 * k] = wv[k] ? spike_value : 0.0f;
             }
         } else if constexpr (V == 4) {
             constexpr int kChunks = (kFir2MaxSamples + 127) / 128;     // 4
@@ -538,7 +527,7 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
             for (int r = warp; r < kFir2Rows; r += nwarps) {
                 const bool row_ok = r < nrow;
                 const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
-                const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + r * sh.SX + lane * 4);
+                const unsigned dst = stage_saddr + 4u * (unsigned)(r * SXs + lane * 4);
 #pragma unroll
                 for (int k = 0; k < kChunks; ++k) {
                     if (nbytes[k] < 0) continue;
@@ -547,11 +536,10 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
                 }
             }
         } else {
-            float *xs = xbuf + buf * tile_words;
             for (int r = warp; r < kFir2Rows; r += nwarps) {
                 const bool row_ok = r < nrow;
                 const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
-                float *dst = xs + r * sh.SX;
+                float *dst = stage + r * SXs;
                 for (int pcol = lane * V; pcol < WX; pcol += 32 * V) {
                     const int gt = g0 + pcol;
                     const bool ok = row_ok && gt >= 0 && gt < T;
@@ -562,53 +550,99 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
         cp_async_commit();
     };
 
+    // Re-pack the staged tile into the interleaved tile: pair p = rows 2p and 2p+1.  With `note`
+    // the pass also records, in mask[] (one bit per sample position, set by atomic OR), where any
+    // row is non-zero, and in *flag whether any sample is Inf or NaN.
+    auto repack = [&](int64_t tile, bool note, unsigned *mask, unsigned *flag) {
+        if constexpr (PK) {
+            int64_t row0;
+            int t0;
+            tile_origin(tile, row0, t0);
+            const int g0 = DIR < 0 ? t0 - sh.halo : t0;
+            const int w_lo = g0 >> 5;
+            const unsigned *sw = reinterpret_cast<const unsigned *>(stage);
+            for (int p = warp; p < kFir2Rows / 2; p += nwarps) {
+                const unsigned *wa = sw + (2 * p) * kFir2StageWords, *wb = wa + kFir2StageWords;
+                float *dst = xbuf + p * sh.SX;
+                for (int pos = lane; pos < ((WX + 31) & ~31); pos += 32) {
+                    const int gt = g0 + pos;
+                    const int wi = (gt >> 5) - w_lo;                 // 0 .. kFir2StageWords - 1
+                    const unsigned inside = gt < T ? 1u : 0u;           // bits past the row end are ignored
+                    const unsigned ba = (wa[wi] >> (gt & 31)) & inside, bb = (wb[wi] >> (gt & 31)) & inside;
+                    if (pos < WX)
+                        *reinterpret_cast<float2 *>(dst + 2 * pos) = make_float2(ba ? spike_value : 0.0f, bb ? spike_value : 0.0f);
+                    const unsigned live = __ballot_sync(0xffffffffu, pos < WX && (ba | bb));
+                    if (note && lane == 0 && live) atomicOr(mask + (pos >> 5), live);
+                }
+            }
+        } else {
+            const int chunks = SXs >> 2;                 // 16-byte chunks per staged row
+            for (int p = warp; p < kFir2Rows / 2; p += nwarps) {
+                const unsigned sa = stage_saddr + 4u * (unsigned)((2 * p) * SXs), sb = sa + 4u * (unsigned)SXs;
+                const unsigned dst = xbuf_saddr + 4u * (unsigned)(p * sh.SX);
+                for (int c = lane; c < chunks; c += 32) {
+                    const float4 a = ld4(sa + 16u * c), b = ld4(sb + 16u * c);
+                    st4(dst + 32u * c, a.x, b.x, a.y, b.y);
+                    st4(dst + 32u * c + 16u, a.z, b.z, a.w, b.w);
+                    if (note) {
+                        const unsigned m0 = __float_as_uint(a.x) | __float_as_uint(b.x), m1 = __float_as_uint(a.y) | __float_as_uint(b.y);
+                        const unsigned m2 = __float_as_uint(a.z) | __float_as_uint(b.z), m3 = __float_as_uint(a.w) | __float_as_uint(b.w);
+                        const unsigned nib = ((m0 & 0x7fffffffu) ? 1u : 0u) | ((m1 & 0x7fffffffu) ? 2u : 0u) |
+                                             ((m2 & 0x7fffffffu) ? 4u : 0u) | ((m3 & 0x7fffffffu) ? 8u : 0u);
+                        if (nib) atomicOr(mask + (c >> 3), nib << ((c & 7) * 4));
+                        // an exponent of all ones in either row: the OR is not enough, test both
+                        const bool bad = ((__float_as_uint(a.x) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.x) & 0x7f800000u) == 0x7f800000u) |
+                                         ((__float_as_uint(a.y) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.y) & 0x7f800000u) == 0x7f800000u) |
+                                         ((__float_as_uint(a.z) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.z) & 0x7f800000u) == 0x7f800000u) |
+                                         ((__float_as_uint(a.w) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.w) & 0x7f800000u) == 0x7f800000u);
+                        if (bad) *flag = 1u;
+                    }
+                }
+            }
+        }
+    };
+
     const int groups = K >> 2;          // full groups of 4 taps
     const int tail = K & 3;
-    constexpr unsigned step = DIR < 0 ? 0u - 16u : 16u;   // bytes the window moves per group (mod 2^32)
+    constexpr unsigned step = DIR < 0 ? 0u - 32u : 32u;   // bytes the window moves per group (mod 2^32)
     const unsigned fs_addr = (unsigned)__cvta_generic_to_shared(fs);
     const unsigned fsA_addr = (unsigned)__cvta_generic_to_shared(fsA);
     const unsigned fsB_addr = (unsigned)__cvta_generic_to_shared(fsB);
     const int mask_words = (WX + 31) >> 5;
-    const bool may_skip = sparse_ok && K >= 8;
+    const bool may_skip = sparse_ok && K >= 8 && (!PK || (__float_as_uint(spike_value) & 0x7f800000u) != 0x7f800000u);
     bool sparse = false;                 // the last tile looked at was mostly zeros (same value in every thread)
 
     int64_t tile = blockIdx.x;
-    if (tile < ntiles) fill(0, tile);
+    if (tile < ntiles) fill(tile);
     for (int it = 0; tile < ntiles; tile += gridDim.x, ++it) {
         cp_async_wait<0>();
-        __syncthreads();                 // this tile has landed; the other buffer is free again
+        __syncthreads();                 // the staged tile has landed; nobody reads the interleaved tile any more
+        // zeros are looked for in every tile while tiles are sparse (and always for packed input,
+        // where it costs one ballot), else in one tile out of kFir2ScanEvery
+        const bool note = may_skip && (PK || sparse || (it % kFir2ScanEvery) == 0);
+        unsigned *mask = colmask + (it & 1) * kFir2MaskWords;
+        repack(tile, note, mask, nonfinite + (it & 1));
+        __syncthreads();                 // the interleaved tile is complete; the staging buffer is free again
         const int64_t next = tile + gridDim.x;
-        if (next < ntiles) fill((it + 1) & 1, next);
-
-        const int64_t rb = tile / sh.ttiles;
-        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
-        const int64_t rowA = rb * kFir2Rows + lane;
-        // byte address of tile position 0 of this lane's row A
-        const unsigned xtile0 = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + lane * sh.SX);
-        const unsigned xrow = xtile0 + 4u * (unsigned)(DIR < 0 ? sh.halo : 0);
-
-        // Which sample positions hold a non-zero in any of the 64 rows?  Looked at for every tile
-        // while tiles are sparse, else for one tile in kFir2ScanEvery.  Lane = position, loop over
-        // the rows: the OR of the magnitude bits, one ballot per 32 positions.
-        if (may_skip && (sparse || (it % kFir2ScanEvery) == 0)) {
-            for (int wd = warp; wd < mask_words; wd += nwarps) {
-                const int pos = 32 * wd + lane;
-                unsigned bits = 0u;
-                if (pos < WX) {
-                    const unsigned col = xbuf_saddr + 4u * (unsigned)((it & 1) * tile_words + pos);
-#pragma unroll 8
-                    for (int r = 0; r < kFir2Rows; ++r) bits |= __float_as_uint(ld1(col + 4u * (unsigned)(r * sh.SX)));
-                }
-                const unsigned live = __ballot_sync(0xffffffffu, (bits & 0x7fffffffu) != 0u);
-                if (lane == 0) colmask[wd] = live;
-            }
-            __syncthreads();
+        if (next < ntiles) fill(next);
+        if (note) {
             int live = 0;
-            for (int wd = 0; wd < mask_words; ++wd) live += __popc(colmask[wd]);
-            sparse = live * 100 < kFir2SparsePercent * WX;
-        } else if (may_skip) {
+            for (int wd = 0; wd < mask_words; ++wd) live += __popc(mask[wd]);
+            sparse = nonfinite[it & 1] == 0u && live * 100 < kFir2SparsePercent * WX;
+        } else {
             sparse = false;
         }
+        // clear the other mask for the next tile (its last readers passed the first barrier)
+        if (threadIdx.x < kFir2MaskWords) colmask[((it + 1) & 1) * kFir2MaskWords + threadIdx.x] = 0u;
+        if (threadIdx.x == kFir2MaskWords) nonfinite[(it + 1) & 1] = 0u;
+
+        int64_t row0;
+        int t0;
+        tile_origin(tile, row0, t0);
+        const int64_t rowA = row0 + 2 * lane;
+        // byte address of tile position 0 of this lane's row pair
+        const unsigned xtile0 = xbuf_saddr + 4u * (unsigned)(lane * sh.SX);
+        const unsigned xrow = xtile0 + 8u * (unsigned)(DIR < 0 ? sh.halo : 0);
 
         for (int seg = warp; seg < sh.nseg; seg += nwarps) {
             const int tb = seg * kFirSeg;
@@ -620,31 +654,30 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
             if (sparse) {
                 // window of the segment in tile positions: conv starts K - 1 samples before the
                 // first output (tile position halo + tb), corr at the first output
-                fir2_sparse_segment<DIR>(acc, colmask, xtile0, rowb, fsA_addr, fsB_addr,
-                                         DIR < 0 ? sh.halo + tb - (K - 1) : tb, K);
+                fir2_sparse_segment<DIR>(acc, mask, xtile0, fsA_addr, fsB_addr, DIR < 0 ? sh.halo + tb - (K - 1) : tb, K);
             } else {
                 // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
                 f2 w[kFirRing];
-                const unsigned x0 = xrow + 4u * (unsigned)tb - (DIR < 0 ? 16u : 0u);
+                const unsigned x0 = xrow + 8u * (unsigned)tb - (DIR < 0 ? 32u : 0u);
 #pragma unroll
-                for (int q = 0; q < kFirWin / 4; ++q) ld4p(x0 + 16 * q, rowb, w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-                unsigned xp = DIR < 0 ? x0 - 16 : x0 + 4 * kFirWin;    // next four samples to fetch
+                for (int q = 0; q < kFirWin / 2; ++q) ld2p(x0 + 16 * q, w[2 * q], w[2 * q + 1]);
+                unsigned xp = DIR < 0 ? x0 - 32 : x0 + 8 * kFirWin;    // next four sample pairs to fetch
                 unsigned fp = fs_addr;
                 f2 f[2][4];
                 ld2p(fp, f[0][0], f[0][1]);
                 ld2p(fp + 16, f[0][2], f[0][3]);
                 int g = 0;
                 for (; g + kFirPhases <= groups; g += kFirPhases) {
-                    fir2_step<DIR, 0>(acc, w, f, fp + 32, xp, rowb);
-                    fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step, rowb);
-                    fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step, rowb);
-                    fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step, rowb);
-                    fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step, rowb);
-                    fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step, rowb);
+                    fir2_step<DIR, 0>(acc, w, f, fp + 32, xp);
+                    fir2_step<DIR, 1>(acc, w, f, fp + 64, xp + step);
+                    fir2_step<DIR, 2>(acc, w, f, fp + 96, xp + 2 * step);
+                    fir2_step<DIR, 3>(acc, w, f, fp + 128, xp + 3 * step);
+                    fir2_step<DIR, 4>(acc, w, f, fp + 160, xp + 4 * step);
+                    fir2_step<DIR, 5>(acc, w, f, fp + 192, xp + 5 * step);
                     xp += kFirPhases * step;
                     fp += 32 * kFirPhases;
                 }
-                fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, rowb, groups - g, tail);
+                fir2_rest<DIR, 0>(acc, w, f, fp + 32, xp, groups - g, tail);
             }
 
             float oa[kFirSeg], ob[kFirSeg];
@@ -657,7 +690,7 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
             const int left = T - (t0 + tb);          // > 0, multiple of V
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int64_t row = rowA + 32 * h;
+                const int64_t row = rowA + h;
                 if (row >= rows) continue;
                 const float *o = h ? ob : oa;
                 float *dst = out + row * (int64_t)T + t0 + tb;
@@ -769,7 +802,9 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
     }
     sh.nseg = (int)ceil_div(segs, sh.ttiles);
     sh.ttiles = (int)ceil_div(segs, sh.nseg);
-    sh.SX = pad_stride(sh.nseg * kFirSeg + sh.halo);
+    // words per row pair of the interleaved tile: = 4 (mod 8), so that the 128-bit loads of a
+    // quarter warp fall into distinct bank groups
+    sh.SX = pad_stride(2 * (sh.nseg * kFirSeg + sh.halo));
     // Warps per CTA: warp w runs on scheduler w % 4 and takes segments w, w+nw, ...; pick the
     // multiple of four whose busiest scheduler has the least work, preferring fewer warps.
     if (sh.nseg <= 8) {
@@ -802,7 +837,10 @@ static int launch_fir2(float *out, const float *in, const float *filt,
     if (!taken) return SLAYER_B200_OK;
     const int64_t ntiles = ceil_div(rows, kFir2Rows) * sh.ttiles;
     const size_t kp = (size_t)((Keff + 3) & ~3LL);
-    const size_t smem = sizeof(float) * (2 * (kp + 4) + 4 * (kp + 2 * kFirSeg) + kFir2MaskWords + 2 * (size_t)kFir2Rows * sh.SX);
+    const size_t wx = (size_t)sh.nseg * kFirSeg + sh.halo;
+    const size_t stage_words = (size_t)kFir2Rows * (PK ? (size_t)kFir2StageWords : ((wx + 3) & ~(size_t)3));
+    const size_t smem = sizeof(float) * (2 * (kp + 4) + 4 * (kp + 2 * kFirSeg) + 2 * kFir2MaskWords + 4 + stage_words +
+                                         (size_t)(kFir2Rows / 2) * sh.SX);
     const int vw = PK ? tile_vec_width(T, {out}) : tile_vec_width(T, {out, in});
     auto kern = vw == 4 ? fir2_kernel<DIR, 4, PK> : (vw == 2 ? fir2_kernel<DIR, 2, PK> : fir2_kernel<DIR, 1, PK>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);

@@ -16,7 +16,23 @@ in the backward pass, exactly as the reference's ``spikeDesired`` built from ``.
 import numpy as np
 import torch
 
-from .layer import spikeLayer
+from .layer import slayerCuda, spikeLayer
+
+
+class _NumSpikesFunction(torch.autograd.Function):
+    """Value and gradient of the spike-count loss from one kernel (``slayerCuda.numSpikesLoss``):
+    forward keeps the gradient for a unit upstream gradient, backward scales it."""
+
+    @staticmethod
+    def forward(ctx, spikeOut, desiredCount, srmKernel, start, stop, Ts, scale):
+        sq, grad = slayerCuda.numSpikesLoss(spikeOut.contiguous(), desiredCount, srmKernel, start, stop, Ts, scale)
+        ctx.save_for_backward(grad)
+        return (sq * (0.5 * Ts)).float()
+
+    @staticmethod
+    def backward(ctx, gradLoss):
+        (grad,) = ctx.saved_tensors
+        return grad * gradLoss, None, None, None, None, None, None
 
 
 class spikeLoss(torch.nn.Module):
@@ -29,6 +45,7 @@ class spikeLoss(torch.nn.Module):
         self.simulation = networkDescriptor['simulation']
         self.errorDescriptor = networkDescriptor['training']['error']
         self.slayer = slayerClass(self.neuron, self.simulation)
+        self.fused = True          # numSpikes: one fused kernel; False = the tensor expressions
 
     def spikeTime(self, spikeOut, spikeDesired):
         """Van Rossum-like distance between two spike trains (src/spikeLoss.py:39-59)."""
@@ -47,6 +64,14 @@ class spikeLoss(torch.nn.Module):
         stop = int(np.rint(region['stop'] / Ts))
         T = spikeOut.shape[-1]
         lo, hi = slice(start, stop).indices(T)[:2]        # the slice the reference takes, made explicit
+
+        if spikeOut.is_cuda and spikeOut.dtype == torch.float32 and self.fused and stop != start and T <= 8192:
+            # one kernel for the loss and its gradient (same arithmetic as the expressions below)
+            onehot = desiredClass.to(spikeOut.device)
+            desired = torch.where(onehot == True, float(count[True]), float(count[False]))    # noqa: E712
+            desired = desired.to(torch.float32).expand(spikeOut.shape[:-1] + (1,)).reshape(-1).contiguous()
+            return _NumSpikesFunction.apply(spikeOut, desired, self.slayer.srmKernel, start, stop, float(Ts),
+                                            float(numSpikesScale))
 
         with torch.no_grad():
             inside = torch.zeros(T, dtype=spikeOut.dtype, device=spikeOut.device)

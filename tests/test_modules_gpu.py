@@ -311,3 +311,34 @@ def test_num_spikes_loss_against_a_host_restatement():
         grad[..., :T - i] += kv * e[..., i:]
     np.testing.assert_allclose(x.grad.cpu().numpy(), grad * Ts * Ts, rtol=2e-4, atol=1e-5)
     assert ours_loss.spikeClassifier.getClass(x.detach()).shape == (5,)
+
+
+@pytest.mark.parametrize("Ts,region,shape", [(1.0, (0, 300), (64, 10, 1, 1, 300)), (1.0, (40, 260), (5, 10, 1, 1, 300)),
+                                             (0.5, (10, 120), (3, 4, 2, 2, 300)), (1.0, (0, 2000), (2, 7, 1, 1, 2000))])
+def test_num_spikes_loss_fused_kernel_equals_the_tensor_expressions(Ts, region, shape):
+    """The one-kernel numSpikes (value and gradient) against the tensor-expression form of the
+    same module, which follows src/spikeLoss.py:85-104 line by line: loss within 1e-6, gradient
+    within 1e-5 of its largest entry; and a scaled upstream gradient scales the result."""
+    from slayerpytorch_b200 import loss as ours_loss
+    T = shape[-1]
+    params = {"neuron": {"type": "SRMALPHA", "theta": 10, "tauSr": 10.0, "tauRef": 1.0, "scaleRef": 2,
+                         "tauRho": 1, "scaleRho": 1},
+              "simulation": {"Ts": Ts, "tSample": int(T * Ts), "nSample": 12},
+              "training": {"error": {"type": "NumSpikes", "tgtSpikeRegion": {"start": region[0], "stop": region[1]},
+                                     "tgtSpikeCount": {True: 60, False: 10}}}}
+    g = torch.Generator().manual_seed(T + shape[0])
+    spikes = ((torch.rand(shape, generator=g) < 0.08).float() / Ts).cuda()
+    desired = (torch.rand(shape[:2] + (1, 1, 1), generator=g) < 0.2).float()
+    results = []
+    for fused in (True, False):
+        err = ours_loss.spikeLoss(params).cuda()
+        err.fused = fused
+        x = spikes.clone().requires_grad_(True)
+        loss = err.numSpikes(x, desired, 0.7)
+        (3.0 * loss).backward()
+        results.append((loss.detach(), x.grad))
+    (la, ga), (lb, gb) = results
+    assert la.dtype == torch.float32 and la.dim() == 0
+    torch.testing.assert_close(la, lb, rtol=1e-6, atol=0)
+    torch.testing.assert_close(ga, gb, rtol=1e-5, atol=1e-5 * gb.abs().max().item())
+    assert ga.abs().sum() > 0
