@@ -290,10 +290,11 @@ int slayer_b200_selftest_bounded_wait(int polls, void *stream);
 int slayer_b200_set_tma(int enable);
 
 /*
- * Enable (non-zero) or disable (zero, the default) the packed form of the conv / corr kernel
- * (two rows per lane, two-wide fp32 FMAs, zero skipping); returns the previous setting.
- * Disabled, the scalar kernel runs; both compute the same bits.  It has no counterpart in the
- * reference.
+ * Select the conv / corr kernel; returns the previous setting.  0: the scalar kernel.  1: the
+ * packed kernel (two rows per lane, two-wide fp32 FMAs, zero skipping) with its tile size chosen
+ * per launch; 2: the packed kernel with half-size tiles (two CTAs per SM) wherever they fit;
+ * 3: the packed kernel with full-size tiles (one CTA per SM).  All compute the same bits.  It has
+ * no counterpart in the reference.
  */
 int slayer_b200_set_fir_packed(int enable);
 

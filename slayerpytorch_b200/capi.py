@@ -90,9 +90,11 @@ def device_status():
     return value.value
 
 
-def set_fir_packed(enable):
-    """Enable/disable the packed conv / corr kernel; returns the previous setting."""
-    return bool(load().slayer_b200_set_fir_packed(1 if enable else 0))
+def set_fir_packed(mode):
+    """Select the conv / corr kernel: 0 / False = scalar, 1 / True = packed (tile size chosen per
+    launch), 2 = packed with half-size tiles (two CTAs per SM), 3 = packed with full-size tiles.
+    Returns the previous setting."""
+    return int(load().slayer_b200_set_fir_packed(int(mode)))
 
 
 def set_fir_skip_zeros(enable):

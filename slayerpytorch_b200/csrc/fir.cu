@@ -311,8 +311,10 @@ typedef unsigned long long f2;      // two packed fp32 values
 // 16-sample segments.
 // ---------------------------------------------------------------------------------------
 constexpr int kFir2Rows = 64;
-constexpr int kFir2MaxSamples = 428;     // staged samples per row: 2 buffers x 64 rows x 428 words fit one SM
-constexpr int kFir2MaskWords = 16;       // one bit per staged sample position (>= kFir2MaxSamples / 32, padded)
+constexpr int kFir2MaxSamples = 428;     // staged samples per row: staging + tile of 64 rows x 428 words fit one SM
+constexpr int kFir2HalfSamples = 212;    // ... and of 64 rows x 212 words fit twice
+constexpr int kFir2MaskWords = 20;       // one bit per staged sample position (14 words for 428 samples) plus the
+                                         // words a segment's 128-bit window may read past them
 constexpr int kFir2StageWords = 16;      // packed input: staged words per row (covers 428 samples at any bit offset)
 constexpr int kFir2ScanEvery = 8;        // dense mode: look at every 8th tile for zeros
 constexpr int kFir2SparsePercent = 45;   // a tile runs the zero-skipping path below this share of live positions
@@ -405,39 +407,45 @@ __device__ __forceinline__ void fir2_rest(f2 (&acc)[kFirSeg], f2 (&w)[kFirRing],
 // taps with 16 zeros in front and behind: a tap outside [0, K) multiplies the sample by zero,
 // which changes nothing for finite samples (tiles that hold an Inf or NaN take the dense form).
 // pos0 = tile position of the window's first sample.
+constexpr int kFir2WinWords = 4;         // the zero-skipping segment holds its window's mask in 4 registers
+constexpr int kFir2SparseMaxTaps = 32 * kFir2WinWords - kFirSeg + 1;      // 113: K + 15 positions fit 128 bits
+
 template <int DIR>
 __device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const unsigned *colmask, unsigned xrow_tile0,
                                                     unsigned fsA_addr, unsigned fsB_addr, int pos0, int K)
 {
-    // window: positions pos0 .. pos0 + K + 14 (K - 1 past samples + 16 outputs)
+    // window: positions pos0 .. pos0 + K + 14 (K - 1 past samples + 16 outputs); its mask, bit j of
+    // the 128-bit value = position pos0 + j, is cut out of the tile's mask once
     const int npos = K + kFirSeg - 1;
-    // conv walks positions downwards from the last one, corr upwards from the first one
-    for (int done = 0; done < npos;) {
-        const int p = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;
-        const int word = p >> 5, bit = p & 31;
-        unsigned m = colmask[word];
-        int skip;
-        if (DIR < 0) {
-            m &= (2u << bit) - 1u;                                     // bits 0 .. bit
-            skip = m ? bit - (31 - __clz(m)) : bit + 1;                // positions to step over
-        } else {
-            m &= 0xffffffffu << bit;                                   // bits bit .. 31
-            skip = m ? (__ffs(m) - 1) - bit : 32 - bit;
+    const int w0 = pos0 >> 5, sh = pos0 & 31;
+    unsigned m[kFir2WinWords];
+#pragma unroll
+    for (int k = 0; k < kFir2WinWords; ++k) {
+        const unsigned lo = colmask[w0 + k], hi = colmask[w0 + k + 1];       // the mask array is padded
+        m[k] = __funnelshift_r(lo, hi, sh);
+        const int left = npos - 32 * k;                                        // window bits in this word
+        if (left < 32) m[k] &= left > 0 ? (1u << left) - 1u : 0u;
+    }
+    // conv walks the live positions downwards from the last one, corr upwards from the first one
+#pragma unroll
+    for (int kk = 0; kk < kFir2WinWords; ++kk) {
+        const int k = DIR < 0 ? kFir2WinWords - 1 - kk : kk;
+        unsigned mk = m[k];
+        while (mk) {
+            const int b = DIR < 0 ? 31 - __clz(mk) : __ffs(mk) - 1;
+            mk &= ~(1u << b);
+            const int j = 32 * k + b;                                          // position pos0 + j
+            const f2 x = ld1p(xrow_tile0 + 8u * (unsigned)(pos0 + j));
+            // conv: output mm takes tap (K - 1 + mm) - j;  corr: tap j - mm
+            const int a = DIR < 0 ? K - 1 - j : j - (kFirSeg - 1);             // lowest tap index of the 16
+            const int n0 = a + kFirSeg;                                        // index into the padded table (>= 1)
+            const unsigned tp = ((n0 & 1) ? fsB_addr + 8u * (unsigned)(n0 - 1) : fsA_addr + 8u * (unsigned)n0);
+            f2 f[kFirSeg];
+#pragma unroll
+            for (int q = 0; q < kFirSeg / 2; ++q) ld2p(tp + 16 * q, f[2 * q], f[2 * q + 1]);
+#pragma unroll
+            for (int mm = 0; mm < kFirSeg; ++mm) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
         }
-        done += skip;
-        if (!m || done >= npos) continue;
-        const int q = DIR < 0 ? pos0 + npos - 1 - done : pos0 + done;  // the live position
-        ++done;
-        const f2 x = ld1p(xrow_tile0 + 8u * (unsigned)q);
-        // conv: output m takes tap (pos0 + K - 1 + m) - q;  corr: tap q - pos0 - m
-        const int a = DIR < 0 ? pos0 + K - 1 - q : q - pos0 - (kFirSeg - 1);      // lowest tap index of the 16
-        const int n0 = a + kFirSeg;                                               // index into the padded table (>= 1)
-        const unsigned tp = ((n0 & 1) ? fsB_addr + 8u * (unsigned)(n0 - 1) : fsA_addr + 8u * (unsigned)n0);
-        f2 f[kFirSeg];
-#pragma unroll
-        for (int k = 0; k < kFirSeg / 2; ++k) ld2p(tp + 16 * k, f[2 * k], f[2 * k + 1]);
-#pragma unroll
-        for (int mm = 0; mm < kFirSeg; ++mm) fma2_acc(acc[mm], x, f[DIR < 0 ? mm : kFirSeg - 1 - mm]);
     }
 }
 
@@ -590,12 +598,11 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
                         const unsigned nib = ((m0 & 0x7fffffffu) ? 1u : 0u) | ((m1 & 0x7fffffffu) ? 2u : 0u) |
                                              ((m2 & 0x7fffffffu) ? 4u : 0u) | ((m3 & 0x7fffffffu) ? 8u : 0u);
                         if (nib) atomicOr(mask + (c >> 3), nib << ((c & 7) * 4));
-                        // an exponent of all ones in either row: the OR is not enough, test both
-                        const bool bad = ((__float_as_uint(a.x) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.x) & 0x7f800000u) == 0x7f800000u) |
-                                         ((__float_as_uint(a.y) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.y) & 0x7f800000u) == 0x7f800000u) |
-                                         ((__float_as_uint(a.z) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.z) & 0x7f800000u) == 0x7f800000u) |
-                                         ((__float_as_uint(a.w) & 0x7f800000u) == 0x7f800000u) | ((__float_as_uint(b.w) & 0x7f800000u) == 0x7f800000u);
-                        if (bad) *flag = 1u;
+                        // 0 * v is NaN exactly when v is Inf or NaN, and NaN survives the sum
+                        float z = a.x * 0.0f;
+                        z = fmaf(a.y, 0.0f, z); z = fmaf(a.z, 0.0f, z); z = fmaf(a.w, 0.0f, z);
+                        z = fmaf(b.x, 0.0f, z); z = fmaf(b.y, 0.0f, z); z = fmaf(b.z, 0.0f, z); z = fmaf(b.w, 0.0f, z);
+                        if (z != z) *flag = 1u;
                     }
                 }
             }
@@ -609,7 +616,7 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
     const unsigned fsA_addr = (unsigned)__cvta_generic_to_shared(fsA);
     const unsigned fsB_addr = (unsigned)__cvta_generic_to_shared(fsB);
     const int mask_words = (WX + 31) >> 5;
-    const bool may_skip = sparse_ok && K >= 8 && (!PK || (__float_as_uint(spike_value) & 0x7f800000u) != 0x7f800000u);
+    const bool may_skip = sparse_ok && K >= 8 && K <= kFir2SparseMaxTaps && (!PK || (__float_as_uint(spike_value) & 0x7f800000u) != 0x7f800000u);
     bool sparse = false;                 // the last tile looked at was mostly zeros (same value in every thread)
 
     int64_t tile = blockIdx.x;
@@ -784,10 +791,10 @@ static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
 }
 
 // Tile shape of the packed kernel (64-row tiles, one CTA per SM); false if the filter is too long.
-static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
+static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh, int max_samples)
 {
     sh.halo = (int)(((K + 3) & ~3LL) + 8);     // taps rounded up plus two quads of look-ahead
-    const int room = kFir2MaxSamples - 4 - sh.halo;           // samples left for outputs (4 = stride padding)
+    const int room = max_samples - 4 - sh.halo;               // samples left for outputs (4 = stride padding)
     const int nseg_max = room / kFirSeg;
     if (nseg_max < 1) return false;
     const int64_t segs = ceil_div(T, kFirSeg);
@@ -832,8 +839,14 @@ static int launch_fir2(float *out, const float *in, const float *filt,
                        int64_t rows, int64_t T, int64_t Keff, float Ts, cudaStream_t stream, bool &taken,
                        float spike_value = 0.0f)
 {
+    // Two CTAs per SM with half-size tiles (more warps to keep the FMA pipe busy across barriers,
+    // and one CTA's tile copy overlaps the other's arithmetic) where a half-size tile still has
+    // room for five segments next to the filter's halo; else one CTA per SM with full-size tiles.
     FirShape sh;
-    taken = fir2_shape(rows, T, Keff, sh);
+    const int halo = (int)(((Keff + 3) & ~3LL) + 8);
+    const int mode = g_fir_packed.load();
+    const bool half = mode == 2 ? true : (mode == 3 ? false : (kFir2HalfSamples - 4 - halo) / kFirSeg >= 5);
+    taken = (half && fir2_shape(rows, T, Keff, sh, kFir2HalfSamples)) || fir2_shape(rows, T, Keff, sh, kFir2MaxSamples);
     if (!taken) return SLAYER_B200_OK;
     const int64_t ntiles = ceil_div(rows, kFir2Rows) * sh.ttiles;
     const size_t kp = (size_t)((Keff + 3) & ~3LL);
@@ -913,7 +926,7 @@ static int check_fir_args(const char *name, float *out, const float *in, const f
 
 extern "C" int slayer_b200_set_fir_packed(int enable)
 {
-    return sb200::g_fir_packed.exchange(enable ? 1 : 0);
+    return sb200::g_fir_packed.exchange(enable < 0 ? 0 : (enable > 3 ? 1 : enable));
 }
 
 extern "C" int slayer_b200_set_fir_skip_zeros(int enable)

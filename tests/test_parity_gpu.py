@@ -78,12 +78,13 @@ def test_shift_unaligned_buffers_take_the_scalar_path():
 
 
 # --------------------------------------------------------------------------- conv / corr
-@pytest.fixture(params=["packed", "scalar"])
+@pytest.fixture(params=["packed", "packed-half-tiles", "packed-full-tiles", "scalar"])
 def fir_variant(request):
     """conv / corr have two kernels that must give the same bits: the packed one (two rows per
-    lane, two-wide FMAs; the default) and the scalar one."""
+    lane, two-wide FMAs), with either of its tile sizes, and the scalar one."""
     from slayerpytorch_b200 import capi
-    before = capi.set_fir_packed(request.param == "packed")
+    mode = {"scalar": 0, "packed": 1, "packed-half-tiles": 2, "packed-full-tiles": 3}[request.param]
+    before = capi.set_fir_packed(mode)
     yield request.param
     capi.set_fir_packed(before)
 
@@ -168,9 +169,10 @@ def test_conv_corr_on_spike_tensors_skip_zeros(density, T, K):
     f = rng.randn(K).astype(np.float32)
     xd, fd = G.dev(x), G.dev(f)
     want_conv, want_corr = co.conv(x, f, 1.0), co.corr(x, f, 1.0)
-    before = capi.set_fir_packed(True)
+    before = capi.set_fir_packed(1)
     try:
-        for skip in (True, False):
+        for mode, skip in ((2, True), (3, True), (1, False)):
+            capi.set_fir_packed(mode)
             capi.set_fir_skip_zeros(skip)
             assert_close_or_equal(G.host(G.c_conv(xd, fd, 1.0)), want_conv)
             assert_close_or_equal(G.host(G.c_conv(xd, fd, 1.0, corr=True)), want_corr)
