@@ -97,6 +97,22 @@ int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const float *w,
                                  uint32_t vDecay, uint32_t refDelay, void *stream);
 
 /*
+ * slayer_b200_loihi_get_spikes followed by a delay of `delay` time steps (0 .. 63) on the spikes,
+ * with the spikes written once, already delayed: delayed[r, t] = s[r, t - delay] (0 for
+ * t < delay); v as above; u may be NULL, in which case the current is not written (callers that
+ * keep only spikes and voltage, as _spike.forward does, src/slayerLoihi.py:257-262).  The same
+ * bits as getSpikes<float>() (src/cuda/spikeLoihiKernels.h:75-96) followed by the scalar
+ * shift<float>() (src/cuda/shiftKernels.h:63-98) that every Loihi layer applies with a delay of
+ * one step (delayShift(spike, 1), exampleLoihi/03_IBMGesture/ibmGestureTrain.py:56-79); 12 instead
+ * of 24 bytes per element.  Needs 16-byte aligned buffers and theta < 2^31, else
+ * SLAYER_B200_EUNSUPPORTED (run the two calls instead).
+ */
+int slayer_b200_loihi_get_spikes_delayed(float *delayed, float *v, float *u, const float *w,
+                                         int64_t rows, int64_t T,
+                                         uint32_t wgtExp, uint32_t theta, uint32_t iDecay,
+                                         uint32_t vDecay, uint32_t refDelay, int64_t delay, void *stream);
+
+/*
  * Surrogate gradient of the spike function, fused into one pass:
  *   out[i] = g[i] * ( scale / tau * exp(-|u[i] - theta| / tau) ),   i < n.
  * `out` may alias `g`.  Replaces the chain of elementwise tensor operations in

@@ -38,6 +38,7 @@ SYMBOLS = {
                                              ctypes.c_double, _i64, _p]),
     "slayer_b200_num_spikes_loss": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_loihi_get_spikes": (_int, [_p, _p, _p, _p, _i64, _i64, _u32, _u32, _u32, _u32, _u32, _p]),
+    "slayer_b200_loihi_get_spikes_delayed": (_int, [_p, _p, _p, _p, _i64, _i64, _u32, _u32, _u32, _u32, _u32, _i64, _p]),
     "slayer_b200_spike_grad": (_int, [_p, _p, _p, _i64, _f, _f, _f, _p]),
     "slayer_b200_srm_get_spikes_delayed": (_int, [_p, _p, _p, _p, _p, _f, _i64, _i64, _i64, _i64, _f, _f, _p]),
     "slayer_b200_spike_grad_shift": (_int, [_p, _p, _p, _p, _f, _i64, _i64, _i64, _f, _f, _f, _f, _p]),

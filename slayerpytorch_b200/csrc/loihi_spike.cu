@@ -182,7 +182,7 @@ struct LoihiRow {
 // Two wide tiles of the same rows and steps to two arrays of the same shape: the row, its skew,
 // the bounds and the offset are worked out once per pass and shared by the two stores; the
 // spike samples of the same tile are expanded from bit masks in the same pass.
-template <bool SKEW>
+template <bool SKEW, bool WRITE_U>
 __device__ __forceinline__ void wide_store_loihi(const float *tile_u, const float *tile_v, const unsigned *masks,
                                                  float *gu, float *gv, float *gs, int64_t row0, int64_t rows,
                                                  int j, int T, int lane, int skew0)
@@ -200,13 +200,13 @@ __device__ __forceinline__ void wide_store_loihi(const float *tile_u, const floa
         const int t = kWide * j - (SKEW ? row_skew(skew0, r, T) : 0) + c16 * 4;
         if (t >= T || t + 4 <= 0) continue;
         const int wd = hoff + tile_word(r, c);
-        const float4 vu = *reinterpret_cast<const float4 *>(tile_u + wd);
+        const float4 vu = WRITE_U ? *reinterpret_cast<const float4 *>(tile_u + wd) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         const float4 vv = *reinterpret_cast<const float4 *>(tile_v + wd);
         const unsigned m = mhalf[r] >> c;
         const float4 vs = make_float4((m & 1u) ? 1.0f : 0.0f, (m & 2u) ? 1.0f : 0.0f, (m & 4u) ? 1.0f : 0.0f, (m & 8u) ? 1.0f : 0.0f);
         const int64_t off = (row0 + r) * (int64_t)T + t;
         if (t >= 0 && t + 4 <= T) {
-            *reinterpret_cast<float4 *>(gu + off) = vu;
+            if (WRITE_U) *reinterpret_cast<float4 *>(gu + off) = vu;
             *reinterpret_cast<float4 *>(gv + off) = vv;
             *reinterpret_cast<float4 *>(gs + off) = vs;
         } else {
@@ -216,7 +216,7 @@ __device__ __forceinline__ void wide_store_loihi(const float *tile_u, const floa
 #pragma unroll
             for (int k = 0; k < 4; ++k)
                 if (t + k >= 0 && t + k < T) {
-                    gu[off + k] = eu[k];
+                    if (WRITE_U) gu[off + k] = eu[k];
                     gv[off + k] = ev[k];
                     gs[off + k] = es[k];
                 }
@@ -233,12 +233,18 @@ __device__ __forceinline__ void wide_store_loihi(const float *tile_u, const floa
 // their way out.  Samples before a row's start are padded with zeros and the sample at t = 0
 // is replaced by zero: with zero input the state stays zero and all outputs are zero, which is
 // what the definition prescribes for t = 0 (0 > theta cannot fire because theta >= 0 here).
+//
+// WRITE_U = false leaves the current out (callers that only keep spikes and voltage: 12 instead
+// of 16 bytes per element).  `delay` (0 .. 63 steps) writes the spikes already delayed,
+// s_out[t] = s[t - delay]: a Loihi layer is always followed by a delay of one step, and the
+// spike bits of a tile only need a 64-bit shift with carry from the previous tile for that, so
+// the separate shift pass (8 bytes per element) disappears.
 // ---------------------------------------------------------------------------------------
-template <bool SKEW>
+template <bool SKEW, bool WRITE_U>
 __global__ void __launch_bounds__(256)
 loihi_get_spikes_wide_kernel(float *s, float *v, float *u, const float *w,
                              int64_t rows, int T, unsigned weightScale, int theta,
-                             unsigned iKeep, unsigned vKeep, int vDecayMark, unsigned refDelay, int depth)
+                             unsigned iKeep, unsigned vKeep, int vDecayMark, unsigned refDelay, int depth, int delay)
 {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31;
@@ -263,6 +269,7 @@ loihi_get_spikes_wide_kernel(float *s, float *v, float *u, const float *w,
     const unsigned dmask = (unsigned)depth - 1u;
     LoihiRow st;
     st.reset();
+    unsigned long long prev_bits = 0ull;      // spike bits of the previous tile of this lane's row
 
     auto prefetch = [&](float *dst) {
         wide_prefetch_skew<SKEW>(dst, w, rb_next * kTile, rows, it_next, T, lane, skew_next, 0.0f);
@@ -280,7 +287,10 @@ loihi_get_spikes_wide_kernel(float *s, float *v, float *u, const float *w,
     for (int it = 0; rb < nblocks; ++q) {
         const int64_t row0 = rb * kTile;
         float *tile = tiles + (q & dmask) * kWideWords;
-        if (it == 0) st.reset();
+        if (it == 0) {
+            st.reset();
+            prev_bits = 0ull;
+        }
         if (rb_next < nblocks) prefetch(tiles + ((q + dmask) & dmask) * kWideWords);
         cp_async_commit();
         if (depth == 2) cp_async_wait<1>();
@@ -307,18 +317,25 @@ loihi_get_spikes_wide_kernel(float *s, float *v, float *u, const float *w,
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                     if (st.step(wv[k], weightScale, theta, iKeep, vKeep, vMarkF, refDelay, uo[k], vo[k])) mh |= 1u << (c4 * 4 + k);
-                *reinterpret_cast<float4 *>(th + tile_chunk(lane, c4)) = make_float4(uo[0], uo[1], uo[2], uo[3]);
+                if (WRITE_U) *reinterpret_cast<float4 *>(th + tile_chunk(lane, c4)) = make_float4(uo[0], uo[1], uo[2], uo[3]);
                 *reinterpret_cast<float4 *>(tv + tile_chunk(lane, c4)) = make_float4(vo[0], vo[1], vo[2], vo[3]);
                 cur = nxt;
             }
             if (h == 0) m[0] = mh;
             else m[1] = mh;
         }
-        masks[lane] = m[0];
-        masks[kTile + lane] = m[1];
+        {
+            // the tile's 64 spike bits, delayed: bits that leave at the top come back in at the
+            // bottom of the next tile
+            const unsigned long long cur_bits = ((unsigned long long)m[1] << 32) | m[0];
+            const unsigned long long out_bits = delay ? (cur_bits << delay) | (prev_bits >> (64 - delay)) : cur_bits;
+            prev_bits = cur_bits;
+            masks[lane] = (unsigned)out_bits;
+            masks[kTile + lane] = (unsigned)(out_bits >> 32);
+        }
         __syncwarp();
 
-        wide_store_loihi<SKEW>(tile, tile_v, masks, u, v, s, row0, rows, it, T, lane, skew);
+        wide_store_loihi<SKEW, WRITE_U>(tile, tile_v, masks, u, v, s, row0, rows, it, T, lane, skew);
         __syncwarp();
         if (++it == ntiles) {
             it = 0;
@@ -356,7 +373,7 @@ static int launch_loihi(const LoihiArgs &a)
     return check_launch("loihi_get_spikes kernel launch");
 }
 
-static int launch_loihi_wide(const LoihiArgs &a)
+static int launch_loihi_wide(const LoihiArgs &a, int delay = 0)
 {
     const int64_t nblocks = ceil_div(a.rows, kTile);
     // prefetch depth 4 when every warp of the launch is resident at once even with the larger
@@ -369,11 +386,12 @@ static int launch_loihi_wide(const LoihiArgs &a)
     const size_t smem = (size_t)warps * warp_bytes;
     // rows that start on 32-byte boundaries need no skew
     const bool skew = (a.T & 7) != 0 || (reinterpret_cast<uintptr_t>(a.w) & 31u) != 0;
-    auto kern = skew ? loihi_get_spikes_wide_kernel<true> : loihi_get_spikes_wide_kernel<false>;
+    auto kern = a.u ? (skew ? loihi_get_spikes_wide_kernel<true, true> : loihi_get_spikes_wide_kernel<false, true>)
+                    : (skew ? loihi_get_spikes_wide_kernel<true, false> : loihi_get_spikes_wide_kernel<false, false>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
     kern<<<(unsigned)grid, warps * 32, smem, a.stream>>>(a.s, a.v, a.u, a.w, a.rows, a.T, a.weightScale, a.theta,
-                                                         a.iKeep, a.vKeep, a.vMark, a.refDelay, depth);
+                                                         a.iKeep, a.vKeep, a.vMark, a.refDelay, depth, delay);
     return check_launch("loihi_get_spikes (wide tile) kernel launch");
 }
 
@@ -406,4 +424,29 @@ extern "C" int slayer_b200_loihi_get_spikes(float *s, float *v, float *u, const 
         case 2: return launch_loihi<2>(a);
         default: return launch_loihi<1>(a);
     }
+}
+
+extern "C" int slayer_b200_loihi_get_spikes_delayed(float *delayed, float *v, float *u, const float *w,
+                                                    int64_t rows, int64_t T,
+                                                    uint32_t wgtExp, uint32_t theta, uint32_t iDecay,
+                                                    uint32_t vDecay, uint32_t refDelay, int64_t delay, void *stream_)
+{
+    using namespace sb200;
+    clear_error();
+    SB200_REQUIRE(rows >= 0 && T >= 0, "loihi_get_spikes_delayed: negative size");
+    SB200_REQUIRE(T < (1LL << 31) - 64, "loihi_get_spikes_delayed: T=%lld too large", (long long)T);
+    SB200_REQUIRE(refDelay >= 1, "loihi_get_spikes_delayed: refDelay must be >= 1");
+    SB200_REQUIRE(wgtExp <= 25, "loihi_get_spikes_delayed: wgtExp=%u out of range", wgtExp);
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    SB200_REQUIRE(delayed && v && w, "loihi_get_spikes_delayed: null pointer");
+    SB200_REQUIRE(delayed != v && delayed != u && v != u && delayed != w && v != w && u != w,
+                  "loihi_get_spikes_delayed: buffers must be distinct");
+    if (delay < 0 || delay > 63 || theta >= 0x80000000u || !all_aligned16({delayed, v, w}) || (u && !aligned16(u))) {
+        set_error("loihi_get_spikes_delayed: needs a delay of 0 .. 63 steps, 16-byte aligned buffers and a threshold "
+                  "below 2^31; otherwise run slayer_b200_loihi_get_spikes and slayer_b200_shift_scalar");
+        return SLAYER_B200_EUNSUPPORTED;
+    }
+    const LoihiArgs a = {delayed, v, u, w, rows, (int)T, 1u << (6 + wgtExp), (int)theta,
+                         4096u - iDecay, 4096u - vDecay, (int)vDecay, refDelay, (cudaStream_t)stream_};
+    return launch_loihi_wide(a, (int)delay);
 }

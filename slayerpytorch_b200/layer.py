@@ -253,6 +253,39 @@ class _LoihiSpikeFunction(torch.autograd.Function):
         return slayerCuda.corr(g, srmKernel, ctx.Ts), None, None, None
 
 
+class _LoihiSpikeDelayFunction(torch.autograd.Function):
+    """Loihi neuron followed by a delay of a whole number of steps, as one autograd node: the
+    forward is one launch that writes the spikes already delayed and skips the current
+    (``slayerLoihiCuda.getSpikesDelayed``), the backward is the fused shift-back + surrogate
+    gradient (``slayerCuda.spikeGradShift``) followed by corr.  Same results as
+    ``_LoihiSpikeFunction`` followed by ``_DelayShiftFunction`` (src/slayerLoihi.py:243-283,
+    src/slayer.py:959-979)."""
+
+    @staticmethod
+    def forward(ctx, weightedSpikes, srmKernel, neuron, Ts, delaySteps):
+        if weightedSpikes.dtype == torch.int32:
+            Ts = 1
+        w = weightedSpikes if Ts == 1 and weightedSpikes.dtype == torch.float32 else (weightedSpikes * Ts).float()
+        delayed, voltage = slayerLoihiCuda.getSpikesDelayed(
+            w.contiguous(), neuron['wgtExp'], neuron['theta'], neuron['iDecay'], neuron['vDecay'], neuron['refDelay'],
+            int(delaySteps))
+        if Ts != 1:
+            delayed = delayed / Ts
+        ctx.save_for_backward(voltage, srmKernel)
+        ctx.theta = float(neuron['theta'])
+        ctx.tau = float(neuron['tauRho'] * neuron['theta'])
+        ctx.scale = float(neuron['scaleRho'])
+        ctx.Ts = float(Ts)
+        ctx.shift_back = torch.tensor([-float(delaySteps) * float(Ts)], device=voltage.device)
+        return delayed
+
+    @staticmethod
+    def backward(ctx, grad):
+        voltage, srmKernel = ctx.saved_tensors
+        g = slayerCuda.spikeGradShift(grad.contiguous(), voltage, ctx.shift_back, ctx.theta, ctx.tau, ctx.scale, ctx.Ts)
+        return slayerCuda.corr(g, srmKernel, ctx.Ts), None, None, None, None
+
+
 # ----------------------------------------------------------------------------- modules
 class _DenseLayer(torch.nn.Conv3d):
     """Fully connected layer over NCHWT tensors: a 1x1x1 3-D convolution, as the reference's
@@ -380,6 +413,13 @@ class loihiLayer(spikeLayer):
 
     def spikeLoihi(self, weightedSpikes):
         return _LoihiSpikeFunction.apply(weightedSpikes, self.srmKernel, self.neuron, self.simulation['Ts'])
+
+    def spikeLoihiDelayed(self, weightedSpikes, delaySteps=1):
+        """``delayShift(spikeLoihi(w), delaySteps * Ts, Ts)`` - a Loihi layer and the delay that
+        always follows it - as one autograd node with a one-launch forward.  ``delaySteps`` is a
+        whole number of time steps.  Not part of the reference's interface."""
+        return _LoihiSpikeDelayFunction.apply(weightedSpikes, self.srmKernel, self.neuron, self.simulation['Ts'],
+                                              int(delaySteps))
 
     def spikeLoihiFull(self, weightedSpikes):
         return _LoihiSpikeFunction.loihi(weightedSpikes, self.neuron, self.simulation['Ts'])

@@ -142,3 +142,12 @@ def c_conv_packed(bits, T, f, value, Ts):
     capi.call("slayer_b200_conv_packed", ptr(out), ptr(bits), ptr(f), out.numel() // T if T else 0, T, f.numel(),
               float(value), float(Ts), stream())
     return out
+
+
+def c_loihi_delayed(w, wgtExp, theta, iDecay, vDecay, refDelay, delay, current=True):
+    d, v = torch.full_like(w, float("nan")), torch.full_like(w, float("nan"))
+    u = torch.full_like(w, float("nan")) if current else None
+    rows, T = rows_T(w)
+    capi.call("slayer_b200_loihi_get_spikes_delayed", ptr(d), ptr(v), ptr(u) if current else None, ptr(w), rows, T,
+              int(wgtExp), int(theta), int(iDecay), int(vDecay), int(refDelay), int(delay), stream())
+    return d, v, u

@@ -342,3 +342,23 @@ def test_num_spikes_loss_fused_kernel_equals_the_tensor_expressions(Ts, region, 
     torch.testing.assert_close(la, lb, rtol=1e-6, atol=0)
     torch.testing.assert_close(ga, gb, rtol=1e-5, atol=1e-5 * gb.abs().max().item())
     assert ga.abs().sum() > 0
+
+
+def test_loihi_spike_delayed_layer_function_equals_the_two_steps():
+    """layer.spikeLoihiDelayed = delayShift(spikeLoihi(w), 1): same forward bits, same gradient."""
+    from slayerpytorch_b200 import layer as L
+    neuron = {"type": "LOIHI", "vThMant": 80, "vDecay": 128, "iDecay": 1024, "refDelay": 1, "wgtExp": 0,
+              "tauRho": 1, "scaleRho": 1}
+    net = L.loihiLayer(dict(neuron), {"Ts": 1.0, "tSample": 1450}).cuda()
+    g = torch.Generator().manual_seed(21)
+    w = (torch.randint(-60, 60, (2, 6, 3, 3, 1450), generator=g) * (torch.rand(2, 6, 3, 3, 1450, generator=g) < 0.3)).float().cuda()
+    gout = torch.randn(2, 6, 3, 3, 1450, generator=g).cuda()
+    for steps in (1, 3):
+        a = w.clone().requires_grad_(True)
+        ya = net.delayShift(net.spikeLoihi(a), float(steps), 1.0)
+        ya.backward(gout)
+        b = w.clone().requires_grad_(True)
+        yb = net.spikeLoihiDelayed(b, steps)
+        yb.backward(gout)
+        assert torch.equal(ya, yb) and ya.sum() > 0
+        assert torch.equal(a.grad, b.grad)

@@ -383,6 +383,46 @@ def test_loihi_threshold_at_and_above_2_to_31(theta):
         assert (want[0].sum() > 0) == (theta >= 0x80000000)
 
 
+@pytest.mark.parametrize("T", [1, 2, 33, 64, 65, 200, 1450])
+@pytest.mark.parametrize("delay", [0, 1, 2, 31, 32, 63])
+def test_loihi_get_spikes_delayed_equals_get_spikes_then_shift(T, delay):
+    """Spikes written once, already delayed, with and without the current: the bits of getSpikes
+    followed by a scalar shift, and of the oracle."""
+    rng = np.random.RandomState(T * 64 + delay)
+    params = (0, 5120, 1024, 128, 2)
+    w = (np.round((rng.rand(3, 13, 1, 2, T) - 0.5) * 90) * (rng.rand(3, 13, 1, 2, T) < 0.3)).astype(np.float32)
+    wd = G.dev(w)
+    s_o, v_o, u_o = co.loihi_get_spikes(w, *params)
+    want_d = co.shift(s_o, float(delay), 1.0)
+    for current in (True, False):
+        d, v, u = G.c_loihi_delayed(wd, *params, delay, current=current)
+        np.testing.assert_array_equal(G.host(d), want_d)
+        np.testing.assert_array_equal(G.host(v), v_o)
+        if current:
+            np.testing.assert_array_equal(G.host(u), u_o)
+    s, _, _ = G.c_loihi(wd, *params)
+    np.testing.assert_array_equal(G.host(d), G.host(G.c_shift_scalar(s, delay, 1.0)))
+    assert T < 30 or s_o.sum() > 0
+
+
+def test_loihi_get_spikes_delayed_sizes_outside_the_fused_path():
+    import slayerpytorch_b200
+    from slayerpytorch_b200.capi import SlayerB200Error
+    _, lc = slayerpytorch_b200.load_ops()
+    rng = np.random.RandomState(4)
+    w = (np.round((rng.rand(40, 300) - 0.5) * 90) * (rng.rand(40, 300) < 0.3)).astype(np.float32)
+    wd = G.dev(w).view(1, 40, 1, 1, 300)
+    with pytest.raises(SlayerB200Error):
+        G.c_loihi_delayed(wd, 0, 5120, 1024, 128, 1, 64)
+    s_o, v_o, u_o = co.loihi_get_spikes(w, 0, 5120, 1024, 128, 1)
+    for delay in (64, 100, 400):                       # the operator runs getSpikes + shift
+        d, v, u = lc.getSpikesDelayed(wd, 0, 5120, 1024, 128, 1, delay, True)
+        np.testing.assert_array_equal(G.host(d).reshape(40, 300), co.shift(s_o, float(delay), 1.0))
+        np.testing.assert_array_equal(G.host(v).reshape(40, 300), v_o)
+        np.testing.assert_array_equal(G.host(u).reshape(40, 300), u_o)
+    assert len(lc.getSpikesDelayed(wd, 0, 5120, 1024, 128, 1, 1)) == 2
+
+
 def test_loihi_reference_numpy_model_fixture(golden_dir):
     g = np.load(golden_dir + "/ref_python.npz")
     for k in range(int(g["nrn_count"])):
