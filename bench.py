@@ -62,11 +62,11 @@ FMA_LANES = 148 * 128 * 2            # fp32 flops per clock of the whole GPU (14
 
 # algorithmic bytes per neuron-timestep of each operator (reads + writes of fp32 tensors)
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12, "spikeGradShift": 12,
-             "getSpikesDelayed": 12, "delayGrad": 8, "loihi": 16, "spikeGradCorr": 12}
+             "getSpikesDelayed": 12, "delayGrad": 8, "loihi": 16, "loihiDelayed": 12, "spikeGradCorr": 12}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count) on launches too large for L2; see the summaries under profiles/.
 NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
-                           "spike_grad_shift_rows_kernel": 11.6, "loihi_get_spikes_kernel": 15.8,
+                           "spike_grad_shift_rows_kernel": 11.6, "loihi_get_spikes_wide_kernel": None,
                            "delay_grad_kernel": 8.0}
 
 
@@ -78,7 +78,8 @@ def kernel_of(op, T):
             "getSpikesDelayed": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "shift": "shift_vec4_kernel" if quad else "shift_flat4_kernel",
             "spikeGrad": "spike_grad_vec4_kernel", "spikeGradShift": "spike_grad_shift_rows_kernel",
-            "delayGrad": "delay_grad_kernel", "loihi": "loihi_get_spikes_kernel"}[op]
+            "delayGrad": "delay_grad_kernel", "loihi": "loihi_get_spikes_wide_kernel",
+            "loihiDelayed": "loihi_get_spikes_wide_kernel"}[op]
 
 
 def measured_peak_gbs():
@@ -153,6 +154,9 @@ class OurOps:
 
     def loihi(self, w, wgtExp, theta, iDecay, vDecay, refDelay):
         return tuple(self.lc.getSpikes(w, wgtExp, theta, iDecay, vDecay, refDelay))
+
+    def loihiDelayed(self, w, wgtExp, theta, iDecay, vDecay, refDelay, delay):
+        return tuple(self.lc.getSpikesDelayed(w, wgtExp, theta, iDecay, vDecay, refDelay, delay))
 
 
 class RefCudaOps:
@@ -288,14 +292,18 @@ class Workload:
                     outs.append(run("corr", i, L["rows_in"], lambda: ops.corr(L["g_p"], srm, Ts)))
             else:
                 k = self.kernels[0]
-                s, v, u = run("loihi", i, rows, lambda: ops.loihi(L["w"], n["wgtExp"], n["theta"], n["iDecay"],
-                                                                  n["vDecay"], n["refDelay"]))
-                d = run("shift", i, rows, lambda: ops.shift(s, 1.0, Ts))
                 if ops.fused:
+                    # the spikes are written once, already delayed by one step, and the current (which
+                    # the layer does not keep) is not written; shift back + surrogate gradient in one pass
+                    d, v = run("loihiDelayed", i, rows, lambda: ops.loihiDelayed(L["w"], n["wgtExp"], n["theta"], n["iDecay"],
+                                                                                 n["vDecay"], n["refDelay"], 1))
                     gu = run("spikeGradShift", i, rows,
                              lambda: ops.spikeGradShift(L["g"], v, L["minus_one"], theta, tau, scale, Ts))
-                    outs += [s, v, u, d, gu]
+                    outs += [v, d, gu]
                 else:
+                    s, v, u = run("loihi", i, rows, lambda: ops.loihi(L["w"], n["wgtExp"], n["theta"], n["iDecay"],
+                                                                      n["vDecay"], n["refDelay"]))
+                    d = run("shift", i, rows, lambda: ops.shift(s, 1.0, Ts))
                     b0 = run("shift", i, rows, lambda: ops.shift(L["g"], -1.0, Ts))
                     gu = run("spikeGrad", i, rows, lambda: ops.spikeGrad(b0, v, theta, tau, scale))
                     outs += [s, v, u, d, b0, gu]
@@ -310,8 +318,9 @@ class Workload:
         dry = Dry()
         dry.fused = fused
         for name in ("conv", "corr", "getSpikes", "shift", "spikeGrad", "delayGrad", "getSpikesDelayed",
-                     "spikeGradShift", "loihi"):
-            setattr(dry, name, (lambda *a, **k: (None, None, None)) if name == "loihi" else (lambda *a, **k: None))
+                     "spikeGradShift", "loihi", "loihiDelayed"):
+            setattr(dry, name, (lambda *a, **k: (None, None, None)) if name == "loihi" else
+                    ((lambda *a, **k: (None, None)) if name == "loihiDelayed" else (lambda *a, **k: None)))
 
         def run(op, layer, rows, fn):
             taps = 0
@@ -809,8 +818,9 @@ def time_ours(args, rank, world, device):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": wl.name,
                    "fusion": ("none: the reference's sequence of launches" if args.unfused else
-                              "getSpikes+delay as one launch (getSpikesDelayed) and shift back + surrogate gradient as one "
-                              "launch (spikeGradShift) wherever a delay follows the spikes; same results"),
+                              "getSpikes+delay as one launch (SRM: getSpikesDelayed; Loihi: getSpikesDelayed without the "
+                              "current) and shift back + surrogate gradient as one launch (spikeGradShift) wherever a delay "
+                              "follows the spikes; same results"),
                    "neuron_timesteps_per_step_per_gpu": wl.units, "batch_per_gpu": wl.batch,
                    "l2": "flushed between steps (256 MiB write); in-place potentials restored between steps, untimed",
                    "spike_rates": [round(r, 4) for r in wl.rates],
@@ -905,7 +915,7 @@ def time_e2e(args, wl, ops, device, world, flush, L, HostPipeline, chunk_bounds)
                     results.append(lambda s_in=s_in: s_in.grad)
             else:
                 w = by[(i, "w")].detach().requires_grad_(True)
-                y = net.delayShift(net.spikeLoihi(w), 1)
+                y = net.delayShift(net.spikeLoihi(w), 1) if args.unfused else net.spikeLoihiDelayed(w, 1)
                 heads.append(y)
                 grads.append(by[(i, "g")])
                 results += [y.detach, lambda w=w: w.grad]
