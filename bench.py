@@ -795,7 +795,10 @@ def time_ours(args, rank, world, device):
     clocks = sampler.stop()
 
     # ---- end to end through the public layer API with host buffers
-    e2e = time_e2e(args, wl, ops, device, world, flush, L, HostPipeline, chunk_bounds)
+    if args.no_e2e:
+        e2e = {"ms_total": float("nan"), "serial_ms_total": 0.0, "steps": 1, "h2d": 0, "d2h": 0, "how": "skipped (--no-e2e)"}
+    else:
+        e2e = time_e2e(args, wl, ops, device, world, flush, L, HostPipeline, chunk_bounds)
 
     units_all = torch.tensor([float(wl.units)], dtype=torch.float64, device=device)
     t = torch.tensor([total_ms, eager_ms, e2e["ms_total"], e2e["serial_ms_total"], ar_ms or 0.0], dtype=torch.float64, device=device)
@@ -849,7 +852,7 @@ def time_ours(args, rank, world, device):
     del wl
     torch.cuda.empty_cache()
     if world == 1:
-        out["cpu_baseline"] = cpu_baseline_value(args.config, reps=3)
+        out["cpu_baseline"] = cpu_baseline_value(args.config, reps=3) if not args.no_e2e else None
         if not args.no_all_configs:
             out["configs"] = all_configs(args, ops, device, flush, peak, peak_kind, out)
         out["loss"] = loss_leg(ops, device)
@@ -866,11 +869,20 @@ def time_e2e(args, wl, ops, device, world, flush, L, HostPipeline, chunk_bounds)
     else:
         net = L.spikeLayer(dict(n), {"Ts": wl.Ts, "tSample": wl.T}).to(device)
     in_keys = {"psp_spike": ("a", "g"), "spike_w": ("s_in", "u0", "g_s", "g_p"), "loihi": ("w", "g")}
+    # Layers of the form spike(W(psp(.))) through the fused node spikePsp = psp of the next layer
+    # applied to the spikes of this one: the spikes stay on the device as bits, and neither they
+    # nor the gradient that reaches them cross PCIe; what crosses per layer is its potential, the
+    # next layer's psp output and that output's gradient.
+    chained = wl.layers[0]["kind"] == "spike_w" and not args.unfused
+    last = len(wl.layers) - 1
     names = []
     for i, Lr in enumerate(wl.layers):
         for k in in_keys[Lr["kind"]]:
-            if Lr.get(k) is not None:
-                names.append((i, k))
+            if Lr.get(k) is None:
+                continue
+            if chained and ((k == "s_in" and i > 0) or (k == "g_s" and i < last)):
+                continue
+            names.append((i, k))
     dev_in = [wl.layers[i][k] for i, k in names]
     delays = {}
     for i, Lr in enumerate(wl.layers):
@@ -900,6 +912,21 @@ def time_e2e(args, wl, ops, device, world, flush, L, HostPipeline, chunk_bounds)
                 heads.append(y)
                 grads.append(by[(i, "g")])
                 results += [y.detach, lambda a=a: a.grad]
+            elif Lr["kind"] == "spike_w" and chained:
+                if i == 0:
+                    results.append(net.psp(by[(0, "s_in")]).detach)            # psp of the network input
+                u = by[(i, "u0")].detach().requires_grad_(True)
+                if i < last:
+                    p_next, packed = net.spikePsp(u)
+                    heads.append(p_next)
+                    grads.append(by[(i + 1, "g_p")])
+                    results += [p_next.detach, (lambda packed=packed: packed.bits)]
+                else:
+                    y = net.spike(u)
+                    heads.append(y)
+                    grads.append(by[(i, "g_s")])
+                    results.append(y.detach)
+                results.append(lambda u=u: u.grad)
             elif Lr["kind"] == "spike_w":
                 back = (i, "g_p") in by
                 s_in = by[(i, "s_in")].detach().requires_grad_(back)
@@ -973,8 +1000,9 @@ def time_e2e(args, wl, ops, device, world, flush, L, HostPipeline, chunk_bounds)
         for a, b in zip(want, h_out):
             if not torch.equal(a.view(torch.int32), b.view(torch.int32)):
                 raise RuntimeError("pipelined end-to-end result differs from the single-call result")
-    how = "HostPipeline: %d batch chunks, copies and kernels overlapped on three streams%s; %d host tensors in, %d out" % (
-        len(chunk_bounds(batch, chunks)), ", each chunk's step one CUDA-graph launch" if capture else "", len(h_in), len(h_out))
+    how = "HostPipeline: %d batch chunks, copies and kernels overlapped on three streams%s; %d host tensors in, %d out%s" % (
+        len(chunk_bounds(batch, chunks)), ", each chunk's step one CUDA-graph launch" if capture else "", len(h_in), len(h_out),
+        "; spike -> psp of the next layer as one node (spikePsp): spikes cross as bits, their gradients not at all" if chained else "")
     del pipe, h_in, h_out
     return {"ms_total": total, "serial_ms_total": serial_total, "steps": steps, "h2d": h2d, "d2h": d2h, "how": how}
 
@@ -1208,6 +1236,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10, help="at most this many end-to-end steps are timed")
     ap.add_argument("--e2e-capture", default="chunk", choices=["pipeline", "chunk"],
                     help="CUDA-graph granularity of the end-to-end pipeline (small workloads only)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) measurement, e.g. under a profiler")
     ap.add_argument("--no-all-configs", action="store_true", help="skip the resident-input numbers of the other configurations")
     ap.add_argument("--no-reference-cuda", action="store_true", help="reference arm: skip the reference's CUDA kernels")
     args = ap.parse_args()

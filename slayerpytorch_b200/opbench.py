@@ -3,7 +3,7 @@
     python -m slayerpytorch_b200.opbench --op getSpikes --rows 262144 --T 300 --iters 5
 
 Operators: conv, corr, convPacked, getSpikes, getSpikesPacked, getSpikesDelayed, shift, shiftScalar,
-spikeGrad, spikeGradShift, delayGrad, loihi.  Prints one JSON line with
+spikeGrad, spikeGradShift, delayGrad, loihi, loihiDelayed.  Prints one JSON line with
 the average launch time, algorithmic GB/s (8 bytes per element for conv/corr/shift, 12 for
 getSpikes/spikeGrad, 16 for loihi) and elements per second.  Small enough to run under a
 profiler: every iteration is exactly one kernel launch of the operator (getSpikes works in
@@ -20,7 +20,7 @@ from slayerpytorch_b200.layer import alpha_kernel, loihi_psp_kernel
 
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "spikeGradShift": 12, "delayGrad": 8,
              "getSpikesDelayed": 12, "getSpikesPacked": 8.125, "convPacked": 4.125,
-             "loihi": 16}
+             "loihi": 16, "loihiDelayed": 12}
 
 
 def main(argv=None):
@@ -108,7 +108,10 @@ def main(argv=None):
     else:
         w = (torch.randint(-128, 128, shape, device=dev, generator=gen)
              * (torch.rand(shape, device=dev, generator=gen) < 0.05)).float()
-        fn = lambda: lc.getSpikes(w, 0, 5120, 1024, 128, 1)
+        if args.op == "loihi":
+            fn = lambda: lc.getSpikes(w, 0, 5120, 1024, 128, 1)
+        else:           # spikes written already delayed by one step, current not written
+            fn = lambda: lc.getSpikesDelayed(w, 0, 5120, 1024, 128, 1, 1)
 
     times = []
     out = None
@@ -126,7 +129,7 @@ def main(argv=None):
         extra["spike_rate"] = float(out.mean())
     if args.op in ("conv", "corr", "convPacked"):
         extra["input_density"] = float((a != 0).float().mean())
-    if args.op == "loihi":
+    if args.op in ("loihi", "loihiDelayed"):
         extra["spike_rate"] = float(out[0].mean())
     ms = sum(times) / len(times)
     print(json.dumps({"op": args.op, "rows": batch * neurons, "T": args.T, "elements": el,
