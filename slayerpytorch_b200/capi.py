@@ -47,6 +47,7 @@ SYMBOLS = {
     "slayer_b200_set_tma": (_int, [_int]),
     "slayer_b200_set_fir_packed": (_int, [_int]),
     "slayer_b200_set_fir_skip_zeros": (_int, [_int]),
+    "slayer_b200_set_fir_flow": (_int, [_int]),
 }
 
 _lib = None
@@ -96,6 +97,12 @@ def set_fir_packed(mode):
     launch), 2 = packed with half-size tiles (two CTAs per SM), 3 = packed with full-size tiles.
     Returns the previous setting."""
     return int(load().slayer_b200_set_fir_packed(int(mode)))
+
+
+def set_fir_flow(mode):
+    """Form of the scalar conv / corr kernel: 1 = no per-tile barrier (default), 2 = the same with
+    more registers, 0 = one barrier per tile.  Returns the previous setting."""
+    return int(load().slayer_b200_set_fir_flow(int(mode)))
 
 
 def set_fir_skip_zeros(enable):

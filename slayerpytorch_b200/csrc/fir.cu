@@ -6,10 +6,11 @@
 // output loop, so results are reproducible bit for bit whatever the tiling.  Samples outside
 // the row enter the chain as +0, which leaves the accumulator unchanged for finite taps.
 //
-// Two kernels compute the same bits.  fir_kernel, described next, is the scalar form and the
-// default.  fir2_kernel (further down) packs two rows per lane into two-wide FMAs, skips the
-// zeros of spike tensors and can read bit-packed spike tensors; slayer_b200_set_fir_packed(1)
-// selects it for conv / corr, and slayer_b200_conv_packed always runs it.
+// Three kernels compute the same bits.  fir_kernel, described next, is the scalar form;
+// fir_flow_kernel (further down, the default) is the same arithmetic without a CTA-wide barrier
+// per tile.  fir2_kernel packs two rows per lane into two-wide FMAs, skips the zeros of spike
+// tensors and can read bit-packed spike tensors; slayer_b200_set_fir_packed(1) selects it for
+// conv / corr, and slayer_b200_conv_packed always runs it.
 //
 // Cost: 8 algorithmic bytes and 2K flops per element.  For K above ~47 taps the fp32 FMA
 // pipes, not HBM, bound the kernel, so the design goal is to keep those pipes fed:
@@ -30,6 +31,7 @@
 
 #include "common.cuh"
 #include "tile.cuh"
+#include "tma.cuh"
 
 namespace sb200 {
 
@@ -721,6 +723,218 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
     cp_async_wait<0>();
 }
 
+
+// ---------------------------------------------------------------------------------------
+// The scalar kernel without a CTA-wide barrier per tile ("flow" form, the default).
+//
+// fir_kernel above synchronises its warps at every tile; with 19 segments over 8 warps three
+// warps carry 3 segments and five carry 2, so about a fifth of the warp-time of a tile is spent
+// waiting at the barrier (barrier stalls are the largest stall reason in its profile).  Here
+// the 16-sample segments of all tiles of a CTA form one sequence that is dealt out to the warps
+// round robin, across tile boundaries, so every warp gets the same number of segments in the
+// long run, and the two hand-overs of a double-buffered tile are split-phase barriers in shared
+// memory (mbarrier) that nobody has to reach at the same time:
+//   landed[b]  every thread attaches its cp.async copies of a tile to it
+//              (cp.async.mbarrier.arrive.noinc); a warp waits for it before its first segment
+//              of that tile;
+//   free[b]    a warp arrives when it has finished its segments of the tile in buffer b; a warp
+//              waits for it before it copies the tile after next into that buffer, which it
+//              does after its first segment of the tile in between - so a fast warp always has
+//              a segment to work on while the slow ones finish.
+// Arithmetic, tile layout and results are those of fir_kernel.  Every wait is bounded: a warp
+// that gives up records kStatusFirWaitTimeout in the device status word and leaves.
+// ---------------------------------------------------------------------------------------
+constexpr int kStatusFirWaitTimeout = 0x5102;
+constexpr int kFirPollLimit = 1 << 24;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// the barrier's pending count was initialised to include this arrival, which happens when the
+// cp.async copies this thread has issued so far have completed
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// MINB = 2 caps the registers at 64 per thread (two CTAs of up to 16 warps per SM); MINB = 1 lets
+// the compiler take about 110, which two CTAs of 8 warps still fit.
+template <int DIR, int V, int MINB>
+__global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
+fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
+                int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int Tt = sh.nseg * kFirSeg;
+    const int WX = Tt + sh.halo;
+    const int KP = ((K + 3) & ~3) + 4;       // taps, zero padded; one spare quad for the look-ahead load
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);      // landed[0], landed[1], free[0], free[1]
+    float *fs = smem + 8;
+    float *xbuf = fs + KP;                   // 2 x [kFirRows x SX]
+    const int tile_words = kFirRows * sh.SX;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+
+    for (int i = threadIdx.x; i < KP; i += blockDim.x) fs[i] = i < K ? filt[i] : 0.0f;
+    if (threadIdx.x == 0) {
+        mbar_init(bars + 0, blockDim.x);
+        mbar_init(bars + 1, blockDim.x);
+        mbar_init(bars + 2, nwarps);
+        mbar_init(bars + 3, nwarps);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const unsigned xbuf_saddr = (unsigned)__cvta_generic_to_shared(xbuf);
+    auto fill = [&](int buf, int64_t tile) {
+        float *xs = xbuf + buf * tile_words;
+        const int64_t rb = tile / sh.ttiles;
+        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        const int64_t row0 = rb * kFirRows;
+        const int64_t nrow = rows - row0;
+        const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
+        if constexpr (V == 4) {
+            constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
+            int goff[kChunks], nbytes[kChunks];          // source offset in the row; 16, 0 (zero fill) or -1 (no chunk)
+#pragma unroll
+            for (int k = 0; k < kChunks; ++k) {
+                const int pcol = lane * 4 + 128 * k;
+                const int gt = g0 + pcol;
+                const bool ok = gt >= 0 && gt < T;
+                goff[k] = ok ? gt : 0;
+                nbytes[k] = pcol < WX ? (ok ? 16 : 0) : -1;
+            }
+            for (int r = warp; r < kFirRows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+                const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + r * sh.SX + lane * 4);
+#pragma unroll
+                for (int k = 0; k < kChunks; ++k) {
+                    if (nbytes[k] < 0) continue;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
+                                 ::"r"(dst + 512u * k), "l"(src + goff[k]), "r"(row_ok ? nbytes[k] : 0) : "memory");
+                }
+            }
+        } else {
+            for (int r = warp; r < kFirRows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const float *src = in + (row0 + (row_ok ? r : 0)) * (int64_t)T;
+                float *dst = xs + r * sh.SX;
+                for (int pcol = lane * V; pcol < WX; pcol += 32 * V) {
+                    const int gt = g0 + pcol;
+                    const bool ok = row_ok && gt >= 0 && gt < T;
+                    cp_async<4 * V>(dst + pcol, ok ? src + gt : in, ok);
+                }
+            }
+        }
+        cp_async_arrive_noinc(bars + buf);
+    };
+
+    const int groups = K >> 2;          // full groups of 4 taps
+    const int tail = K & 3;
+    constexpr unsigned step = DIR < 0 ? 0u - 16u : 16u;   // bytes the window moves per group (mod 2^32)
+    const unsigned fs_addr = (unsigned)__cvta_generic_to_shared(fs);
+
+    // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int64_t first = blockIdx.x;
+    const int n = first < ntiles ? (int)((ntiles - first + gridDim.x - 1) / gridDim.x) : 0;
+    if (n > 0) fill(0, first);
+    if (n > 1) fill(1, first + gridDim.x);
+    bool gave_up = false;
+    int unit0 = warp;                   // this warp's next segment in the CTA-wide sequence, minus it * nseg
+    for (int it = 0; it < n && !gave_up; ++it) {
+        const int b = it & 1;
+        const int64_t tile = first + (int64_t)it * gridDim.x;
+        if (__any_sync(0xffffffffu, !mbar_wait_bounded(bars + b, (unsigned)(it >> 1) & 1u, kFirPollLimit))) {
+            gave_up = true;
+            break;
+        }
+        const int64_t rb = tile / sh.ttiles;
+        const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+        const int64_t row = rb * kFirRows + lane;
+        // byte address of tile position 0 of this lane's row
+        const unsigned xrow = xbuf_saddr + 4u * (unsigned)(b * tile_words + lane * sh.SX + (DIR < 0 ? sh.halo : 0));
+
+        // the tile after this one goes into the other buffer once every warp is done with the tile
+        // that is in it now; this warp sees to its rows after its first segment of this tile
+        bool next_pending = it >= 1 && it + 1 < n;
+        auto fill_next = [&]() {
+            if (__any_sync(0xffffffffu, !mbar_wait_bounded(bars + 2 + (b ^ 1), (unsigned)((it - 1) >> 1) & 1u, kFirPollLimit))) {
+                gave_up = true;
+                return;
+            }
+            fill(b ^ 1, tile + gridDim.x);
+        };
+
+        int seg = unit0;
+        for (; seg < sh.nseg && !gave_up; seg += nwarps) {
+            const int tb = seg * kFirSeg;
+            if (t0 + tb < T) {          // else: whole segment beyond the row end (warp-uniform)
+                float acc[kFirSeg];
+#pragma unroll
+                for (int m = 0; m < kFirSeg; ++m) acc[m] = 0.0f;
+
+                // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
+                float w[kFirRing];
+                const unsigned x0 = xrow + 4u * (unsigned)tb - (DIR < 0 ? 16u : 0u);
+#pragma unroll
+                for (int q = 0; q < kFirWin / 4; ++q) put4(w, 4 * q, ld4(x0 + 16 * q));
+                unsigned xp = DIR < 0 ? x0 - 16 : x0 + 4 * kFirWin;    // next sample quad to fetch
+                unsigned fp = fs_addr;
+                float4 f[2];
+                f[0] = ld4(fp);
+                int g = 0;
+                for (; g + kFirPhases <= groups; g += kFirPhases) {
+                    fir_step<DIR, 0>(acc, w, f, fp + 16, xp);
+                    fir_step<DIR, 1>(acc, w, f, fp + 32, xp + step);
+                    fir_step<DIR, 2>(acc, w, f, fp + 48, xp + 2 * step);
+                    fir_step<DIR, 3>(acc, w, f, fp + 64, xp + 3 * step);
+                    fir_step<DIR, 4>(acc, w, f, fp + 80, xp + 4 * step);
+                    fir_step<DIR, 5>(acc, w, f, fp + 96, xp + 5 * step);
+                    xp += kFirPhases * step;
+                    fp += 16 * kFirPhases;
+                }
+                fir_rest<DIR, 0>(acc, w, f, fp + 16, xp, groups - g, tail);
+
+                if (row < rows) {
+                    float *dst = out + row * (int64_t)T + t0 + tb;
+                    const int left = T - (t0 + tb);          // > 0, multiple of V
+                    if (V == 4) {
+#pragma unroll
+                        for (int q = 0; q < kFirSeg / 4; ++q)
+                            if (4 * q < left)
+                                *reinterpret_cast<float4 *>(dst + 4 * q) = make_float4(
+                                    acc[4 * q] * Ts, acc[4 * q + 1] * Ts, acc[4 * q + 2] * Ts, acc[4 * q + 3] * Ts);
+                    } else if (V == 2) {
+#pragma unroll
+                        for (int q = 0; q < kFirSeg / 2; ++q)
+                            if (2 * q < left)
+                                *reinterpret_cast<float2 *>(dst + 2 * q) = make_float2(acc[2 * q] * Ts, acc[2 * q + 1] * Ts);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < kFirSeg; ++q)
+                            if (q < left) dst[q] = acc[q] * Ts;
+                    }
+                }
+            }
+            if (next_pending) {
+                next_pending = false;
+                fill_next();
+            }
+        }
+        if (next_pending && !gave_up) fill_next();      // this warp had no segment in this tile
+        unit0 = seg - sh.nseg;                          // position of its next segment in the next tile
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + 2 + b);       // done with this tile's buffer
+    }
+    if (gave_up && lane == 0) atomicExch(status, kStatusFirWaitTimeout);
+    cp_async_wait<0>();
+}
+
 // Thread-per-output restatement for filters too long for the shared-memory tile.
 template <int DIR>
 __global__ void __launch_bounds__(256)
@@ -832,6 +1046,7 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh, int max
 }
 
 static std::atomic<int> g_fir_packed{0};
+static std::atomic<int> g_fir_flow{1};
 static std::atomic<int> g_fir_skip_zeros{1};
 
 template <int DIR, bool PK = false>
@@ -898,16 +1113,26 @@ static int launch_fir(float *out, const float *in, const float *filt,
         fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts);
         return check_launch("fir (long filter) kernel launch");
     }
-    const size_t smem = sizeof(float) * ((size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
+    const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
     const int vw = tile_vec_width(T, {out, in});
-    auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
-    int rc = reserve_dynamic_smem((const void *)kern, smem);
-    if (rc) return rc;
     int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
     if (ctas_per_sm > 8) ctas_per_sm = 8;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     int64_t grid = ctas_per_sm * (int64_t)sm_count();
     if (grid > ntiles) grid = ntiles;
+    int *status = g_fir_flow.load() != 0 ? device_status_word() : nullptr;
+    if (status) {
+        const bool roomy = g_fir_flow.load() == 2 && sh.nwarps <= 8;
+        auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1> : fir_flow_kernel<DIR, 1, 1>))
+                          : (vw == 4 ? fir_flow_kernel<DIR, 4, 2> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2> : fir_flow_kernel<DIR, 1, 2>));
+        int rc = reserve_dynamic_smem((const void *)kern, smem);
+        if (rc) return rc;
+        kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status);
+        return check_launch("fir (flow) kernel launch");
+    }
+    auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
+    int rc = reserve_dynamic_smem((const void *)kern, smem);
+    if (rc) return rc;
     kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles);
     return check_launch("fir kernel launch");
 }
@@ -927,6 +1152,11 @@ static int check_fir_args(const char *name, float *out, const float *in, const f
 extern "C" int slayer_b200_set_fir_packed(int enable)
 {
     return sb200::g_fir_packed.exchange(enable < 0 ? 0 : (enable > 3 ? 1 : enable));
+}
+
+extern "C" int slayer_b200_set_fir_flow(int mode)
+{
+    return sb200::g_fir_flow.exchange(mode < 0 || mode > 2 ? 1 : mode);
 }
 
 extern "C" int slayer_b200_set_fir_skip_zeros(int enable)

@@ -35,6 +35,8 @@ def main(argv=None):
     ap.add_argument("--neurons", type=int, default=512, help="rows per batch sample (length of the shift table)")
     ap.add_argument("--packed-fir", type=int, default=None, metavar="MODE",
                     help="conv/corr: kernel selection as slayer_b200_set_fir_packed takes it (0 scalar, 1 packed, 2 / 3 tile size)")
+    ap.add_argument("--fir-flow", type=int, default=None, metavar="MODE",
+                    help="conv/corr: form of the scalar kernel as slayer_b200_set_fir_flow takes it (0, 1, 2)")
     ap.add_argument("--no-skip-zeros", action="store_true", help="conv/corr: packed kernel without its zero-skipping path")
     ap.add_argument("--spikes", action="store_true", help="conv/corr: the input is a 0/1 spike tensor of the given density")
     args = ap.parse_args(argv)
@@ -43,6 +45,9 @@ def main(argv=None):
     if args.packed_fir is not None:
         from slayerpytorch_b200 import capi
         capi.set_fir_packed(args.packed_fir)
+    if args.fir_flow is not None:
+        from slayerpytorch_b200 import capi
+        capi.set_fir_flow(args.fir_flow)
     if args.no_skip_zeros:
         from slayerpytorch_b200 import capi
         capi.set_fir_skip_zeros(False)

@@ -78,15 +78,20 @@ def test_shift_unaligned_buffers_take_the_scalar_path():
 
 
 # --------------------------------------------------------------------------- conv / corr
-@pytest.fixture(params=["packed", "packed-half-tiles", "packed-full-tiles", "scalar"])
+@pytest.fixture(params=["scalar", "scalar-roomy", "scalar-tile-barrier", "packed", "packed-half-tiles", "packed-full-tiles"])
 def fir_variant(request):
-    """conv / corr have two kernels that must give the same bits: the packed one (two rows per
-    lane, two-wide FMAs), with either of its tile sizes, and the scalar one."""
+    """conv / corr have several kernels that must give the same bits: the scalar one in its three
+    forms (segments dealt out across tiles with split-phase barriers - the default -, the same
+    with more registers, one CTA-wide barrier per tile) and the packed one (two rows per lane,
+    two-wide FMAs) with either of its tile sizes."""
     from slayerpytorch_b200 import capi
-    mode = {"scalar": 0, "packed": 1, "packed-half-tiles": 2, "packed-full-tiles": 3}[request.param]
-    before = capi.set_fir_packed(mode)
+    packed, flow = {"scalar": (0, 1), "scalar-roomy": (0, 2), "scalar-tile-barrier": (0, 0), "packed": (1, 1),
+                    "packed-half-tiles": (2, 1), "packed-full-tiles": (3, 1)}[request.param]
+    before = capi.set_fir_packed(packed), capi.set_fir_flow(flow)
     yield request.param
-    capi.set_fir_packed(before)
+    capi.set_fir_packed(before[0])
+    capi.set_fir_flow(before[1])
+    assert capi.device_status() == 0
 
 
 @pytest.mark.parametrize("T", [1, 5, 64, 300, 301, 500, 1450, 2000])
