@@ -315,12 +315,12 @@ int slayer_b200_set_tma(int enable);
 int slayer_b200_set_fir_packed(int enable);
 
 /*
- * Select the form of the scalar conv / corr kernel; returns the previous setting.  1 (the
- * default): warps take the 16-sample segments of a CTA's tiles round robin across tile
- * boundaries and hand tiles over through split-phase shared-memory barriers (bounded waits; a
- * wait that runs out records 0x5102 in the device status word); 2: the same with a larger
- * register budget; 0: one CTA-wide barrier per tile.  All compute the same bits.  It has no
- * counterpart in the reference.
+ * Select the form of the scalar conv / corr kernel; returns the previous setting.  1: warps
+ * take the 16-sample segments of a CTA's tiles round robin across tile boundaries and hand tiles
+ * over through split-phase shared-memory barriers (bounded waits; a wait that runs out records
+ * 0x5102 in the device status word); 2 (the default): the same with a larger register budget
+ * where two CTAs per SM still fit; 0: one CTA-wide barrier per tile.  All compute the same bits.
+ * It has no counterpart in the reference.
  */
 int slayer_b200_set_fir_flow(int mode);
 

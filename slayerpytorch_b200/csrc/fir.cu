@@ -745,7 +745,7 @@ fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *
 // that gives up records kStatusFirWaitTimeout in the device status word and leaves.
 // ---------------------------------------------------------------------------------------
 constexpr int kStatusFirWaitTimeout = 0x5102;
-constexpr int kFirPollLimit = 1 << 24;
+constexpr int kFirPollLimit = 1 << 22;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 {
@@ -761,6 +761,19 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar)
 
 // MINB = 2 caps the registers at 64 per thread (two CTAs of up to 16 warps per SM); MINB = 1 lets
 // the compiler take about 110, which two CTAs of 8 warps still fit.
+// Poll a barrier at most `limit` times, backing off between polls so that a waiting warp does
+// not take issue slots from the warps that are computing.  Returns false if the phase did not
+// complete.  The result is the same in every lane of the warp.
+__device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int limit)
+{
+    bool ok = false;
+    for (int i = 0; i < limit && !ok; ++i) {
+        ok = mbar_try_wait(bar, parity);
+        if (!ok) __nanosleep(40);
+    }
+    return !__any_sync(0xffffffffu, !ok);
+}
+
 template <int DIR, int V, int MINB>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
@@ -849,7 +862,7 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
     for (int it = 0; it < n && !gave_up; ++it) {
         const int b = it & 1;
         const int64_t tile = first + (int64_t)it * gridDim.x;
-        if (__any_sync(0xffffffffu, !mbar_wait_bounded(bars + b, (unsigned)(it >> 1) & 1u, kFirPollLimit))) {
+        if (!fir_wait(bars + b, (unsigned)(it >> 1) & 1u, kFirPollLimit)) {
             gave_up = true;
             break;
         }
@@ -860,15 +873,21 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
         const unsigned xrow = xbuf_saddr + 4u * (unsigned)(b * tile_words + lane * sh.SX + (DIR < 0 ? sh.halo : 0));
 
         // the tile after this one goes into the other buffer once every warp is done with the tile
-        // that is in it now; this warp sees to its rows after its first segment of this tile
+        // that is in it now: at once if that is already so, else after this warp's first segment
+        // of this tile
         bool next_pending = it >= 1 && it + 1 < n;
+        const unsigned free_parity = (unsigned)((it - 1) >> 1) & 1u;
         auto fill_next = [&]() {
-            if (__any_sync(0xffffffffu, !mbar_wait_bounded(bars + 2 + (b ^ 1), (unsigned)((it - 1) >> 1) & 1u, kFirPollLimit))) {
+            if (!fir_wait(bars + 2 + (b ^ 1), free_parity, kFirPollLimit)) {
                 gave_up = true;
                 return;
             }
             fill(b ^ 1, tile + gridDim.x);
         };
+        if (next_pending && __shfl_sync(0xffffffffu, mbar_try_wait(bars + 2 + (b ^ 1), free_parity) ? 1 : 0, 0)) {
+            next_pending = false;
+            fill(b ^ 1, tile + gridDim.x);
+        }
 
         int seg = unit0;
         for (; seg < sh.nseg && !gave_up; seg += nwarps) {
@@ -1046,7 +1065,7 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh, int max
 }
 
 static std::atomic<int> g_fir_packed{0};
-static std::atomic<int> g_fir_flow{1};
+static std::atomic<int> g_fir_flow{2};
 static std::atomic<int> g_fir_skip_zeros{1};
 
 template <int DIR, bool PK = false>

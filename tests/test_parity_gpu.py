@@ -78,15 +78,15 @@ def test_shift_unaligned_buffers_take_the_scalar_path():
 
 
 # --------------------------------------------------------------------------- conv / corr
-@pytest.fixture(params=["scalar", "scalar-roomy", "scalar-tile-barrier", "packed", "packed-half-tiles", "packed-full-tiles"])
+@pytest.fixture(params=["scalar-lean", "scalar", "scalar-tile-barrier", "packed", "packed-half-tiles", "packed-full-tiles"])
 def fir_variant(request):
     """conv / corr have several kernels that must give the same bits: the scalar one in its three
-    forms (segments dealt out across tiles with split-phase barriers - the default -, the same
-    with more registers, one CTA-wide barrier per tile) and the packed one (two rows per lane,
+    forms (segments dealt out across tiles with split-phase barriers, the same with more
+    registers - the default -, one CTA-wide barrier per tile) and the packed one (two rows per lane,
     two-wide FMAs) with either of its tile sizes."""
     from slayerpytorch_b200 import capi
-    packed, flow = {"scalar": (0, 1), "scalar-roomy": (0, 2), "scalar-tile-barrier": (0, 0), "packed": (1, 1),
-                    "packed-half-tiles": (2, 1), "packed-full-tiles": (3, 1)}[request.param]
+    packed, flow = {"scalar-lean": (0, 1), "scalar": (0, 2), "scalar-tile-barrier": (0, 0), "packed": (1, 2),
+                    "packed-half-tiles": (2, 2), "packed-full-tiles": (3, 2)}[request.param]
     before = capi.set_fir_packed(packed), capi.set_fir_flow(flow)
     yield request.param
     capi.set_fir_packed(before[0])
