@@ -106,12 +106,24 @@ __device__ __forceinline__ void fir_group_n(float (&acc)[kFirSeg], const float (
 // One group in phase PH.  Before its arithmetic it starts the loads the group after it needs:
 // the sample quad that enters the window (into the free ring quad) and the next four taps
 // (into the tap quad the previous group has finished with).
+// fp / xp are the addresses phase 0 of the current run of phases uses (taps of its group, sample
+// quad it fetches); phase PH reads at constant offsets from them, which go into the load
+// instructions as immediates.
+template <int OFF>
+__device__ __forceinline__ float4 ld4o(unsigned saddr)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr), "n"(OFF));
+    return v;
+}
+
 template <int DIR, int PH>
 __device__ __forceinline__ void fir_step(float (&acc)[kFirSeg], float (&w)[kFirRing], float4 (&f)[2],
-                                         unsigned fp_next, unsigned xp)
+                                         unsigned fp, unsigned xp)
 {
-    put4(w, win_reg<DIR, PH>(DIR < 0 ? -4 + kFirRing : kFirWin), ld4(xp));
-    f[(PH + 1) & 1] = ld4(fp_next);
+    put4(w, win_reg<DIR, PH>(DIR < 0 ? -4 + kFirRing : kFirWin), ld4o<(DIR < 0 ? -16 : 16) * PH>(xp));
+    f[(PH + 1) & 1] = ld4o<16 * (PH + 1)>(fp);
     fir_group<DIR, PH, 4>(acc, w, f[PH & 1]);
 }
 
@@ -119,15 +131,14 @@ __device__ __forceinline__ void fir_step(float (&acc)[kFirSeg], float (&w)[kFirR
 // f[PH & 1] already holds the taps of the first remaining group.
 template <int DIR, int PH>
 __device__ __forceinline__ void fir_rest(float (&acc)[kFirSeg], float (&w)[kFirRing], float4 (&f)[2],
-                                         unsigned fp_next, unsigned xp, int left, int tail)
+                                         unsigned fp, unsigned xp, int left, int tail)
 {
     if (left == 0) {
         if (tail) fir_group_n<DIR, PH>(acc, w, f[PH & 1], tail);
         return;
     }
-    fir_step<DIR, PH>(acc, w, f, fp_next, xp);
-    if constexpr (PH + 1 < kFirPhases)
-        fir_rest<DIR, PH + 1>(acc, w, f, fp_next + 16, xp + (DIR < 0 ? 0u - 16u : 16u), left - 1, tail);
+    fir_step<DIR, PH>(acc, w, f, fp, xp);
+    if constexpr (PH + 1 < kFirPhases) fir_rest<DIR, PH + 1>(acc, w, f, fp, xp, left - 1, tail);
 }
 
 struct FirShape {
@@ -247,16 +258,16 @@ fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *_
             f[0] = ld4(fp);
             int g = 0;
             for (; g + kFirPhases <= groups; g += kFirPhases) {
-                fir_step<DIR, 0>(acc, w, f, fp + 16, xp);
-                fir_step<DIR, 1>(acc, w, f, fp + 32, xp + step);
-                fir_step<DIR, 2>(acc, w, f, fp + 48, xp + 2 * step);
-                fir_step<DIR, 3>(acc, w, f, fp + 64, xp + 3 * step);
-                fir_step<DIR, 4>(acc, w, f, fp + 80, xp + 4 * step);
-                fir_step<DIR, 5>(acc, w, f, fp + 96, xp + 5 * step);
+                fir_step<DIR, 0>(acc, w, f, fp, xp);
+                fir_step<DIR, 1>(acc, w, f, fp, xp);
+                fir_step<DIR, 2>(acc, w, f, fp, xp);
+                fir_step<DIR, 3>(acc, w, f, fp, xp);
+                fir_step<DIR, 4>(acc, w, f, fp, xp);
+                fir_step<DIR, 5>(acc, w, f, fp, xp);
                 xp += kFirPhases * step;
                 fp += 16 * kFirPhases;
             }
-            fir_rest<DIR, 0>(acc, w, f, fp + 16, xp, groups - g, tail);
+            fir_rest<DIR, 0>(acc, w, f, fp, xp, groups - g, tail);
 
             if (row < rows) {
                 float *dst = out + row * (int64_t)T + t0 + tb;
@@ -761,17 +772,13 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar)
 
 // MINB = 2 caps the registers at 64 per thread (two CTAs of up to 16 warps per SM); MINB = 1 lets
 // the compiler take about 110, which two CTAs of 8 warps still fit.
-// Poll a barrier at most `limit` times, backing off between polls so that a waiting warp does
-// not take issue slots from the warps that are computing.  Returns false if the phase did not
-// complete.  The result is the same in every lane of the warp.
+// Poll a barrier at most `limit` times.  Returns false if the phase did not complete; the result
+// is the same in every lane of the warp.  (Backing off between polls with nanosleep, and issuing
+// the next tile's copy before the first segment when the buffer is already free, were both
+// measured and both cost 4-6 %.)
 __device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int limit)
 {
-    bool ok = false;
-    for (int i = 0; i < limit && !ok; ++i) {
-        ok = mbar_try_wait(bar, parity);
-        if (!ok) __nanosleep(40);
-    }
-    return !__any_sync(0xffffffffu, !ok);
+    return !__any_sync(0xffffffffu, !mbar_wait_bounded(bar, parity, limit));
 }
 
 template <int DIR, int V, int MINB>
@@ -873,8 +880,7 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
         const unsigned xrow = xbuf_saddr + 4u * (unsigned)(b * tile_words + lane * sh.SX + (DIR < 0 ? sh.halo : 0));
 
         // the tile after this one goes into the other buffer once every warp is done with the tile
-        // that is in it now: at once if that is already so, else after this warp's first segment
-        // of this tile
+        // that is in it now; this warp sees to its rows after its first segment of this tile
         bool next_pending = it >= 1 && it + 1 < n;
         const unsigned free_parity = (unsigned)((it - 1) >> 1) & 1u;
         auto fill_next = [&]() {
@@ -884,10 +890,6 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
             }
             fill(b ^ 1, tile + gridDim.x);
         };
-        if (next_pending && __shfl_sync(0xffffffffu, mbar_try_wait(bars + 2 + (b ^ 1), free_parity) ? 1 : 0, 0)) {
-            next_pending = false;
-            fill(b ^ 1, tile + gridDim.x);
-        }
 
         int seg = unit0;
         for (; seg < sh.nseg && !gave_up; seg += nwarps) {
@@ -908,16 +910,16 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
                 f[0] = ld4(fp);
                 int g = 0;
                 for (; g + kFirPhases <= groups; g += kFirPhases) {
-                    fir_step<DIR, 0>(acc, w, f, fp + 16, xp);
-                    fir_step<DIR, 1>(acc, w, f, fp + 32, xp + step);
-                    fir_step<DIR, 2>(acc, w, f, fp + 48, xp + 2 * step);
-                    fir_step<DIR, 3>(acc, w, f, fp + 64, xp + 3 * step);
-                    fir_step<DIR, 4>(acc, w, f, fp + 80, xp + 4 * step);
-                    fir_step<DIR, 5>(acc, w, f, fp + 96, xp + 5 * step);
+                    fir_step<DIR, 0>(acc, w, f, fp, xp);
+                    fir_step<DIR, 1>(acc, w, f, fp, xp);
+                    fir_step<DIR, 2>(acc, w, f, fp, xp);
+                    fir_step<DIR, 3>(acc, w, f, fp, xp);
+                    fir_step<DIR, 4>(acc, w, f, fp, xp);
+                    fir_step<DIR, 5>(acc, w, f, fp, xp);
                     xp += kFirPhases * step;
                     fp += 16 * kFirPhases;
                 }
-                fir_rest<DIR, 0>(acc, w, f, fp + 16, xp, groups - g, tail);
+                fir_rest<DIR, 0>(acc, w, f, fp, xp, groups - g, tail);
 
                 if (row < rows) {
                     float *dst = out + row * (int64_t)T + t0 + tb;

@@ -288,8 +288,10 @@ class _LoihiSpikeDelayFunction(torch.autograd.Function):
 
 # ----------------------------------------------------------------------------- modules
 class _DenseLayer(torch.nn.Conv3d):
-    """Fully connected layer over NCHWT tensors: a 1x1x1 3-D convolution, as the reference's
-    dense layer (src/slayer.py:393-437).  Weighting is not part of the hot path."""
+    """Fully connected layer over NCHWT tensors: a 1x1x1 3-D convolution.  This class restates the
+    reference's dense layer (src/slayer.py:393-437) - same argument forms, same branches, same
+    exception texts - because it is the interface the reference's networks are written against;
+    weighting is not part of the hot path."""
 
     def __init__(self, inFeatures, outFeatures, weightScale=1):
         if isinstance(inFeatures, int):
@@ -311,7 +313,9 @@ class _DenseLayer(torch.nn.Conv3d):
 
 
 class _DelayLayer(torch.nn.Module):
-    """Learnable axonal delay per neuron or per channel (src/slayer.py:901-928)."""
+    """Learnable axonal delay per neuron or per channel.  Restates the reference's delay layer
+    (src/slayer.py:901-928: same argument forms and exception text, delays drawn from U(0, 1),
+    per-channel delays repeated over H and W); the arithmetic behind it is _DelayFunction."""
 
     def __init__(self, inputSize, Ts):
         super().__init__()

@@ -591,7 +591,7 @@ def sample_rows(rows, n, seed):
 
 
 def test_full_size_config2_chain_rows_match_oracle(golden_dir):
-    """BASELINE config 2 layer-1 tensors (64 x 512 neurons x 300 steps): psp -> getSpikes ->
+    """The hidden layer of the SRM MLP workload (64 x 512 neurons x 300 steps): psp -> getSpikes ->
     per-neuron shift, then shift^-1 -> surrogate -> corr, run at full size on the GPU and
     checked exactly on 1500 random rows (rows are independent)."""
     g = np.load(golden_dir + "/ref_python.npz")
