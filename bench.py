@@ -65,15 +65,15 @@ ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12,
              "getSpikesDelayed": 12, "delayGrad": 8, "loihi": 16, "loihiDelayed": 12, "spikeGradCorr": 12}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count) on launches too large for L2; see the summaries under profiles/.
-NCU_TRAFFIC_PER_ELEMENT = {"fir_kernel": 7.33, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
-                           "spike_grad_shift_rows_kernel": 11.6, "loihi_get_spikes_wide_kernel": None,
+NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
+                           "spike_grad_shift_rows_kernel": 11.6, "loihi_get_spikes_wide_kernel": 11.9,
                            "delay_grad_kernel": 8.0}
 
 
 def kernel_of(op, T):
     """Name of the kernel an operator launches for 16-byte aligned fp32 tensors of row length T."""
     quad = T % 4 == 0
-    return {"conv": "fir_kernel", "corr": "fir_kernel", "spikeGradCorr": "fir_kernel",
+    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "spikeGradCorr": "fir_flow_kernel",
             "getSpikes": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "getSpikesDelayed": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "shift": "shift_vec4_kernel" if quad else "shift_flat4_kernel",
