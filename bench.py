@@ -70,8 +70,19 @@ NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "srm_get_spikes_tma_kernel":
                            "delay_grad_kernel": 8.0}
 
 
+# conv inputs of at least this many samples are probed on the device and go to the event-driven
+# kernel when at most SPARSE_DENSITY of the sampled samples are non-zero (csrc/fir.cu, fir_sparse.cuh)
+PROBE_MIN_ELEMENTS = 1 << 25
+SPARSE_DENSITY = 61 / 1024
+
+
+def conv_is_probed(el, T, taps):
+    return el >= PROBE_MIN_ELEMENTS and 64 <= T <= 4096 and 1 <= taps <= 1024
+
+
 def kernel_of(op, T):
-    """Name of the kernel an operator launches for 16-byte aligned fp32 tensors of row length T."""
+    """Name of the kernel an operator launches for 16-byte aligned fp32 tensors of row length T
+    (conv on a mostly-zero input: fir_sparse_kernel instead, see conv_is_probed)."""
     quad = T % 4 == 0
     return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "spikeGradCorr": "fir_flow_kernel",
             "getSpikes": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
@@ -328,19 +339,39 @@ class Workload:
                 taps = int(self.kernels[0].numel())
             calls.append((op, layer, rows * self.T, taps))
             return fn()
+        if not hasattr(self, "conv_density"):
+            # fraction of non-zero samples of every conv input (what the probe kernel estimates)
+            self.conv_density = {}
+            for i, L in enumerate(self.layers):
+                a = L.get("a") if L["kind"] == "psp_spike" else L.get("s_in")
+                if a is not None:
+                    self.conv_density[i] = float((a != 0).float().mean())
         self.step(dry, run)
         self.delay_grads = []
         return calls
 
     def launches_per_step(self, fused):
-        return len(self.op_list(fused))
+        """Kernels launched per step: one per operator call, three for a conv that is probed (the
+        probe, the event-driven kernel and the dense kernel, one of the two returning at once)."""
+        return sum(3 if (op == "conv" and conv_is_probed(el, self.T, taps)) else 1
+                   for op, _, el, taps in self.op_list(fused))
+
+    def sparse_convs(self, fused):
+        """Layers whose conv goes to the event-driven kernel, with the density of its input."""
+        return {layer: self.conv_density[layer] for op, layer, el, taps in self.op_list(fused)
+                if op == "conv" and conv_is_probed(el, self.T, taps)
+                and self.conv_density.get(layer, 1.0) <= SPARSE_DENSITY}
 
     def chain_bound_ms(self, fused, peak_gbs, sm_mhz):
-        """Sum over the step's launches of max(algorithmic bytes / HBM peak, flops / fp32 FMA peak)."""
+        """Sum over the step's launches of max(algorithmic bytes / HBM peak, flops / fp32 FMA peak);
+        a conv on a mostly-zero input that the event-driven kernel takes only owes the products
+        with non-zero samples (2 K flop x density per element)."""
         fma = FMA_LANES * sm_mhz * 1e6
+        sparse = self.sparse_convs(fused)
         total = 0.0
-        for op, _, el, taps in self.op_list(fused):
-            total += max(ALG_BYTES[op] * el / (peak_gbs * 1e9), 2.0 * taps * el / fma)
+        for op, layer, el, taps in self.op_list(fused):
+            flops = 2.0 * taps * el * (sparse[layer] if (op == "conv" and layer in sparse) else 1.0)
+            total += max(ALG_BYTES[op] * el / (peak_gbs * 1e9), flops / fma)
         return total * 1e3
 
 
@@ -743,13 +774,17 @@ def op_table_of(wl, per_op):
 
 def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
     """The kernel with the largest share of the step, described on its largest launch."""
+    sparse = wl.sparse_convs(True)
+
+    def k_of(op, layer):
+        return "fir_sparse_kernel" if (op == "conv" and layer in sparse) else kernel_of(op, wl.T)
     share = {}
     for (op, layer, rows), v in per_op.items():
-        k = kernel_of(op, wl.T)
+        k = k_of(op, layer)
         share[k] = share.get(k, 0.0) + sum(v)
     total = sum(share.values())
     dominant = max(share, key=share.get)
-    cands = [(rows, op, layer) for (op, layer, rows) in per_op if kernel_of(op, wl.T) == dominant]
+    cands = [(rows, op, layer) for (op, layer, rows) in per_op if k_of(op, layer) == dominant]
     rows, op, layer = max(cands)
     times = per_op[(op, layer, rows)]
     avg_ms = sum(times) / len(times)
@@ -764,6 +799,8 @@ def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
            "launch": "L%d/%s, %d x %d fp32" % (layer, op, rows, wl.T), "peak_kind": peak_kind,
            "traffic": (tpe * el if tpe else None), "algorithmic_bytes": alg, "avg_launch_us": round(avg_ms * 1e3, 2),
            "hbm": hbm}
+    if dominant == "fir_sparse_kernel":
+        taps = 0                         # the products with zeros are not owed: HBM bounds it
     fma_bound = taps and (2.0 * taps / (fma_peak * 1e12)) > (ALG_BYTES[op] / (peak * 1e9))
     if fma_bound:
         tfl = 2.0 * taps * el / (avg_ms * 1e-3) / 1e12
@@ -841,7 +878,9 @@ def time_ours(args, rank, world, device):
         "eager_ms_per_step": eager_ms / args.steps,
         "gpu_launches": wl.launches_per_step(fused) * args.steps,
         "chain": {"bound_ms": round(bound_ms, 4), "frac_of_bound": round(bound_ms / (total_ms / args.steps), 4),
-                  "how": "sum over the step's launches of max(algorithmic bytes / measured HBM peak, 2K flop / fp32 FMA peak at the sampled clock)"},
+                  "how": "sum over the step's launches of max(algorithmic bytes / measured HBM peak, 2K flop / fp32 FMA peak at the "
+                         "sampled clock); a conv that the event-driven kernel takes owes 2K flop x input density",
+                  "event_driven_conv_layers": {("L%d" % k): round(v, 4) for k, v in wl.sparse_convs(fused).items()}},
         "roofline": roofline_of(wl, per_op, peak, peak_kind, sm_mhz),
         "per_op": op_table_of(wl, per_op),
     }

@@ -325,13 +325,31 @@ int slayer_b200_set_fir_packed(int enable);
 int slayer_b200_set_fir_flow(int mode);
 
 /*
- * Enable (non-zero, the default) or disable the zero-skipping path of the packed conv / corr
- * kernel (it only matters where that kernel runs); returns the previous setting.  Enabled, the kernel looks at its input tiles and, where
- * most sample positions are zero in all 64 rows of a tile (spike tensors), only visits the
- * positions that are not; the results are the same bits (a zero sample leaves every sum it
- * enters unchanged).  It has no counterpart in the reference.
+ * Stages (tiles of 32 rows x 64 steps) that every warp of the bulk-tensor-copy SRM spike kernel
+ * keeps in shared memory in launches too large to be resident at once: 2 .. 8; returns the
+ * previous setting, and only that for a value outside the range.  Fewer stages per warp leave
+ * room for more warps per SM.  The result does not depend on it.  The no-allocation entry point
+ * is not affected.  It has no counterpart in the reference.
  */
-int slayer_b200_set_fir_skip_zeros(int enable);
+int slayer_b200_set_srm_stages(int stages);
+
+/*
+ * Zero skipping in conv / corr / conv_packed; returns the previous setting.  A zero sample leaves
+ * every sum it enters unchanged, so all settings give the same bits.
+ *   0: never.
+ *   1 (the default): conv and conv_packed inputs of at least 2^25 samples with rows of 64 .. 4096
+ *      steps and at most 1024 taps are sampled by a probe kernel (corr, which filters gradients, is
+ *      not); if at most 6 % (conv_packed: 20 %) of the sampled samples are non-zero
+ *      (spike tensors) and every tap is finite, the event-driven kernel runs - a warp lists the
+ *      non-zero samples of a row and adds their contributions to the outputs they reach, work in
+ *      proportion to events x taps - otherwise the dense kernel.  The decision stays on the
+ *      device: both kernels are enqueued and the one ruled out returns at once.  The packed
+ *      two-row kernel (slayer_b200_set_fir_packed) also skips sample positions that are zero in
+ *      all 64 rows of a tile.
+ *   2: the event-driven kernel for every input it can take, whatever the density (testing).
+ * It has no counterpart in the reference.
+ */
+int slayer_b200_set_fir_skip_zeros(int mode);
 
 #ifdef __cplusplus
 }

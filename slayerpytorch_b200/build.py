@@ -31,6 +31,7 @@ CUDA_SOURCES = {
     "common.cu": [],
     "shift.cu": [],
     "fir.cu": ["-ftz=true"],
+    "fir_sparse.cu": ["-ftz=true"],
     "srm_spike.cu": ["-ftz=true"],
     "loihi_spike.cu": [],
     "spike_grad.cu": [],
@@ -40,7 +41,7 @@ CUDA_SOURCES = {
     "loss.cu": ["-ftz=true"],
     "tma.cu": [],
 }
-HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", os.path.join(INCLUDE, "slayer_b200.h")]
+HEADERS = ["common.cuh", "tile.cuh", "tma.cuh", "fir_sparse.cuh", os.path.join(INCLUDE, "slayer_b200.h")]
 
 MODULES = {"slayerCuda": "bindings_slayer.cpp", "slayerLoihiCuda": "bindings_loihi.cpp"}
 

@@ -48,6 +48,7 @@ SYMBOLS = {
     "slayer_b200_set_fir_packed": (_int, [_int]),
     "slayer_b200_set_fir_skip_zeros": (_int, [_int]),
     "slayer_b200_set_fir_flow": (_int, [_int]),
+    "slayer_b200_set_srm_stages": (_int, [_int]),
 }
 
 _lib = None
@@ -105,9 +106,16 @@ def set_fir_flow(mode):
     return int(load().slayer_b200_set_fir_flow(int(mode)))
 
 
-def set_fir_skip_zeros(enable):
-    """Enable/disable the zero-skipping path of the packed conv / corr kernel; returns the previous setting."""
-    return bool(load().slayer_b200_set_fir_skip_zeros(1 if enable else 0))
+def set_srm_stages(stages):
+    """Stages per warp of the SRM spike kernel in large launches (2 .. 8); returns the previous setting."""
+    return int(load().slayer_b200_set_srm_stages(int(stages)))
+
+
+def set_fir_skip_zeros(mode):
+    """Zero skipping in conv / corr / conv_packed: 0 / False = never, 1 / True = a probe on the device
+    picks the event-driven kernel for mostly-zero inputs (default), 2 = the event-driven kernel for
+    every input it can take.  Returns the previous setting."""
+    return int(load().slayer_b200_set_fir_skip_zeros(int(mode)))
 
 
 def set_tma(enable):

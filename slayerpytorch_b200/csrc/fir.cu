@@ -28,8 +28,10 @@
 // The row stride of the tile is = 4 (mod 8) words, which makes the per-row 128-bit loads of a
 // warp conflict free.
 #include <atomic>
+#include <cfloat>
 
 #include "common.cuh"
+#include "fir_sparse.cuh"
 #include "tile.cuh"
 #include "tma.cuh"
 
@@ -154,8 +156,9 @@ struct FirShape {
 template <int DIR, int V>
 __global__ void __launch_bounds__(kFirMaxWarps * 32)
 fir_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-           int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles)
+           int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, const int *skip_flag)
 {
+    if (skip_flag != nullptr && *skip_flag != 0) return;      // the event-driven kernel has this call
     extern __shared__ __align__(16) float smem[];
     const int Tt = sh.nseg * kFirSeg;
     const int WX = Tt + sh.halo;
@@ -470,8 +473,10 @@ __device__ __forceinline__ void fir2_sparse_segment(f2 (&acc)[kFirSeg], const un
 template <int DIR, int V, bool PK = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, 1)
 fir2_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, bool sparse_ok, float spike_value)
+            int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, bool sparse_ok, float spike_value,
+            const int *skip_flag)
 {
+    if (skip_flag != nullptr && *skip_flag != 0) return;      // the event-driven kernel has this call
     extern __shared__ __align__(16) float smem[];
     const int Tt = sh.nseg * kFirSeg;
     const int WX = Tt + sh.halo;
@@ -784,8 +789,9 @@ __device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int lim
 template <int DIR, int V, int MINB>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-                int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status)
+                int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status, const int *skip_flag)
 {
+    if (skip_flag != nullptr && *skip_flag != 0) return;      // the event-driven kernel has this call
     extern __shared__ __align__(16) float smem[];
     const int Tt = sh.nseg * kFirSeg;
     const int WX = Tt + sh.halo;
@@ -960,8 +966,9 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
 template <int DIR>
 __global__ void __launch_bounds__(256)
 fir_long_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-                int64_t rows, int64_t T, int64_t K, float Ts)
+                int64_t rows, int64_t T, int64_t K, float Ts, const int *skip_flag)
 {
+    if (skip_flag != nullptr && *skip_flag != 0) return;      // the event-driven kernel has this call
     const int64_t n = rows * T;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
@@ -1069,11 +1076,14 @@ static bool fir2_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh, int max
 static std::atomic<int> g_fir_packed{0};
 static std::atomic<int> g_fir_flow{2};
 static std::atomic<int> g_fir_skip_zeros{1};
+// Below this many input samples the dense kernel takes less than about 0.1 ms and the probe and
+// the second launch (about 10 microseconds together) are not worth it.
+constexpr int64_t kFirProbeMinElements = 1 << 25;
 
 template <int DIR, bool PK = false>
 static int launch_fir2(float *out, const float *in, const float *filt,
                        int64_t rows, int64_t T, int64_t Keff, float Ts, cudaStream_t stream, bool &taken,
-                       float spike_value = 0.0f)
+                       float spike_value = 0.0f, const int *skip_flag = nullptr)
 {
     // Two CTAs per SM with half-size tiles (more warps to keep the FMA pipe busy across barriers,
     // and one CTA's tile copy overlaps the other's arithmetic) where a half-size tile still has
@@ -1103,7 +1113,7 @@ static int launch_fir2(float *out, const float *in, const float *filt,
     int64_t grid = ctas_per_sm * (int64_t)sm_count();
     if (grid > ntiles) grid = ntiles;
     kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles,
-                                                           g_fir_skip_zeros.load() != 0, spike_value);
+                                                           g_fir_skip_zeros.load() != 0, spike_value, skip_flag);
     return check_launch("fir (packed) kernel launch");
 }
 
@@ -1118,9 +1128,26 @@ static int launch_fir(float *out, const float *in, const float *filt,
         return SLAYER_B200_OK;
     }
     const int64_t Keff = K < T ? K : T;              // taps beyond the row length never contribute
+    // Mostly-zero inputs (spike tensors) of some size: the event-driven kernel.  Mode 2 takes it
+    // unconditionally; mode 1 lets a probe on the device decide between it and the dense kernel
+    // (both are enqueued; the one ruled out returns at once).
+    const int *skip_flag = nullptr;
+    const int zmode = g_fir_skip_zeros.load();
+    if (zmode != 0 && fir_sparse_eligible(rows, T, Keff)) {
+        if (zmode == 2) return fir_sparse_launch(DIR, false, out, in, filt, rows, T, Keff, Ts, 0.0f, nullptr, stream);
+        // (corr runs in the backward pass, on gradients, which are dense: it is not probed)
+        if (DIR < 0 && rows * T >= kFirProbeMinElements) {
+            int rc = fir_sparse_probe(in, rows, T, false, filt, Keff, stream, &skip_flag);
+            if (rc) return rc;
+            if (skip_flag) {
+                rc = fir_sparse_launch(DIR, false, out, in, filt, rows, T, Keff, Ts, 0.0f, skip_flag, stream);
+                if (rc) return rc;
+            }
+        }
+    }
     if (g_fir_packed.load() != 0) {
         bool taken = false;
-        const int rc = launch_fir2<DIR>(out, in, filt, rows, T, Keff, Ts, stream, taken);
+        const int rc = launch_fir2<DIR>(out, in, filt, rows, T, Keff, Ts, stream, taken, 0.0f, skip_flag);
         if (taken) return rc;
     }
     FirShape sh;
@@ -1131,7 +1158,7 @@ static int launch_fir(float *out, const float *in, const float *filt,
         int64_t g = ceil_div(n, 256);
         const int64_t cap = (int64_t)sm_count() * 32;
         if (g > cap) g = cap;
-        fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts);
+        fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts, skip_flag);
         return check_launch("fir (long filter) kernel launch");
     }
     const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
@@ -1148,13 +1175,13 @@ static int launch_fir(float *out, const float *in, const float *filt,
                           : (vw == 4 ? fir_flow_kernel<DIR, 4, 2> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2> : fir_flow_kernel<DIR, 1, 2>));
         int rc = reserve_dynamic_smem((const void *)kern, smem);
         if (rc) return rc;
-        kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status);
+        kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status, skip_flag);
         return check_launch("fir (flow) kernel launch");
     }
     auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
-    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles);
+    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, skip_flag);
     return check_launch("fir kernel launch");
 }
 
@@ -1180,9 +1207,9 @@ extern "C" int slayer_b200_set_fir_flow(int mode)
     return sb200::g_fir_flow.exchange(mode < 0 || mode > 2 ? 1 : mode);
 }
 
-extern "C" int slayer_b200_set_fir_skip_zeros(int enable)
+extern "C" int slayer_b200_set_fir_skip_zeros(int mode)
 {
-    return sb200::g_fir_skip_zeros.exchange(enable ? 1 : 0);
+    return sb200::g_fir_skip_zeros.exchange(mode < 0 || mode > 2 ? 1 : mode);
 }
 
 extern "C" int slayer_b200_conv(float *out, const float *in, const float *filter,
@@ -1209,9 +1236,26 @@ extern "C" int slayer_b200_conv_packed(float *out, const uint32_t *bits, const f
         if (e != cudaSuccess) { set_error("conv_packed: memset failed: %s", cudaGetErrorString(e)); return SLAYER_B200_ECUDA; }
         return SLAYER_B200_OK;
     }
+    const int64_t Keff = K < T ? K : T;
+    const int *skip_flag = nullptr;
+    const int zmode = g_fir_skip_zeros.load();
+    FirShape probe_shape;
+    const bool dense_ok = fir2_shape(rows, T, Keff, probe_shape, kFir2MaxSamples);
+    if (zmode != 0 && fir_sparse_eligible(rows, T, Keff) && fabsf(spike_value) <= FLT_MAX) {
+        // (filters too long for the tiled kernel: the event-driven one, whatever the density)
+        if (zmode == 2 || !dense_ok) return fir_sparse_launch(-1, true, out, bits, filter, rows, T, Keff, Ts, spike_value, nullptr, (cudaStream_t)stream);
+        if (rows * T >= kFirProbeMinElements) {
+            rc = fir_sparse_probe(bits, rows, T, true, filter, Keff, (cudaStream_t)stream, &skip_flag);
+            if (rc) return rc;
+            if (skip_flag) {
+                rc = fir_sparse_launch(-1, true, out, bits, filter, rows, T, Keff, Ts, spike_value, skip_flag, (cudaStream_t)stream);
+                if (rc) return rc;
+            }
+        }
+    }
     bool taken = false;
-    rc = launch_fir2<-1, true>(out, reinterpret_cast<const float *>(bits), filter, rows, T, K < T ? K : T, Ts,
-                               (cudaStream_t)stream, taken, spike_value);
+    rc = launch_fir2<-1, true>(out, reinterpret_cast<const float *>(bits), filter, rows, T, Keff, Ts,
+                               (cudaStream_t)stream, taken, spike_value, skip_flag);
     if (!taken) {
         set_error("conv_packed: a filter of %lld taps is too long for the tiled kernel; unpack the spikes and call "
                   "slayer_b200_conv", (long long)K);

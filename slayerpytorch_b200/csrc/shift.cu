@@ -143,6 +143,84 @@ spike_grad_shift_rows_kernel(float4 *__restrict__ out, const float4 *__restrict_
     }
 }
 
+// The same fused pass for rows of any length (16-byte aligned buffers, T % 4 != 0): rows start
+// anywhere in a 16-byte quad, so a CTA takes a block of rows whose first element is quad aligned
+// (rows_per_block is a multiple of 4 / gcd(T, 4)) and its threads stride over the aligned quads
+// of that contiguous range, (row, time) advanced incrementally.  A quad inside one row whose
+// source samples lie inside the same row is assembled from two aligned source quads; the few
+// quads that straddle a row end, or whose source does, go sample by sample.
+template <bool LUT>
+__global__ void __launch_bounds__(256)
+spike_grad_shift_flat_rows_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ u,
+                                  const float *__restrict__ lut, float shift, float Ts,
+                                  int64_t rows, int T, int64_t nNeurons, int rows_per_block,
+                                  float theta, float tau, float c)
+{
+    __shared__ int sd[kRhoRowsMax];
+    const int64_t total = rows * (int64_t)T;
+    const int step_e = 4 * (int)blockDim.x;                 // elements a thread advances per iteration
+    const int step_r = step_e / T, step_t = step_e % T;
+    for (int64_t r0 = (int64_t)blockIdx.x * rows_per_block; r0 < rows; r0 += (int64_t)gridDim.x * rows_per_block) {
+        const int nr = (int)(rows - r0 < rows_per_block ? rows - r0 : rows_per_block);
+        __syncthreads();                       // the previous block of rows is done with sd
+        if ((int)threadIdx.x < nr)
+            sd[threadIdx.x] = shift_steps(LUT ? __ldg(lut + ((r0 + threadIdx.x) % nNeurons)) : shift, Ts);
+        __syncthreads();
+        const int64_t base = r0 * (int64_t)T;               // multiple of 4: the block starts on a quad
+        const int n_el = nr * T;                            // elements of the block (the last block may end inside a quad)
+        int e = 4 * (int)threadIdx.x;                       // element offset of this thread's quad inside the block
+        int r = e / T, t = e - r * T;
+        for (; e < n_el; e += step_e) {
+            const int d = sd[r < nr ? r : nr - 1];
+            const int64_t src = base + e - d;               // flat index of the first source sample
+            const bool whole = e + 4 <= n_el;               // false only for the ragged end of the array
+            // u and out are element for element the same quad, whatever the rows do
+            float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (whole) uv = __ldg(reinterpret_cast<const float4 *>(u + base + e));
+            float4 g;
+            if (t + 4 <= T && t - d >= 0 && t - d + 4 <= T && (src & ~3LL) + 8 <= total) {
+                // whole quad inside row r, fed from inside row r: two aligned source quads
+                const float4 *in4 = reinterpret_cast<const float4 *>(in);
+                const int64_t a = src >> 2;
+                const int o = (int)(src & 3);
+                const float4 v0 = __ldg(in4 + a);
+                g = v0;
+                if (o != 0) {
+                    const float4 v1 = __ldg(in4 + a + 1);
+                    if (o == 1) g = make_float4(v0.y, v0.z, v0.w, v1.x);
+                    else if (o == 2) g = make_float4(v0.z, v0.w, v1.x, v1.y);
+                    else g = make_float4(v0.w, v1.x, v1.y, v1.z);
+                }
+            } else {
+                // a quad that straddles a row end, or whose source does: four independent loads
+                float ge[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    int rk = r, tk = t + k;
+                    while (tk >= T) { tk -= T; ++rk; }
+                    const bool in_block = e + k < n_el;
+                    const int ts = tk - sd[in_block ? rk : 0];
+                    ge[k] = (in_block && ts >= 0 && ts < T) ? __ldg(in + base + (int64_t)rk * T + ts) : 0.0f;
+                }
+                g = make_float4(ge[0], ge[1], ge[2], ge[3]);
+            }
+            if (whole) {
+                *reinterpret_cast<float4 *>(out + base + e) =
+                    make_float4(rho_times(g.x, uv.x, theta, tau, c), rho_times(g.y, uv.y, theta, tau, c),
+                                rho_times(g.z, uv.z, theta, tau, c), rho_times(g.w, uv.w, theta, tau, c));
+            } else {
+                const float ge[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (e + k < n_el) out[base + e + k] = rho_times(ge[k], __ldg(u + base + e + k), theta, tau, c);
+            }
+            r += step_r;
+            t += step_t;
+            if (t >= T) { t -= T; ++r; }
+        }
+    }
+}
+
 // Any row length (16-byte aligned buffers): rows start anywhere in a quad.
 template <bool LUT, bool RHO>
 __global__ void __launch_bounds__(256)
@@ -254,6 +332,17 @@ static int launch_shift(float *out, const float *in, const float *lut, float shi
     } else if (vec) {
         if (lut) shift_vec4_kernel<true, RHO><<<g, threads, 0, stream>>>((float4 *)out, (const float4 *)in, l, 0.f, Ts, rows, (int)(T / 4), nn, lpr_log2, ra);
         else shift_vec4_kernel<false, RHO><<<g, threads, 0, stream>>>((float4 *)out, (const float4 *)in, nullptr, shift, Ts, rows, (int)(T / 4), nn, lpr_log2, ra);
+    } else if (flat && RHO && T < (1 << 20)) {
+        const int unit = (T & 1) ? 4 : 2;               // rows per quad-aligned unit (T % 4 != 0 here)
+        int rpb = (int)((4096 + T - 1) / T);            // about four quads per thread and block of rows
+        rpb = ((rpb + unit - 1) / unit) * unit;
+        if (rpb > kRhoRowsMax) rpb = kRhoRowsMax;       // kRhoRowsMax is a multiple of 4
+        int64_t nb = ceil_div(rows, rpb);
+        if (nb > cap) nb = cap;
+        if (lut) spike_grad_shift_flat_rows_kernel<true><<<(unsigned)nb, threads, 0, stream>>>(
+            out, in, ra.u, l, 0.f, Ts, rows, (int)T, nn, rpb, ra.theta, ra.tau, ra.c);
+        else spike_grad_shift_flat_rows_kernel<false><<<(unsigned)nb, threads, 0, stream>>>(
+            out, in, ra.u, nullptr, shift, Ts, rows, (int)T, nn, rpb, ra.theta, ra.tau, ra.c);
     } else if (flat) {
         if (lut) shift_flat4_kernel<true, RHO><<<g, threads, 0, stream>>>(out, in, l, 0.f, Ts, rows, (int)T, nn, lpr_log2, ra);
         else shift_flat4_kernel<false, RHO><<<g, threads, 0, stream>>>(out, in, nullptr, shift, Ts, rows, (int)T, nn, lpr_log2, ra);

@@ -32,6 +32,7 @@
 // Three data-movement paths feed the same recurrence: bulk tensor copies (TMA) for the loads
 // when rows start on 16-byte boundaries (T % 4 == 0), cp.async with row-skewed wide tiles for
 // any other row length, and cp.async with 32-step tiles for unaligned buffers.
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -410,6 +411,8 @@ constexpr int kBoxBytes = kTileWords * 4;       // 4 KB
 constexpr int kStageBytes = 2 * kBoxBytes;      // one wide tile
 constexpr int kUStages = 3;                     // stages per warp in large launches
 constexpr int kMaxUStages = 8;
+// stages per warp in large launches of the allocating entry points (2 or 3; a tuning switch)
+static std::atomic<int> g_srm_stages{kUStages};
 constexpr int kLoadPollLimit = 1 << 22;         // polls of a load barrier before giving up
 
 // dynamic shared memory of a launch with `warps` warps per CTA and `ustages` stages per warp
@@ -747,7 +750,7 @@ static int launch_srm(const SrmArgs &a)
             const int64_t warps_per_sm = ceil_div(nblocks, sms);
             int ustages = (int)((208 * 1024) / (warps_per_sm * kStageBytes));
             if (ustages > kMaxUStages) ustages = kMaxUStages;
-            if (ustages < kUStages) ustages = kUStages;
+            if (ustages < g_srm_stages.load()) ustages = g_srm_stages.load();
             spike_launch_shape(nblocks, (size_t)ustages * kStageBytes + 512, warps, grid);
             const size_t smem = srm_tma_smem(warps, ustages, a.nuEff, NB == 0);
             auto kern = srm_get_spikes_tma_kernel<NB, W>;
@@ -827,7 +830,7 @@ static int launch_srm_delayed(const SrmArgs &a, const DelayArgs &da)
     const int64_t warps_per_sm = ceil_div(nblocks, (int64_t)sms);
     int ustages = (int)(((208 * 1024) / warps_per_sm - (int64_t)mask_bytes) / kStageBytes);
     if (ustages > kMaxUStages) ustages = kMaxUStages;
-    if (ustages < kUStages) ustages = kUStages;
+    if (ustages < g_srm_stages.load()) ustages = g_srm_stages.load();
     int warps, grid;
     spike_launch_shape(nblocks, (size_t)ustages * kStageBytes + mask_bytes + 256, warps, grid);
     const size_t smem = srm_tma_smem(warps, ustages, a.nuEff, NB == 0, ntiles);
@@ -873,7 +876,7 @@ static int launch_srm_packed(const SrmArgs &a)
     const int64_t warps_per_sm = ceil_div(nblocks, sms);
     int ustages = (int)((208 * 1024) / (warps_per_sm * kStageBytes));
     if (ustages > kMaxUStages) ustages = kMaxUStages;
-    if (ustages < kUStages) ustages = kUStages;
+    if (ustages < g_srm_stages.load()) ustages = g_srm_stages.load();
     int warps, grid;
     spike_launch_shape(nblocks, (size_t)ustages * kStageBytes + 512, warps, grid);
     const size_t smem = srm_tma_smem(warps, ustages, a.nuEff, NB == 0);
@@ -1168,4 +1171,10 @@ extern "C" int slayer_b200_srm_get_spikes_delayed(float *delayed, float *s_scrat
     if (rc) return rc;
     if (shift_lut) return slayer_b200_shift_lut(delayed, s_scratch, shift_lut, nBatch, nNeurons, T, Ts, stream_);
     return slayer_b200_shift_scalar(delayed, s_scratch, shift, rows, T, Ts, stream_);
+}
+
+extern "C" int slayer_b200_set_srm_stages(int stages)
+{
+    if (stages < 2 || stages > sb200::kMaxUStages) return sb200::g_srm_stages.load();
+    return sb200::g_srm_stages.exchange(stages);
 }

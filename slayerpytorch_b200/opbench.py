@@ -37,7 +37,11 @@ def main(argv=None):
                     help="conv/corr: kernel selection as slayer_b200_set_fir_packed takes it (0 scalar, 1 packed, 2 / 3 tile size)")
     ap.add_argument("--fir-flow", type=int, default=None, metavar="MODE",
                     help="conv/corr: form of the scalar kernel as slayer_b200_set_fir_flow takes it (0, 1, 2)")
-    ap.add_argument("--no-skip-zeros", action="store_true", help="conv/corr: packed kernel without its zero-skipping path")
+    ap.add_argument("--srm-stages", type=int, default=None, metavar="N",
+                    help="getSpikes*: stages per warp as slayer_b200_set_srm_stages takes it (2 .. 8)")
+    ap.add_argument("--no-skip-zeros", action="store_true", help="conv/corr: no zero skipping (the dense kernels only)")
+    ap.add_argument("--skip-zeros", type=int, default=None, metavar="MODE",
+                    help="conv/corr/convPacked: zero skipping as slayer_b200_set_fir_skip_zeros takes it (0 never, 1 probe, 2 always event-driven)")
     ap.add_argument("--spikes", action="store_true", help="conv/corr: the input is a 0/1 spike tensor of the given density")
     args = ap.parse_args(argv)
 
@@ -48,9 +52,15 @@ def main(argv=None):
     if args.fir_flow is not None:
         from slayerpytorch_b200 import capi
         capi.set_fir_flow(args.fir_flow)
+    if args.srm_stages is not None:
+        from slayerpytorch_b200 import capi
+        capi.set_srm_stages(args.srm_stages)
     if args.no_skip_zeros:
         from slayerpytorch_b200 import capi
-        capi.set_fir_skip_zeros(False)
+        capi.set_fir_skip_zeros(0)
+    if args.skip_zeros is not None:
+        from slayerpytorch_b200 import capi
+        capi.set_fir_skip_zeros(args.skip_zeros)
     dev = torch.device("cuda")
     gen = torch.Generator(device=dev).manual_seed(1)
     neurons = min(args.neurons, args.rows)

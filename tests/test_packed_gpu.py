@@ -78,19 +78,31 @@ def test_get_spikes_packed_sizes_the_kernel_does_not_take():
     assert torch.equal(sc.unpackSpikes(bits, 301, 1.0), s) and torch.equal(sc.packSpikes(s), bits)
 
 
+@pytest.mark.parametrize("zeros", [0, 1, 2])
 @pytest.mark.parametrize("density", [0.002, 0.05, 0.5])
 @pytest.mark.parametrize("T,K", [(300, 77), (301, 77), (64, 8), (1450, 110), (33, 40), (2000, 2)])
-def test_conv_packed_equals_conv_of_the_fp32_view(density, T, K):
+def test_conv_packed_equals_conv_of_the_fp32_view(density, T, K, zeros):
+    """zeros: the zero-skipping setting - dense tiled kernel only, probe (these inputs have 2^25
+    samples and more where T allows the event-driven kernel), event-driven kernel forced."""
+    from slayerpytorch_b200 import capi
     rng = np.random.RandomState(int(density * 1000) + T + K)
-    rows = 9000 if T <= 301 else 300
-    s = (rng.rand(rows, T) < density).astype(np.float32)
+    rows = (1 << 25) // T + 5 if T >= 64 else 9000
+    gen = torch.Generator(device="cuda").manual_seed(int(density * 1000) + T + K)
+    s = (torch.rand(rows, T, device="cuda", generator=gen) < density).float()
     f = rng.randn(K).astype(np.float32)
-    bits = G.c_pack(G.dev(s))
-    for Ts in (1.0, 0.1):
-        value = np.float32(1.0) / np.float32(Ts)
-        got = G.host(G.c_conv_packed(bits, T, G.dev(f), value, Ts))
-        np.testing.assert_array_equal(got, G.host(G.c_conv(G.dev(s * value), G.dev(f), Ts)))
-        np.testing.assert_array_equal(got, co.conv(s * value, f, Ts))
+    bits = G.c_pack(s)
+    before = capi.set_fir_skip_zeros(zeros)
+    try:
+        for Ts in (1.0, 0.1):
+            value = np.float32(1.0) / np.float32(Ts)
+            got = G.c_conv_packed(bits, T, G.dev(f), value, Ts)
+            capi.set_fir_skip_zeros(0)
+            assert torch.equal(got, G.c_conv(s * float(value), G.dev(f), Ts))
+            capi.set_fir_skip_zeros(zeros)
+            np.testing.assert_array_equal(G.host(got[:300]), co.conv(G.host(s[:300]) * value, f, Ts))
+    finally:
+        capi.set_fir_skip_zeros(before)
+    assert capi.device_status() == 0
 
 
 def test_conv_packed_very_long_filter():

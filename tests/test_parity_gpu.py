@@ -78,19 +78,23 @@ def test_shift_unaligned_buffers_take_the_scalar_path():
 
 
 # --------------------------------------------------------------------------- conv / corr
-@pytest.fixture(params=["scalar-lean", "scalar", "scalar-tile-barrier", "packed", "packed-half-tiles", "packed-full-tiles"])
+@pytest.fixture(params=["scalar-lean", "scalar", "scalar-tile-barrier", "packed", "packed-half-tiles", "packed-full-tiles",
+                        "event-driven"])
 def fir_variant(request):
     """conv / corr have several kernels that must give the same bits: the scalar one in its three
     forms (segments dealt out across tiles with split-phase barriers, the same with more
-    registers - the default -, one CTA-wide barrier per tile) and the packed one (two rows per lane,
-    two-wide FMAs) with either of its tile sizes."""
+    registers - the default -, one CTA-wide barrier per tile), the packed one (two rows per lane,
+    two-wide FMAs) with either of its tile sizes, and the event-driven one (a list of non-zero
+    samples per row; here forced on whatever the input holds)."""
     from slayerpytorch_b200 import capi
-    packed, flow = {"scalar-lean": (0, 1), "scalar": (0, 2), "scalar-tile-barrier": (0, 0), "packed": (1, 2),
-                    "packed-half-tiles": (2, 2), "packed-full-tiles": (3, 2)}[request.param]
-    before = capi.set_fir_packed(packed), capi.set_fir_flow(flow)
+    packed, flow, zeros = {"scalar-lean": (0, 1, 1), "scalar": (0, 2, 1), "scalar-tile-barrier": (0, 0, 1), "packed": (1, 2, 1),
+                           "packed-half-tiles": (2, 2, 1), "packed-full-tiles": (3, 2, 1),
+                           "event-driven": (0, 2, 2)}[request.param]
+    before = capi.set_fir_packed(packed), capi.set_fir_flow(flow), capi.set_fir_skip_zeros(zeros)
     yield request.param
     capi.set_fir_packed(before[0])
     capi.set_fir_flow(before[1])
+    capi.set_fir_skip_zeros(before[2])
     assert capi.device_status() == 0
 
 
@@ -184,6 +188,66 @@ def test_conv_corr_on_spike_tensors_skip_zeros(density, T, K):
     finally:
         capi.set_fir_skip_zeros(True)
         capi.set_fir_packed(before)
+
+
+@pytest.mark.parametrize("density", [0.0, 0.01, 0.04, 0.3])
+@pytest.mark.parametrize("T,K", [(300, 77), (301, 2), (1450, 110), (64, 64), (4096, 33)])
+def test_conv_corr_probe_picks_a_kernel_and_the_bits_do_not_change(density, T, K):
+    """conv inputs of 2^25 samples and more are sampled on the device and go to the event-driven
+    kernel or to the dense one; forced either way the bits are the same (corr too, which only takes
+    the event-driven kernel when forced), and the oracle's on sampled rows.  Some rows are dense,
+    one holds non-finite samples, a -0.0 counts as zero."""
+    from slayerpytorch_b200 import capi
+    rng = np.random.RandomState(int(density * 1e3) + T + K)
+    rows = (1 << 25) // T + 37
+    gen = torch.Generator(device="cuda").manual_seed(int(density * 1e3) + T + K)
+    xd = torch.randn(rows, T, device="cuda", generator=gen)
+    xd.mul_((torch.rand(rows, T, device="cuda", generator=gen) < density).float())
+    special = {11: rng.randn(T), rows - 1: rng.randn(T), 17: np.zeros(T), 5: np.zeros(T)}
+    special[5][7 % T] = -0.0
+    special[17][T // 2], special[17][T - 1], special[17][0] = np.inf, np.nan, -np.inf
+    for r, v in special.items():
+        xd[r] = torch.from_numpy(v.astype(np.float32)).cuda()
+    f = rng.randn(K).astype(np.float32)
+    fd = G.dev(f)
+    got = {}
+    before = capi.set_fir_skip_zeros(1)
+    try:
+        for mode in (0, 1, 2):
+            capi.set_fir_skip_zeros(mode)
+            got[mode] = (G.c_conv(xd, fd, 0.5), G.c_conv(xd, fd, 0.5, corr=True))
+    finally:
+        capi.set_fir_skip_zeros(before)
+    for mode in (1, 2):
+        for a, b in zip(got[mode], got[0]):
+            assert torch.equal(torch.nan_to_num(a, nan=12345.0), torch.nan_to_num(b, nan=12345.0))
+            assert torch.equal(torch.isnan(a), torch.isnan(b))
+    pick = torch.tensor([0, 1, 5, 11, 12, 16, 18, rows // 2, rows - 2, rows - 1], device="cuda")
+    x = G.host(xd[pick])
+    assert_close_or_equal(G.host(got[1][0][pick]), co.conv(x, f, 0.5))
+    assert_close_or_equal(G.host(got[1][1][pick]), co.corr(x, f, 0.5))
+
+
+def test_conv_probe_with_a_non_finite_tap_takes_the_dense_kernel():
+    """0 x Inf is NaN: with a non-finite tap a zero sample does change the sums it enters, so the
+    probe rules the event-driven kernel out and the dense result stands."""
+    from slayerpytorch_b200 import capi
+    rng = np.random.RandomState(21)
+    rows, T = (1 << 25) // 300 + 1, 300
+    xd = (torch.rand(rows, T, device="cuda") < 0.01).float()
+    f = rng.randn(20).astype(np.float32)
+    f[7] = -np.inf
+    fd = G.dev(f)
+    before = capi.set_fir_skip_zeros(0)
+    try:
+        dense = G.c_conv(xd, fd, 1.0)
+        capi.set_fir_skip_zeros(1)
+        auto = G.c_conv(xd, fd, 1.0)
+    finally:
+        capi.set_fir_skip_zeros(before)
+    assert not torch.isfinite(dense[:, 7:]).any()
+    assert torch.equal(torch.isnan(auto), torch.isnan(dense))
+    assert torch.equal(torch.nan_to_num(auto, nan=1.0), torch.nan_to_num(dense, nan=1.0))
 
 
 def test_conv_skip_zeros_with_non_finite_samples():
@@ -518,7 +582,8 @@ def test_srm_delayed_sizes_outside_the_fused_path(T):
 # ----------------------------------------------------------------------- spike_grad_shift
 @pytest.mark.parametrize("shape,Ts", [((1, 1, 1, 1, 1), 1.0), ((2, 3, 1, 1, 7), 1.0), ((5, 10, 4, 3, 500), 0.1),
                                       ((3, 16, 1, 1, 300), 1.0), ((4, 8, 2, 1, 301), 0.5), ((2, 6, 1, 1, 1450), 1.0),
-                                      ((3, 5, 1, 1, 33), 2.0)])
+                                      ((3, 5, 1, 1, 33), 2.0), ((7, 37, 1, 1, 1450), 1.0), ((5, 51, 1, 1, 6), 1.0),
+                                      ((3, 11, 1, 1, 2), 1.0), ((13, 67, 1, 1, 45), 1.0), ((1, 3, 1, 1, 5001), 1.0)])
 def test_spike_grad_shift_equals_shift_then_spike_grad(shape, Ts):
     """The fused backward pass gives the bits of the two operators it replaces, and of the oracle."""
     rng = np.random.RandomState(sum(shape) + 1)
