@@ -5,9 +5,9 @@
 // A dense filter spends K multiply-adds per output sample whatever the input holds; at the spike
 // rates of a trained network (a few percent) almost all of them multiply a zero.  Here a warp
 // takes one row: it turns the row into a list of its non-zero samples (time, value) in shared
-// memory - one ballot per 32 samples - and then walks the outputs 64 at a time, lane l owning the
-// samples t0 + l and t0 + 32 + l, adding the contributions of the events that can reach that
-// window in the order the dense sum visits them.  Skipped terms are products with zero, so the
+// memory - one ballot per 32 samples - and then walks the outputs 128 at a time, lane l owning the
+// samples t0 + l, t0 + 32 + l, t0 + 64 + l and t0 + 96 + l, adding the contributions of the events
+// that can reach that window in the order the dense sum visits them.  Skipped terms are products with zero, so the
 // result has the bits of the dense kernel's (taps must be finite: the launcher falls back to
 // the dense kernel otherwise; a row that holds a non-finite sample takes a predicated loop so
 // that the zero padding of the taps never meets an infinity).  Work is proportional to
@@ -28,7 +28,7 @@ namespace sb200 {
 
 namespace {
 
-constexpr int kPad = 96;                // zero taps in front of and behind the filter
+constexpr int kPad = 160;               // zero taps in front of and behind the filter
 constexpr int kProbeThreads = 256;
 constexpr int64_t kProbeSamples = 1 << 18;
 
@@ -159,7 +159,7 @@ __host__ __device__ inline size_t sparse_warp_bytes(int nwords, bool bits)
 // The next row of a warp is on its way while the current one is filtered: fp32 rows by
 // asynchronous copies into the staging buffer (16 bytes each when `vec4`: T % 4 == 0 and a
 // 16-byte aligned base), packed rows in up to four registers per lane.
-template <int DIR, bool BITS>
+template <int DIR, bool BITS, int NACC>
 __global__ void __launch_bounds__(256)
 fir_sparse_kernel(float *__restrict__ out, const void *__restrict__ in_, const float *__restrict__ filt,
                   int64_t rows, int T, int K, float Ts, float spike_value, bool vec4, const int *run_flag)
@@ -249,36 +249,40 @@ fir_sparse_kernel(float *__restrict__ out, const void *__restrict__ in_, const f
         __syncwarp();           // the list is complete and the staging buffer has been read
         if (row + stride < rows) fetch(row + stride);
 
-        // ---- outputs, 64 at a time: lane l owns t0 + l and t0 + 32 + l
+        // ---- outputs, 32 NACC at a time: lane l owns t0 + l, t0 + 32 + l, ...
         float *o = out + row * (int64_t)T;
-        for (int c = 0; c < nwords; c += 2) {
+        for (int c = 0; c < nwords; c += NACC) {
             int lo, hi;
             if (DIR < 0) {
                 lo = cnt[c - H > 0 ? c - H : 0];
-                hi = cnt[c + 2 < nwords ? c + 2 : nwords];
+                hi = cnt[c + NACC < nwords ? c + NACC : nwords];
             } else {
                 lo = cnt[c];
-                hi = cnt[c + 2 + H < nwords ? c + 2 + H : nwords];
+                hi = cnt[c + NACC + H < nwords ? c + NACC + H : nwords];
             }
-            float a0 = 0.0f, a1 = 0.0f;
+            float acc[NACC];
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
             if (bad == 0u) {
                 // tap index of this lane's first sample for an event at t: k = (32 c + lane) - t
-                // (conv) or t - (32 c + lane) (corr); the second sample is 32 taps further on
-                // (conv) or back (corr); taps outside the filter read as zero
+                // (conv) or t - (32 c + lane) (corr); its sample j is 32 j taps further on (conv)
+                // or back (corr); taps outside the filter read as zero
                 const float *wb = wl + (DIR < 0 ? 32 * c : -32 * c);
                 if (DIR < 0) {
 #pragma unroll 2
                     for (int i = hi - 1; i >= lo; --i) {
                         const Event e = list[i];
-                        a0 = fmaf(e.x, wb[-e.t], a0);
-                        a1 = fmaf(e.x, wb[32 - e.t], a1);
+                        const float *we = wb - e.t;
+#pragma unroll
+                        for (int j = 0; j < NACC; ++j) acc[j] = fmaf(e.x, we[32 * j], acc[j]);
                     }
                 } else {
 #pragma unroll 2
                     for (int i = lo; i < hi; ++i) {
                         const Event e = list[i];
-                        a0 = fmaf(e.x, wb[e.t], a0);
-                        a1 = fmaf(e.x, wb[e.t - 32], a1);
+                        const float *we = wb + e.t;
+#pragma unroll
+                        for (int j = 0; j < NACC; ++j) acc[j] = fmaf(e.x, we[-32 * j], acc[j]);
                     }
                 }
             } else {
@@ -287,20 +291,23 @@ fir_sparse_kernel(float *__restrict__ out, const void *__restrict__ in_, const f
                 for (int n = 0; n < hi - lo; ++n) {
                     const Event e = list[DIR < 0 ? hi - 1 - n : lo + n];
                     const int k0 = DIR < 0 ? t0 - e.t : e.t - t0;
-                    const int k1 = DIR < 0 ? k0 + 32 : k0 - 32;
-                    if ((unsigned)k0 < (unsigned)K) a0 = fmaf(e.x, wp[kPad + k0], a0);
-                    if ((unsigned)k1 < (unsigned)K) a1 = fmaf(e.x, wp[kPad + k1], a1);
+#pragma unroll
+                    for (int j = 0; j < NACC; ++j) {
+                        const int k = DIR < 0 ? k0 + 32 * j : k0 - 32 * j;
+                        if ((unsigned)k < (unsigned)K) acc[j] = fmaf(e.x, wp[kPad + k], acc[j]);
+                    }
                 }
             }
             const int t0 = 32 * c + lane;
-            if (t0 < T) o[t0] = a0 * Ts;
-            if (t0 + 32 < T) o[t0 + 32] = a1 * Ts;
+#pragma unroll
+            for (int j = 0; j < NACC; ++j)
+                if (t0 + 32 * j < T) o[t0 + 32 * j] = acc[j] * Ts;
         }
         __syncwarp();           // the list is rebuilt for the next row
     }
 }
 
-template <int DIR, bool BITS>
+template <int DIR, bool BITS, int NACC>
 int launch_sparse(float *out, const void *in, const float *filt, int64_t rows, int64_t T, int64_t K, float Ts,
                   float spike_value, const int *run_flag, cudaStream_t stream)
 {
@@ -311,7 +318,7 @@ int launch_sparse(float *out, const void *in, const float *filt, int64_t rows, i
     int nwarps = 8;
     while (nwarps > 1 && taps + nwarps * per_warp > 100 * 1024) nwarps >>= 1;
     const size_t smem = taps + nwarps * per_warp;
-    auto kern = fir_sparse_kernel<DIR, BITS>;
+    auto kern = fir_sparse_kernel<DIR, BITS, NACC>;
     int rc = reserve_dynamic_smem((const void *)kern, smem);
     if (rc) return rc;
     // a persistent grid: exactly the CTAs that are resident at once
@@ -362,9 +369,9 @@ int fir_sparse_probe(const void *in, int64_t rows, int64_t T, bool bits, const f
 int fir_sparse_launch(int dir, bool bits, float *out, const void *in, const float *filt, int64_t rows, int64_t T,
                       int64_t K, float Ts, float spike_value, const int *run_flag, cudaStream_t stream)
 {
-    if (bits) return launch_sparse<-1, true>(out, in, filt, rows, T, K, Ts, spike_value, run_flag, stream);
-    if (dir < 0) return launch_sparse<-1, false>(out, in, filt, rows, T, K, Ts, 0.0f, run_flag, stream);
-    return launch_sparse<1, false>(out, in, filt, rows, T, K, Ts, 0.0f, run_flag, stream);
+    if (bits) return launch_sparse<-1, true, 4>(out, in, filt, rows, T, K, Ts, spike_value, run_flag, stream);
+    if (dir < 0) return launch_sparse<-1, false, 4>(out, in, filt, rows, T, K, Ts, 0.0f, run_flag, stream);
+    return launch_sparse<1, false, 4>(out, in, filt, rows, T, K, Ts, 0.0f, run_flag, stream);
 }
 
 }  // namespace sb200
