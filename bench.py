@@ -62,7 +62,8 @@ FMA_LANES = 148 * 128 * 2            # fp32 flops per clock of the whole GPU (14
 
 # algorithmic bytes per neuron-timestep of each operator (reads + writes of fp32 tensors)
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12, "spikeGradShift": 12,
-             "getSpikesDelayed": 12, "delayGrad": 8, "loihi": 16, "loihiDelayed": 12, "spikeGradCorr": 12}
+             "getSpikesDelayed": 12, "delayGrad": 8, "loihi": 16, "loihiDelayed": 12,
+             "getSpikesPacked": 8.125, "convPacked": 4.125}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count) on launches too large for L2; see the summaries under profiles/.
 NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
@@ -73,7 +74,7 @@ NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "srm_get_spikes_tma_kernel":
 # conv inputs of at least this many samples are probed on the device and go to the event-driven
 # kernel when at most SPARSE_DENSITY of the sampled samples are non-zero (csrc/fir.cu, fir_sparse.cuh)
 PROBE_MIN_ELEMENTS = 1 << 25
-SPARSE_DENSITY = 61 / 1024
+SPARSE_DENSITY = {"conv": 61 / 1024, "convPacked": 92 / 1024}
 
 
 def conv_is_probed(el, T, taps):
@@ -84,8 +85,9 @@ def kernel_of(op, T):
     """Name of the kernel an operator launches for 16-byte aligned fp32 tensors of row length T
     (conv on a mostly-zero input: fir_sparse_kernel instead, see conv_is_probed)."""
     quad = T % 4 == 0
-    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "spikeGradCorr": "fir_flow_kernel",
+    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "convPacked": "fir_flow_kernel",
             "getSpikes": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
+            "getSpikesPacked": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "getSpikesDelayed": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "shift": "shift_vec4_kernel" if quad else "shift_flat4_kernel",
             "spikeGrad": "spike_grad_vec4_kernel", "spikeGradShift": "spike_grad_shift_rows_kernel",
@@ -161,7 +163,12 @@ class OurOps:
         self.fused = fused
         for name in ("conv", "corr", "getSpikes", "shift", "spikeGrad", "delayGrad", "getSpikesDelayed", "spikeGradShift"):
             setattr(self, name, getattr(self.sc, name))
-        self.spikeGradCorr = getattr(self.sc, "spikeGradCorr", None)
+        # spikes that only feed the next layer's psp stay bit-packed (spike(W(psp(.))) networks)
+        self.packed_spikes = fused
+        self.packSpikes, self.getSpikesPacked = self.sc.packSpikes, self.sc.getSpikesPacked
+
+    def convPacked(self, bits, T, filt, Ts):
+        return self.sc.convPacked(bits, T, filt, Ts, 1.0 / Ts)
 
     def loihi(self, w, wgtExp, theta, iDecay, vDecay, refDelay):
         return tuple(self.lc.getSpikes(w, wgtExp, theta, iDecay, vDecay, refDelay))
@@ -295,8 +302,16 @@ class Workload:
                 outs += [u, b, c]
             elif L["kind"] == "spike_w":
                 srm, ref = self.kernels
-                p = run("conv", i, L["rows_in"], lambda: ops.conv(L["s_in"], srm, Ts))
-                s = run("getSpikes", i, rows, lambda: ops.getSpikes(L["u"], ref, theta, Ts))
+                if getattr(ops, "packed_spikes", False) and "s_bits" in L:
+                    # the spikes of a layer are only read by the next layer's psp: they cross as bits
+                    p = run("convPacked", i, L["rows_in"], lambda: ops.convPacked(L["s_bits"], T, srm, Ts))
+                    if i + 1 < len(self.layers):
+                        s = run("getSpikesPacked", i, rows, lambda: ops.getSpikesPacked(L["u"], ref, theta, Ts))
+                    else:               # the loss reads the output spikes as fp32
+                        s = run("getSpikes", i, rows, lambda: ops.getSpikes(L["u"], ref, theta, Ts))
+                else:
+                    p = run("conv", i, L["rows_in"], lambda: ops.conv(L["s_in"], srm, Ts))
+                    s = run("getSpikes", i, rows, lambda: ops.getSpikes(L["u"], ref, theta, Ts))
                 gu = run("spikeGrad", i, rows, lambda: ops.spikeGrad(L["g_s"], L["u"], theta, tau, scale))
                 outs += [p, s, gu]
                 if L["g_p"] is not None:         # the network input needs no gradient
@@ -328,14 +343,15 @@ class Workload:
         calls = []
         dry = Dry()
         dry.fused = fused
+        dry.packed_spikes = fused
         for name in ("conv", "corr", "getSpikes", "shift", "spikeGrad", "delayGrad", "getSpikesDelayed",
-                     "spikeGradShift", "loihi", "loihiDelayed"):
+                     "spikeGradShift", "loihi", "loihiDelayed", "convPacked", "getSpikesPacked"):
             setattr(dry, name, (lambda *a, **k: (None, None, None)) if name == "loihi" else
                     ((lambda *a, **k: (None, None)) if name == "loihiDelayed" else (lambda *a, **k: None)))
 
         def run(op, layer, rows, fn):
             taps = 0
-            if op in ("conv", "corr"):
+            if op in ("conv", "corr", "convPacked"):
                 taps = int(self.kernels[0].numel())
             calls.append((op, layer, rows * self.T, taps))
             return fn()
@@ -353,14 +369,14 @@ class Workload:
     def launches_per_step(self, fused):
         """Kernels launched per step: one per operator call, three for a conv that is probed (the
         probe, the event-driven kernel and the dense kernel, one of the two returning at once)."""
-        return sum(3 if (op == "conv" and conv_is_probed(el, self.T, taps)) else 1
+        return sum(3 if (op in SPARSE_DENSITY and conv_is_probed(el, self.T, taps)) else 1
                    for op, _, el, taps in self.op_list(fused))
 
     def sparse_convs(self, fused):
         """Layers whose conv goes to the event-driven kernel, with the density of its input."""
         return {layer: self.conv_density[layer] for op, layer, el, taps in self.op_list(fused)
-                if op == "conv" and conv_is_probed(el, self.T, taps)
-                and self.conv_density.get(layer, 1.0) <= SPARSE_DENSITY}
+                if op in SPARSE_DENSITY and conv_is_probed(el, self.T, taps)
+                and self.conv_density.get(layer, 1.0) <= SPARSE_DENSITY[op]}
 
     def chain_bound_ms(self, fused, peak_gbs, sm_mhz):
         """Sum over the step's launches of max(algorithmic bytes / HBM peak, flops / fp32 FMA peak);
@@ -370,7 +386,7 @@ class Workload:
         sparse = self.sparse_convs(fused)
         total = 0.0
         for op, layer, el, taps in self.op_list(fused):
-            flops = 2.0 * taps * el * (sparse[layer] if (op == "conv" and layer in sparse) else 1.0)
+            flops = 2.0 * taps * el * (sparse[layer] if (op in SPARSE_DENSITY and layer in sparse) else 1.0)
             total += max(ALG_BYTES[op] * el / (peak_gbs * 1e9), flops / fma)
         return total * 1e3
 
@@ -503,6 +519,8 @@ def build_cnn(ops, device, rank, world, scaling, batch_override=None):
         u = u0.clone()
         sp = ops.getSpikes(u, ref, theta, Ts)
         layers.append(dict(kind="spike_w", s_in=s, rows_in=s.numel() // T, u0=u0, u=u, rows=u.numel() // T, W=W, p=p))
+        if getattr(ops, "packed_spikes", False):
+            layers[-1]["s_bits"] = ops.packSpikes(s)
         rates.append(float(sp.mean()))
         s = sp
     g = count_loss_grad(ops, s, label, srm, Ts, T)
@@ -777,7 +795,7 @@ def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
     sparse = wl.sparse_convs(True)
 
     def k_of(op, layer):
-        return "fir_sparse_kernel" if (op == "conv" and layer in sparse) else kernel_of(op, wl.T)
+        return "fir_sparse_kernel" if (op in SPARSE_DENSITY and layer in sparse) else kernel_of(op, wl.T)
     share = {}
     for (op, layer, rows), v in per_op.items():
         k = k_of(op, layer)
@@ -792,7 +810,7 @@ def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
     alg = ALG_BYTES[op] * el
     gbs = alg / (avg_ms * 1e-3) / 1e9
     tpe = NCU_TRAFFIC_PER_ELEMENT.get(dominant)
-    taps = int(wl.kernels[0].numel()) if op in ("conv", "corr") else 0
+    taps = int(wl.kernels[0].numel()) if op in ("conv", "corr", "convPacked") else 0
     fma_peak = FMA_LANES * (sm_mhz or 1965.0) * 1e6 / 1e12
     hbm = {"achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4)}
     out = {"kernel": dominant, "kernel_share_of_step": round(share[dominant] / total, 4),
@@ -860,7 +878,8 @@ def time_ours(args, rank, world, device):
                    "fusion": ("none: the reference's sequence of launches" if args.unfused else
                               "getSpikes+delay as one launch (SRM: getSpikesDelayed; Loihi: getSpikesDelayed without the "
                               "current) and shift back + surrogate gradient as one launch (spikeGradShift) wherever a delay "
-                              "follows the spikes; same results"),
+                              "follows the spikes; in spike(W(psp(.))) networks (config 3) the spikes of a layer cross to the "
+                              "next layer's psp bit-packed (getSpikesPacked, convPacked), the output layer's as fp32; same results"),
                    "neuron_timesteps_per_step_per_gpu": wl.units, "batch_per_gpu": wl.batch,
                    "l2": "flushed between steps (256 MiB write); in-place potentials restored between steps, untimed",
                    "spike_rates": [round(r, 4) for r in wl.rates],

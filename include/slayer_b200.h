@@ -339,7 +339,7 @@ int slayer_b200_set_srm_stages(int stages);
  *   0: never.
  *   1 (the default): conv and conv_packed inputs of at least 2^25 samples with rows of 64 .. 4096
  *      steps and at most 1024 taps are sampled by a probe kernel (corr, which filters gradients, is
- *      not); if at most 6 % (conv_packed: 20 %) of the sampled samples are non-zero
+ *      not); if at most 6 % (conv_packed: 9 %) of the sampled samples are non-zero
  *      (spike tensors) and every tap is finite, the event-driven kernel runs - a warp lists the
  *      non-zero samples of a row and adds their contributions to the outputs they reach, work in
  *      proportion to events x taps - otherwise the dense kernel.  The decision stays on the

@@ -786,10 +786,15 @@ __device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int lim
     return !__any_sync(0xffffffffu, !mbar_wait_bounded(bar, parity, limit));
 }
 
-template <int DIR, int V, int MINB>
+// PK: `in` points to bit-packed spikes (32-bit words, ceil(T / 32) per row, bit b of word w =
+// "sample 32 w + b is spike_value"); the warps expand their rows of a tile into the same fp32
+// tile the copies would have filled (a few word loads per row, most of them from L2), so the
+// arithmetic and the results are those of the fp32 input.  V then is the access width of `out`.
+template <int DIR, int V, int MINB, bool PK = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
-                int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status, const int *skip_flag)
+                int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status, const int *skip_flag,
+                float spike_value)
 {
     if (skip_flag != nullptr && *skip_flag != 0) return;      // the event-driven kernel has this call
     extern __shared__ __align__(16) float smem[];
@@ -823,6 +828,47 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
         const int64_t row0 = rb * kFirRows;
         const int64_t nrow = rows - row0;
         const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
+        if constexpr (PK) {
+            // tile position 4 * lane + 128 k holds samples g0 + that .. + 3: g0 is a multiple of
+            // four, so the four bits lie in one word; all loads of up to four rows first
+            constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
+            const unsigned *words = reinterpret_cast<const unsigned *>(in);
+            const int nwords = (T + 31) >> 5;
+            for (int r0 = warp; r0 < kFirRows; r0 += 4 * nwarps) {
+                unsigned wv[4][kChunks];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = r0 + i * nwarps;
+                    const bool row_ok = r < kFirRows && r < nrow;
+                    const unsigned *src = words + (row0 + (row_ok ? r : 0)) * (int64_t)nwords;
+#pragma unroll
+                    for (int k = 0; k < kChunks; ++k) {
+                        const int pcol = lane * 4 + 128 * k;
+                        const int gt = g0 + pcol;
+                        const bool ok = row_ok && pcol < WX && gt >= 0 && (gt >> 5) < nwords;
+                        wv[i][k] = ok ? __ldg(src + (gt >> 5)) : 0u;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = r0 + i * nwarps;
+                    if (r >= kFirRows) continue;
+#pragma unroll
+                    for (int k = 0; k < kChunks; ++k) {
+                        const int pcol = lane * 4 + 128 * k;
+                        if (pcol >= WX) continue;
+                        unsigned m = wv[i][k] >> ((g0 + pcol) & 31);
+                        const int left = T - (g0 + pcol);           // bits past the row end do not count
+                        if (left < 4) m &= left > 0 ? (1u << left) - 1u : 0u;
+                        *reinterpret_cast<float4 *>(xs + r * sh.SX + pcol) =
+                            make_float4((m & 1u) ? spike_value : 0.0f, (m & 2u) ? spike_value : 0.0f,
+                                        (m & 4u) ? spike_value : 0.0f, (m & 8u) ? spike_value : 0.0f);
+                    }
+                }
+            }
+            mbar_arrive(bars + buf);         // (release) this thread's part of the tile is in place
+            return;
+        }
         if constexpr (V == 4) {
             constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
             int goff[kChunks], nbytes[kChunks];          // source offset in the row; 16, 0 (zero fill) or -1 (no chunk)
@@ -1117,6 +1163,56 @@ static int launch_fir2(float *out, const float *in, const float *filt,
     return check_launch("fir (packed) kernel launch");
 }
 
+// The scalar tiled kernels (and, for filters too long to tile, the thread-per-output kernel).
+// PK: `in` points to bit-packed spikes; only the flow kernel expands them, so `taken` comes back
+// false when the shape or the missing status word rules that kernel out.
+template <int DIR, bool PK>
+static int launch_fir_tiled(float *out, const float *in, const float *filt, int64_t rows, int64_t T, int64_t Keff,
+                            float Ts, cudaStream_t stream, const int *skip_flag, float spike_value, bool &taken)
+{
+    taken = true;
+    FirShape sh;
+    const bool tiled = fir_shape(rows, T, Keff, sh);
+    const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
+    if (!tiled) {
+        if (PK) { taken = false; return SLAYER_B200_OK; }
+        const int64_t n = rows * T;
+        int64_t g = ceil_div(n, 256);
+        const int64_t cap = (int64_t)sm_count() * 32;
+        if (g > cap) g = cap;
+        fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts, skip_flag);
+        return check_launch("fir (long filter) kernel launch");
+    }
+    const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
+    const int vw = PK ? tile_vec_width(T, {out}) : tile_vec_width(T, {out, in});
+    int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    int64_t grid = ctas_per_sm * (int64_t)sm_count();
+    if (grid > ntiles) grid = ntiles;
+    int *status = (PK || g_fir_flow.load() != 0) ? device_status_word() : nullptr;
+    if (status) {
+        const bool roomy = (PK || g_fir_flow.load() == 2) && sh.nwarps <= 8;
+        auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1, PK> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1, PK> : fir_flow_kernel<DIR, 1, 1, PK>))
+                          : (vw == 4 ? fir_flow_kernel<DIR, 4, 2, PK> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2, PK> : fir_flow_kernel<DIR, 1, 2, PK>));
+        int rc = reserve_dynamic_smem((const void *)kern, smem);
+        if (rc) return rc;
+        kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status, skip_flag,
+                                                               spike_value);
+        return check_launch("fir (flow) kernel launch");
+    }
+    if constexpr (PK) {
+        taken = false;
+        return SLAYER_B200_OK;
+    } else {
+        auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
+        int rc = reserve_dynamic_smem((const void *)kern, smem);
+        if (rc) return rc;
+        kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, skip_flag);
+        return check_launch("fir kernel launch");
+    }
+}
+
 template <int DIR>
 static int launch_fir(float *out, const float *in, const float *filt,
                       int64_t rows, int64_t T, int64_t K, float Ts, cudaStream_t stream)
@@ -1150,39 +1246,8 @@ static int launch_fir(float *out, const float *in, const float *filt,
         const int rc = launch_fir2<DIR>(out, in, filt, rows, T, Keff, Ts, stream, taken, 0.0f, skip_flag);
         if (taken) return rc;
     }
-    FirShape sh;
-    const bool tiled = fir_shape(rows, T, Keff, sh);
-    const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
-    if (!tiled) {
-        const int64_t n = rows * T;
-        int64_t g = ceil_div(n, 256);
-        const int64_t cap = (int64_t)sm_count() * 32;
-        if (g > cap) g = cap;
-        fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts, skip_flag);
-        return check_launch("fir (long filter) kernel launch");
-    }
-    const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
-    const int vw = tile_vec_width(T, {out, in});
-    int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
-    if (ctas_per_sm > 8) ctas_per_sm = 8;
-    if (ctas_per_sm < 1) ctas_per_sm = 1;
-    int64_t grid = ctas_per_sm * (int64_t)sm_count();
-    if (grid > ntiles) grid = ntiles;
-    int *status = g_fir_flow.load() != 0 ? device_status_word() : nullptr;
-    if (status) {
-        const bool roomy = g_fir_flow.load() == 2 && sh.nwarps <= 8;
-        auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1> : fir_flow_kernel<DIR, 1, 1>))
-                          : (vw == 4 ? fir_flow_kernel<DIR, 4, 2> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2> : fir_flow_kernel<DIR, 1, 2>));
-        int rc = reserve_dynamic_smem((const void *)kern, smem);
-        if (rc) return rc;
-        kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status, skip_flag);
-        return check_launch("fir (flow) kernel launch");
-    }
-    auto kern = vw == 4 ? fir_kernel<DIR, 4> : (vw == 2 ? fir_kernel<DIR, 2> : fir_kernel<DIR, 1>);
-    int rc = reserve_dynamic_smem((const void *)kern, smem);
-    if (rc) return rc;
-    kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, skip_flag);
-    return check_launch("fir kernel launch");
+    bool taken = false;
+    return launch_fir_tiled<DIR, false>(out, in, filt, rows, T, Keff, Ts, stream, skip_flag, 0.0f, taken);
 }
 
 static int check_fir_args(const char *name, float *out, const float *in, const float *filt,
@@ -1240,7 +1305,7 @@ extern "C" int slayer_b200_conv_packed(float *out, const uint32_t *bits, const f
     const int *skip_flag = nullptr;
     const int zmode = g_fir_skip_zeros.load();
     FirShape probe_shape;
-    const bool dense_ok = fir2_shape(rows, T, Keff, probe_shape, kFir2MaxSamples);
+    const bool dense_ok = fir_shape(rows, T, Keff, probe_shape) || fir2_shape(rows, T, Keff, probe_shape, kFir2MaxSamples);
     if (zmode != 0 && fir_sparse_eligible(rows, T, Keff) && fabsf(spike_value) <= FLT_MAX) {
         // (filters too long for the tiled kernel: the event-driven one, whatever the density)
         if (zmode == 2 || !dense_ok) return fir_sparse_launch(-1, true, out, bits, filter, rows, T, Keff, Ts, spike_value, nullptr, (cudaStream_t)stream);
@@ -1253,7 +1318,14 @@ extern "C" int slayer_b200_conv_packed(float *out, const uint32_t *bits, const f
             }
         }
     }
+    // dense input: the scalar kernel expanding the bits as it fills its tiles; the packed two-row
+    // kernel only where slayer_b200_set_fir_packed asks for it or the scalar one cannot take the shape
     bool taken = false;
+    if (g_fir_packed.load() == 0) {
+        rc = launch_fir_tiled<-1, true>(out, reinterpret_cast<const float *>(bits), filter, rows, T, Keff, Ts,
+                                        (cudaStream_t)stream, skip_flag, spike_value, taken);
+        if (taken) return rc;
+    }
     rc = launch_fir2<-1, true>(out, reinterpret_cast<const float *>(bits), filter, rows, T, Keff, Ts,
                                (cudaStream_t)stream, taken, spike_value, skip_flag);
     if (!taken) {

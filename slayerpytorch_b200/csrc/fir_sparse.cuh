@@ -9,10 +9,10 @@ namespace sb200 {
 constexpr int64_t kFirSparseMaxT = 4096;        // 8 bytes of event list per sample and warp
 constexpr int64_t kFirSparseMaxTaps = 1024;
 // The event-driven kernel is chosen when at most this many of 1024 sampled input samples are
-// non-zero: the measured cross-over against the dense kernel it replaces, for 77 taps - 6 %
-// against the scalar kernel on fp32 input, 20 % against the packed-input tiled kernel.
+// non-zero: the measured cross-over against the dense scalar kernel, for 77 taps - 6 % on fp32
+// input, 9 % on packed input (whose event list comes cheaper).
 constexpr int kFirSparseMaxPer1024 = 61;
-constexpr int kFirSparseMaxPer1024Bits = 205;
+constexpr int kFirSparseMaxPer1024Bits = 92;
 
 // Shapes the event-driven kernel takes.
 bool fir_sparse_eligible(int64_t rows, int64_t T, int64_t K);

@@ -105,6 +105,28 @@ def test_conv_packed_equals_conv_of_the_fp32_view(density, T, K, zeros):
     assert capi.device_status() == 0
 
 
+@pytest.mark.parametrize("density", [0.05, 0.5])
+@pytest.mark.parametrize("T,K", [(300, 77), (301, 77), (1450, 110)])
+def test_conv_packed_two_row_kernel(density, T, K):
+    """Dense packed input goes to the scalar kernel, which expands the bits while it fills its
+    tiles; slayer_b200_set_fir_packed(1) sends it to the two-row kernel instead.  Same bits."""
+    from slayerpytorch_b200 import capi
+    rng = np.random.RandomState(int(density * 1000) + T + K + 1)
+    s = (rng.rand(3000, T) < density).astype(np.float32)
+    f = rng.randn(K).astype(np.float32)
+    bits = G.c_pack(G.dev(s))
+    want = co.conv(s * np.float32(2.0), f, 0.5)
+    before = capi.set_fir_skip_zeros(0), capi.set_fir_packed(0)
+    try:
+        for two_row in (0, 1):
+            capi.set_fir_packed(two_row)
+            np.testing.assert_array_equal(G.host(G.c_conv_packed(bits, T, G.dev(f), 2.0, 0.5)), want)
+    finally:
+        capi.set_fir_skip_zeros(before[0])
+        capi.set_fir_packed(before[1])
+    assert capi.device_status() == 0
+
+
 def test_conv_packed_very_long_filter():
     sc, _ = slayerpytorch_b200.load_ops()
     rng = np.random.RandomState(4)
