@@ -43,6 +43,7 @@ constexpr int kFirWin = kFirSeg + 4;           // samples one group of four taps
 constexpr int kFirRing = kFirWin + 4;          // register ring: the window plus the quad being loaded
 constexpr int kFirPhases = kFirRing / 4;       // 6
 constexpr int kFirMaxWarps = 16;
+constexpr int kFirStageWords = 16;      // packed input: words of one row that a tile (at most 432 samples) can touch
 constexpr int kFirTileWordsPerRow = 432;  // 2 buffers x 32 rows x 432 words = 108 KB: two CTAs per SM
 
 // 128-bit load from a 32-bit shared-memory address (explicit state space: the address
@@ -787,9 +788,10 @@ __device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int lim
 }
 
 // PK: `in` points to bit-packed spikes (32-bit words, ceil(T / 32) per row, bit b of word w =
-// "sample 32 w + b is spike_value"); the warps expand their rows of a tile into the same fp32
-// tile the copies would have filled (a few word loads per row, most of them from L2), so the
-// arithmetic and the results are those of the fp32 input.  V then is the access width of `out`.
+// "sample 32 w + b is spike_value"); the words a tile needs are copied into a small staging slot
+// two tiles ahead and the warps expand their rows into the same fp32 tile the copies would have
+// filled, so the arithmetic and the results are those of the fp32 input.  V then is the access
+// width of `out`.
 template <int DIR, int V, int MINB, bool PK = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
@@ -820,6 +822,28 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
     }
     __syncthreads();
 
+    // PK: two staging slots of [32 rows x kFirStageWords] words behind the tiles.  A warp copies
+    // (and later expands) the words of its own rows only, so its own cp.async groups order them.
+    unsigned *stage = reinterpret_cast<unsigned *>(xbuf + 2 * tile_words);
+    auto stage_words = [&](int slot, int64_t tile) {
+        if (tile < ntiles) {
+            const int64_t rb = tile / sh.ttiles;
+            const int t0 = (int)(tile - rb * sh.ttiles) * Tt;
+            const int64_t row0 = rb * kFirRows;
+            const int64_t nrow = rows - row0;
+            const int w0 = (DIR < 0 ? t0 - sh.halo : t0) >> 5;
+            const unsigned *words = reinterpret_cast<const unsigned *>(in);
+            const int nwords = (T + 31) >> 5;
+            if (lane < kFirStageWords) {
+                for (int r = warp; r < kFirRows; r += nwarps) {
+                    const bool ok = r < nrow && w0 + lane >= 0 && w0 + lane < nwords;
+                    cp_async<4>(stage + (slot * kFirRows + r) * kFirStageWords + lane,
+                                ok ? words + (row0 + r) * (int64_t)nwords + (w0 + lane) : words, ok);
+                }
+            }
+        }
+        cp_async_commit();
+    };
     const unsigned xbuf_saddr = (unsigned)__cvta_generic_to_shared(xbuf);
     auto fill = [&](int buf, int64_t tile) {
         float *xs = xbuf + buf * tile_words;
@@ -829,43 +853,30 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
         const int64_t nrow = rows - row0;
         const int g0 = DIR < 0 ? t0 - sh.halo : t0;      // global time of tile position 0
         if constexpr (PK) {
-            // tile position 4 * lane + 128 k holds samples g0 + that .. + 3: g0 is a multiple of
-            // four, so the four bits lie in one word; all loads of up to four rows first
+            // The words of this tile were copied into staging slot `buf` two fills ago (see
+            // stage_words below): expand them.  Tile position 4 * lane + 128 k holds samples
+            // g0 + that .. + 3; g0 is a multiple of four, so the four bits lie in one word.
             constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
-            const unsigned *words = reinterpret_cast<const unsigned *>(in);
-            const int nwords = (T + 31) >> 5;
-            for (int r0 = warp; r0 < kFirRows; r0 += 4 * nwarps) {
-                unsigned wv[4][kChunks];
+            cp_async_wait<1>();              // all but the copies for the tile after this one
+            __syncwarp();
+            const unsigned *st = stage + buf * (kFirRows * kFirStageWords);
+            const int w0 = g0 >> 5;          // (arithmetic shift: g0 may be negative)
+            for (int r = warp; r < kFirRows; r += nwarps) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = r0 + i * nwarps;
-                    const bool row_ok = r < kFirRows && r < nrow;
-                    const unsigned *src = words + (row0 + (row_ok ? r : 0)) * (int64_t)nwords;
-#pragma unroll
-                    for (int k = 0; k < kChunks; ++k) {
-                        const int pcol = lane * 4 + 128 * k;
-                        const int gt = g0 + pcol;
-                        const bool ok = row_ok && pcol < WX && gt >= 0 && (gt >> 5) < nwords;
-                        wv[i][k] = ok ? __ldg(src + (gt >> 5)) : 0u;
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = r0 + i * nwarps;
-                    if (r >= kFirRows) continue;
-#pragma unroll
-                    for (int k = 0; k < kChunks; ++k) {
-                        const int pcol = lane * 4 + 128 * k;
-                        if (pcol >= WX) continue;
-                        unsigned m = wv[i][k] >> ((g0 + pcol) & 31);
-                        const int left = T - (g0 + pcol);           // bits past the row end do not count
-                        if (left < 4) m &= left > 0 ? (1u << left) - 1u : 0u;
-                        *reinterpret_cast<float4 *>(xs + r * sh.SX + pcol) =
-                            make_float4((m & 1u) ? spike_value : 0.0f, (m & 2u) ? spike_value : 0.0f,
-                                        (m & 4u) ? spike_value : 0.0f, (m & 8u) ? spike_value : 0.0f);
-                    }
+                for (int k = 0; k < kChunks; ++k) {
+                    const int pcol = lane * 4 + 128 * k;
+                    if (pcol >= WX) continue;
+                    const int gt = g0 + pcol;
+                    unsigned m = st[r * kFirStageWords + ((gt >> 5) - w0)] >> (gt & 31);
+                    const int left = T - gt;                 // bits past the row end do not count
+                    if (left < 4) m &= left > 0 ? (1u << left) - 1u : 0u;
+                    *reinterpret_cast<float4 *>(xs + r * sh.SX + pcol) =
+                        make_float4((m & 1u) ? spike_value : 0.0f, (m & 2u) ? spike_value : 0.0f,
+                                    (m & 4u) ? spike_value : 0.0f, (m & 8u) ? spike_value : 0.0f);
                 }
             }
+            __syncwarp();                    // the slot has been read: it takes the words of the tile two further on
+            stage_words(buf, tile + 2 * (int64_t)gridDim.x);
             mbar_arrive(bars + buf);         // (release) this thread's part of the tile is in place
             return;
         }
@@ -914,6 +925,10 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
     // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
     const int64_t first = blockIdx.x;
     const int n = first < ntiles ? (int)((ntiles - first + gridDim.x - 1) / gridDim.x) : 0;
+    if constexpr (PK) {
+        stage_words(0, first);
+        stage_words(1, first + gridDim.x);
+    }
     if (n > 0) fill(0, first);
     if (n > 1) fill(1, first + gridDim.x);
     bool gave_up = false;
@@ -1040,10 +1055,10 @@ static inline int pad_stride(int w)       // smallest s >= w with s = 4 (mod 8)
 }
 
 // Tile shape for rows of length T and K taps; returns false if the filter is too long to tile.
-static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh)
+static bool fir_shape(int64_t rows, int64_t T, int64_t K, FirShape &sh, int max_words = kFirTileWordsPerRow)
 {
     sh.halo = (int)(((K + 3) & ~3LL) + 8);     // taps rounded up plus two quads of look-ahead
-    const int room = kFirTileWordsPerRow - 4 - sh.halo;       // words left for outputs (4 = stride padding)
+    const int room = max_words - 4 - sh.halo;                 // words left for outputs (4 = stride padding)
     const int nseg_max = room / kFirSeg;
     if (nseg_max < 1) return false;
     const int64_t segs = ceil_div(T, kFirSeg);
@@ -1172,7 +1187,9 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
 {
     taken = true;
     FirShape sh;
-    const bool tiled = fir_shape(rows, T, Keff, sh);
+    // (packed input: the tiles give up 16 words per row to the two staging slots, so that two
+    // CTAs still fit an SM)
+    const bool tiled = fir_shape(rows, T, Keff, sh, PK ? kFirTileWordsPerRow - kFirStageWords : kFirTileWordsPerRow);
     const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
     if (!tiled) {
         if (PK) { taken = false; return SLAYER_B200_OK; }
@@ -1183,7 +1200,8 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
         fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts, skip_flag);
         return check_launch("fir (long filter) kernel launch");
     }
-    const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX);
+    const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX +
+                                         (PK ? 2 * (size_t)kFirRows * kFirStageWords : 0));
     const int vw = PK ? tile_vec_width(T, {out}) : tile_vec_width(T, {out, in});
     int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
     if (ctas_per_sm > 8) ctas_per_sm = 8;
@@ -1305,7 +1323,8 @@ extern "C" int slayer_b200_conv_packed(float *out, const uint32_t *bits, const f
     const int *skip_flag = nullptr;
     const int zmode = g_fir_skip_zeros.load();
     FirShape probe_shape;
-    const bool dense_ok = fir_shape(rows, T, Keff, probe_shape) || fir2_shape(rows, T, Keff, probe_shape, kFir2MaxSamples);
+    const bool dense_ok = fir_shape(rows, T, Keff, probe_shape, kFirTileWordsPerRow - kFirStageWords) ||
+                          fir2_shape(rows, T, Keff, probe_shape, kFir2MaxSamples);
     if (zmode != 0 && fir_sparse_eligible(rows, T, Keff) && fabsf(spike_value) <= FLT_MAX) {
         // (filters too long for the tiled kernel: the event-driven one, whatever the density)
         if (zmode == 2 || !dense_ok) return fir_sparse_launch(-1, true, out, bits, filter, rows, T, Keff, Ts, spike_value, nullptr, (cudaStream_t)stream);
