@@ -63,7 +63,7 @@ FMA_LANES = 148 * 128 * 2            # fp32 flops per clock of the whole GPU (14
 # algorithmic bytes per neuron-timestep of each operator (reads + writes of fp32 tensors)
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12, "spikeGradShift": 12,
              "getSpikesDelayed": 12, "delayGrad": 8, "loihi": 16, "loihiDelayed": 12,
-             "getSpikesPacked": 8.125, "convPacked": 4.125}
+             "getSpikesPacked": 8.125, "convPacked": 4.125, "corrSpikeGrad": 12}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count) on launches too large for L2; see the summaries under profiles/.
 NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
@@ -85,7 +85,7 @@ def kernel_of(op, T):
     """Name of the kernel an operator launches for 16-byte aligned fp32 tensors of row length T
     (conv on a mostly-zero input: fir_sparse_kernel instead, see conv_is_probed)."""
     quad = T % 4 == 0
-    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "convPacked": "fir_flow_kernel",
+    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "convPacked": "fir_flow_kernel", "corrSpikeGrad": "fir_flow_kernel",
             "getSpikes": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "getSpikesPacked": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "getSpikesDelayed": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
@@ -166,6 +166,9 @@ class OurOps:
         # spikes that only feed the next layer's psp stay bit-packed (spike(W(psp(.))) networks)
         self.packed_spikes = fused
         self.packSpikes, self.getSpikesPacked = self.sc.packSpikes, self.sc.getSpikesPacked
+        # ... and the backward of psp(spike(.)) is one launch: corr, then the surrogate gradient
+        self.corr_spike_grad = fused
+        self.corrSpikeGrad = self.sc.corrSpikeGrad
 
     def convPacked(self, bits, T, filt, Ts):
         return self.sc.convPacked(bits, T, filt, Ts, 1.0 / Ts)
@@ -312,10 +315,20 @@ class Workload:
                 else:
                     p = run("conv", i, L["rows_in"], lambda: ops.conv(L["s_in"], srm, Ts))
                     s = run("getSpikes", i, rows, lambda: ops.getSpikes(L["u"], ref, theta, Ts))
-                gu = run("spikeGrad", i, rows, lambda: ops.spikeGrad(L["g_s"], L["u"], theta, tau, scale))
-                outs += [p, s, gu]
+                outs += [p, s]
+                corr_rho = getattr(ops, "corr_spike_grad", False)
+                if not (corr_rho and i + 1 < len(self.layers)):
+                    # (fused: the surrogate gradient of this layer rides on the corr of the next one, below)
+                    outs.append(run("spikeGrad", i, rows, lambda: ops.spikeGrad(L["g_s"], L["u"], theta, tau, scale)))
                 if L["g_p"] is not None:         # the network input needs no gradient
-                    outs.append(run("corr", i, L["rows_in"], lambda: ops.corr(L["g_p"], srm, Ts)))
+                    if corr_rho:
+                        # psp backward of this layer, then spike backward of the layer that produced
+                        # its input spikes: one launch
+                        below = self.layers[i - 1]
+                        outs.append(run("corrSpikeGrad", i, L["rows_in"],
+                                        lambda: ops.corrSpikeGrad(L["g_p"], srm, below["u"], theta, tau, scale, Ts)))
+                    else:
+                        outs.append(run("corr", i, L["rows_in"], lambda: ops.corr(L["g_p"], srm, Ts)))
             else:
                 k = self.kernels[0]
                 if ops.fused:
@@ -344,14 +357,15 @@ class Workload:
         dry = Dry()
         dry.fused = fused
         dry.packed_spikes = fused
+        dry.corr_spike_grad = fused
         for name in ("conv", "corr", "getSpikes", "shift", "spikeGrad", "delayGrad", "getSpikesDelayed",
-                     "spikeGradShift", "loihi", "loihiDelayed", "convPacked", "getSpikesPacked"):
+                     "spikeGradShift", "loihi", "loihiDelayed", "convPacked", "getSpikesPacked", "corrSpikeGrad"):
             setattr(dry, name, (lambda *a, **k: (None, None, None)) if name == "loihi" else
                     ((lambda *a, **k: (None, None)) if name == "loihiDelayed" else (lambda *a, **k: None)))
 
         def run(op, layer, rows, fn):
             taps = 0
-            if op in ("conv", "corr", "convPacked"):
+            if op in ("conv", "corr", "convPacked", "corrSpikeGrad"):
                 taps = int(self.kernels[0].numel())
             calls.append((op, layer, rows * self.T, taps))
             return fn()
@@ -810,7 +824,7 @@ def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
     alg = ALG_BYTES[op] * el
     gbs = alg / (avg_ms * 1e-3) / 1e9
     tpe = NCU_TRAFFIC_PER_ELEMENT.get(dominant)
-    taps = int(wl.kernels[0].numel()) if op in ("conv", "corr", "convPacked") else 0
+    taps = int(wl.kernels[0].numel()) if op in ("conv", "corr", "convPacked", "corrSpikeGrad") else 0
     fma_peak = FMA_LANES * (sm_mhz or 1965.0) * 1e6 / 1e12
     hbm = {"achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4)}
     out = {"kernel": dominant, "kernel_share_of_step": round(share[dominant] / total, 4),
@@ -879,7 +893,8 @@ def time_ours(args, rank, world, device):
                               "getSpikes+delay as one launch (SRM: getSpikesDelayed; Loihi: getSpikesDelayed without the "
                               "current) and shift back + surrogate gradient as one launch (spikeGradShift) wherever a delay "
                               "follows the spikes; in spike(W(psp(.))) networks (config 3) the spikes of a layer cross to the "
-                              "next layer's psp bit-packed (getSpikesPacked, convPacked), the output layer's as fp32; same results"),
+                              "next layer's psp bit-packed (getSpikesPacked, convPacked), the output layer's as fp32, and the backward of "
+                              "psp(spike(.)) - corr, then the surrogate gradient of the layer below - is one launch (corrSpikeGrad); same results"),
                    "neuron_timesteps_per_step_per_gpu": wl.units, "batch_per_gpu": wl.batch,
                    "l2": "flushed between steps (256 MiB write); in-place potentials restored between steps, untimed",
                    "spike_rates": [round(r, 4) for r in wl.rates],

@@ -53,6 +53,21 @@ int slayer_b200_corr(float *out, const float *in, const float *filter,
                      int64_t rows, int64_t T, int64_t K, float Ts, void *stream);
 
 /*
+ * slayer_b200_corr followed by slayer_b200_spike_grad on its result, in one pass:
+ *   out[r,t] = (Ts * sum_{i<K, t+i<T} in[r,t+i] * filter[i]) * scale/tau * exp(-|u[r,t] - theta| / tau),
+ * the backward step of "spike, then psp": pspFunction.backward / _pspFunction.backward (corr,
+ * src/slayer.py:892) and then spikeFunction.backward (the tensor expression at src/slayer.py:862)
+ * of the layer that produced the spikes, without the intermediate gradient tensor (12 instead of
+ * 20 bytes per element).  The filtered value is rounded to fp32 before it is multiplied, so the
+ * result equals the two calls', except that intermediate values of the surrogate below 1.2e-38
+ * are flushed to zero (the filter's translation unit flushes denormals, the separate pass does
+ * not).  `out` must alias neither `in` nor `u`.  It has no counterpart in the reference.
+ */
+int slayer_b200_corr_spike_grad(float *out, const float *in, const float *filter, const float *u,
+                                int64_t rows, int64_t T, int64_t K, float Ts,
+                                float theta, float tau, float scale, void *stream);
+
+/*
  * Time shift by one amount for all rows:  out[r,t] = in[r,t-d] if 0 <= t-d < T else 0,
  * d = trunc(shift / Ts) (toward zero; negative shifts advance the signal).
  * Replaces shift<float>() scalar form / shiftKernel, src/cuda/shiftKernels.h:9-34, :63-98,

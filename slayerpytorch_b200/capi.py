@@ -22,6 +22,7 @@ SYMBOLS = {
     "slayer_b200_last_error": (ctypes.c_char_p, []),
     "slayer_b200_conv": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "slayer_b200_corr": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
+    "slayer_b200_corr_spike_grad": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _f, _f, _f, _p]),
     "slayer_b200_shift_scalar": (_int, [_p, _p, _f, _i64, _i64, _f, _p]),
     "slayer_b200_shift_lut": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "slayer_b200_srm_get_spikes": (_int, [_p, _p, _p, _i64, _i64, _i64, _f, _f, _p]),

@@ -7,7 +7,7 @@
 //   - a one-element shift tensor is read on the device (no host synchronisation);
 //   - the per-neuron shift covers the whole batch in one launch;
 //   - dtype is checked explicitly;
-//   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift,
+//   - additional operators are exported: spikeGrad, spikeGrad_ (in place), spikeGradShift, corrSpikeGrad,
 //     getSpikesDelayed, delayGrad, the bit-packed spike operators packSpikes, unpackSpikes,
 //     getSpikesPacked and convPacked (packed tensors are int32, [..., ceil(T / 32)]), and the
 //     event binning binEvents / binEventsPacked.
@@ -95,6 +95,27 @@ static torch::Tensor corrCuda(torch::Tensor input, torch::Tensor filter, float T
     check_rc(slayer_b200_corr(output.data_ptr<float>(), input.data_ptr<float>(), filter.data_ptr<float>(),
                               rows, T, filter.numel(), Ts, current_stream()),
              "corr");
+    return output;
+}
+
+// spikeGrad(corr(gradOutput, filter, Ts), membranePotential, ...) in one pass: the backward step
+// of a psp filter that follows a spike layer (src/slayer.py:892, then :862).
+static torch::Tensor corrSpikeGradCuda(torch::Tensor gradOut, torch::Tensor filter, torch::Tensor u,
+                                       float theta, float tau, float scale, float Ts)
+{
+    check_input(gradOut, "gradOutput");
+    check_input(filter, "filter");
+    check_input(u, "membranePotential");
+    check_device(gradOut, filter, "gradOutput", "filter");
+    check_device(gradOut, u, "gradOutput", "membranePotential");
+    TORCH_CHECK(gradOut.sizes() == u.sizes(), "gradOutput and membranePotential must have the same shape");
+    c10::cuda::CUDAGuard guard(gradOut.device());
+    auto output = torch::empty_like(gradOut);
+    const int64_t T = gradOut.dim() ? gradOut.size(-1) : 0;
+    const int64_t rows = T ? gradOut.numel() / T : 0;
+    check_rc(slayer_b200_corr_spike_grad(output.data_ptr<float>(), gradOut.data_ptr<float>(), filter.data_ptr<float>(),
+                                         u.data_ptr<float>(), rows, T, filter.numel(), Ts, theta, tau, scale, current_stream()),
+             "corrSpikeGrad");
     return output;
 }
 
@@ -424,6 +445,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
           "gradOutput * scale/tau * exp(-|u - theta| / tau) in one pass (CUDA)");
     m.def("spikeGrad_", &spikeGradInplaceCuda, "In-place variant of spikeGrad (overwrites gradOutput)");
     m.def("spikeGradShift", &spikeGradShiftCuda, "Surrogate gradient of the time-shifted gradient in one pass (CUDA)");
+    m.def("corrSpikeGrad", &corrSpikeGradCuda, "Correlation in time, then the surrogate gradient on its result, in one pass (CUDA)");
     m.def("delayGrad", &delayGradCuda, "Ts * sum over batch and time of gradOutput * d(output)/dt per neuron (CUDA)");
     m.def("packSpikes", &packSpikesCuda, "Spike tensor -> bit-packed int32 words, ceil(T / 32) per row (CUDA)");
     m.def("unpackSpikes", &unpackSpikesCuda, "Bit-packed spike tensor -> fp32 (value where a bit is set) (CUDA)");

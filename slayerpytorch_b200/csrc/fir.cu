@@ -792,11 +792,20 @@ __device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int lim
 // two tiles ahead and the warps expand their rows into the same fp32 tile the copies would have
 // filled, so the arithmetic and the results are those of the fp32 input.  V then is the access
 // width of `out`.
-template <int DIR, int V, int MINB, bool PK = false>
+// RHO: every output is multiplied by the surrogate gradient of the spike function at the
+// potential `rho.u` of the same row and step, out = (Ts * sum) * (c * exp(-|u - theta| / tau)):
+// the filtered value rounded to fp32 exactly as it would have been stored, then the expression
+// of the separate surrogate-gradient pass - the backward of "spike, then psp" in one launch.
+struct FirRho {
+    const float *u;
+    float theta, tau, c;
+};
+
+template <int DIR, int V, int MINB, bool PK = false, bool RHO = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
                 int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status, const int *skip_flag,
-                float spike_value)
+                float spike_value, FirRho rho)
 {
     if (skip_flag != nullptr && *skip_flag != 0) return;      // the event-driven kernel has this call
     extern __shared__ __align__(16) float smem[];
@@ -991,21 +1000,41 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
                 if (row < rows) {
                     float *dst = out + row * (int64_t)T + t0 + tb;
                     const int left = T - (t0 + tb);          // > 0, multiple of V
+                    if constexpr (RHO) {
+                        const float *up = rho.u + row * (int64_t)T + t0 + tb;
+                        float uv[kFirSeg];
+                        if (V == 4) {
+#pragma unroll
+                            for (int q = 0; q < kFirSeg / 4; ++q) {
+                                float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (4 * q < left) t4 = __ldg(reinterpret_cast<const float4 *>(up + 4 * q));
+                                uv[4 * q] = t4.x; uv[4 * q + 1] = t4.y; uv[4 * q + 2] = t4.z; uv[4 * q + 3] = t4.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < kFirSeg; ++q) uv[q] = q < left ? __ldg(up + q) : 0.0f;
+                        }
+#pragma unroll
+                        for (int q = 0; q < kFirSeg; ++q) acc[q] = rho_times(acc[q] * Ts, uv[q], rho.theta, rho.tau, rho.c);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < kFirSeg; ++q) acc[q] *= Ts;
+                    }
                     if (V == 4) {
 #pragma unroll
                         for (int q = 0; q < kFirSeg / 4; ++q)
                             if (4 * q < left)
                                 *reinterpret_cast<float4 *>(dst + 4 * q) = make_float4(
-                                    acc[4 * q] * Ts, acc[4 * q + 1] * Ts, acc[4 * q + 2] * Ts, acc[4 * q + 3] * Ts);
+                                    acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
                     } else if (V == 2) {
 #pragma unroll
                         for (int q = 0; q < kFirSeg / 2; ++q)
                             if (2 * q < left)
-                                *reinterpret_cast<float2 *>(dst + 2 * q) = make_float2(acc[2 * q] * Ts, acc[2 * q + 1] * Ts);
+                                *reinterpret_cast<float2 *>(dst + 2 * q) = make_float2(acc[2 * q], acc[2 * q + 1]);
                     } else {
 #pragma unroll
                         for (int q = 0; q < kFirSeg; ++q)
-                            if (q < left) dst[q] = acc[q] * Ts;
+                            if (q < left) dst[q] = acc[q];
                     }
                 }
             }
@@ -1181,10 +1210,12 @@ static int launch_fir2(float *out, const float *in, const float *filt,
 // The scalar tiled kernels (and, for filters too long to tile, the thread-per-output kernel).
 // PK: `in` points to bit-packed spikes; only the flow kernel expands them, so `taken` comes back
 // false when the shape or the missing status word rules that kernel out.
-template <int DIR, bool PK>
+template <int DIR, bool PK, bool RHO = false>
 static int launch_fir_tiled(float *out, const float *in, const float *filt, int64_t rows, int64_t T, int64_t Keff,
-                            float Ts, cudaStream_t stream, const int *skip_flag, float spike_value, bool &taken)
+                            float Ts, cudaStream_t stream, const int *skip_flag, float spike_value, bool &taken,
+                            FirRho rho = FirRho{nullptr, 0.0f, 1.0f, 0.0f})
 {
+    constexpr bool kFlowOnly = PK || RHO;           // forms that only the flow kernel has
     taken = true;
     FirShape sh;
     // (packed input: the tiles give up 16 words per row to the two staging slots, so that two
@@ -1192,7 +1223,7 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
     const bool tiled = fir_shape(rows, T, Keff, sh, PK ? kFirTileWordsPerRow - kFirStageWords : kFirTileWordsPerRow);
     const int64_t ntiles = tiled ? ceil_div(rows, kFirRows) * sh.ttiles : 0;
     if (!tiled) {
-        if (PK) { taken = false; return SLAYER_B200_OK; }
+        if (kFlowOnly) { taken = false; return SLAYER_B200_OK; }
         const int64_t n = rows * T;
         int64_t g = ceil_div(n, 256);
         const int64_t cap = (int64_t)sm_count() * 32;
@@ -1202,24 +1233,24 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
     }
     const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX +
                                          (PK ? 2 * (size_t)kFirRows * kFirStageWords : 0));
-    const int vw = PK ? tile_vec_width(T, {out}) : tile_vec_width(T, {out, in});
+    const int vw = PK ? tile_vec_width(T, {out}) : (RHO ? tile_vec_width(T, {out, in, rho.u}) : tile_vec_width(T, {out, in}));
     int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
     if (ctas_per_sm > 8) ctas_per_sm = 8;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     int64_t grid = ctas_per_sm * (int64_t)sm_count();
     if (grid > ntiles) grid = ntiles;
-    int *status = (PK || g_fir_flow.load() != 0) ? device_status_word() : nullptr;
+    int *status = (kFlowOnly || g_fir_flow.load() != 0) ? device_status_word() : nullptr;
     if (status) {
-        const bool roomy = (PK || g_fir_flow.load() == 2) && sh.nwarps <= 8;
-        auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1, PK> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1, PK> : fir_flow_kernel<DIR, 1, 1, PK>))
-                          : (vw == 4 ? fir_flow_kernel<DIR, 4, 2, PK> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2, PK> : fir_flow_kernel<DIR, 1, 2, PK>));
+        const bool roomy = (kFlowOnly || g_fir_flow.load() == 2) && sh.nwarps <= 8;
+        auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1, PK, RHO> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1, PK, RHO> : fir_flow_kernel<DIR, 1, 1, PK, RHO>))
+                          : (vw == 4 ? fir_flow_kernel<DIR, 4, 2, PK, RHO> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2, PK, RHO> : fir_flow_kernel<DIR, 1, 2, PK, RHO>));
         int rc = reserve_dynamic_smem((const void *)kern, smem);
         if (rc) return rc;
         kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status, skip_flag,
-                                                               spike_value);
+                                                               spike_value, rho);
         return check_launch("fir (flow) kernel launch");
     }
-    if constexpr (PK) {
+    if constexpr (kFlowOnly) {
         taken = false;
         return SLAYER_B200_OK;
     } else {
@@ -1363,4 +1394,27 @@ extern "C" int slayer_b200_corr(float *out, const float *in, const float *filter
     int rc = check_fir_args("corr", out, in, filter, rows, T, K);
     if (rc) return rc;
     return launch_fir<1>(out, in, filter, rows, T, K, Ts, (cudaStream_t)stream);
+}
+
+extern "C" int slayer_b200_corr_spike_grad(float *out, const float *in, const float *filter, const float *u,
+                                           int64_t rows, int64_t T, int64_t K, float Ts,
+                                           float theta, float tau, float scale, void *stream)
+{
+    using namespace sb200;
+    clear_error();
+    int rc = check_fir_args("corr_spike_grad", out, in, filter, rows, T, K);
+    if (rc) return rc;
+    SB200_REQUIRE(rows == 0 || T == 0 || u != nullptr, "corr_spike_grad: null pointer");
+    SB200_REQUIRE(out != u || rows == 0 || T == 0, "corr_spike_grad: out must not alias u");
+    if (rows == 0 || T == 0) return SLAYER_B200_OK;
+    if (K > 0) {
+        bool taken = false;
+        rc = launch_fir_tiled<1, false, true>(out, in, filter, rows, T, K < T ? K : T, Ts, (cudaStream_t)stream, nullptr, 0.0f,
+                                              taken, FirRho{u, theta, tau, scale / tau});
+        if (taken) return rc;
+    }
+    // shapes the tiled kernel does not take (and the empty filter): the two passes, the second in place
+    rc = launch_fir<1>(out, in, filter, rows, T, K, Ts, (cudaStream_t)stream);
+    if (rc) return rc;
+    return slayer_b200_spike_grad(out, out, u, rows * T, theta, tau, scale, stream);
 }

@@ -125,9 +125,9 @@ class PackedSpikes:
 class _SpikePspFunction(torch.autograd.Function):
     """psp(spike(u)) as one autograd node: the spikes go from the spike kernel to the psp filter
     as bits (1/8 byte per element instead of two fp32 passes) and are returned packed as a second,
-    non-differentiable output.  Backward is the reference's: corr of the incoming gradient
-    (src/slayer.py:892), then the surrogate gradient on the updated potential (src/slayer.py:862).
-    Same results as _PspFunction applied to _SpikeFunction."""
+    non-differentiable output.  Backward is the reference's - corr of the incoming gradient
+    (src/slayer.py:892), then the surrogate gradient on the updated potential (src/slayer.py:862) -
+    as one launch (corrSpikeGrad).  Same results as _PspFunction applied to _SpikeFunction."""
 
     @staticmethod
     def forward(ctx, u, srmKernel, refKernel, neuron, Ts):
@@ -146,8 +146,8 @@ class _SpikePspFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad, _grad_bits):
         u, srmKernel = ctx.saved_tensors
-        g = slayerCuda.corr(grad.contiguous(), srmKernel, ctx.Ts)
-        return slayerCuda.spikeGrad_(g, u, ctx.theta, ctx.tau, ctx.scale), None, None, None, None
+        g = slayerCuda.corrSpikeGrad(grad.contiguous(), srmKernel, u, ctx.theta, ctx.tau, ctx.scale, ctx.Ts)
+        return g, None, None, None, None
 
 
 class _DelayFunction(torch.autograd.Function):

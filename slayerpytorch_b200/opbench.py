@@ -3,7 +3,7 @@
     python -m slayerpytorch_b200.opbench --op getSpikes --rows 262144 --T 300 --iters 5
 
 Operators: conv, corr, convPacked, getSpikes, getSpikesPacked, getSpikesDelayed, shift, shiftScalar,
-spikeGrad, spikeGradShift, delayGrad, loihi, loihiDelayed.  Prints one JSON line with
+spikeGrad, spikeGradShift, corrSpikeGrad, delayGrad, loihi, loihiDelayed.  Prints one JSON line with
 the average launch time, algorithmic GB/s (8 bytes per element for conv/corr/shift, 12 for
 getSpikes/spikeGrad, 16 for loihi) and elements per second.  Small enough to run under a
 profiler: every iteration is exactly one kernel launch of the operator (getSpikes works in
@@ -20,7 +20,7 @@ from slayerpytorch_b200.layer import alpha_kernel, loihi_psp_kernel
 
 ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "shiftScalar": 8, "spikeGrad": 12, "spikeGradShift": 12, "delayGrad": 8,
              "getSpikesDelayed": 12, "getSpikesPacked": 8.125, "convPacked": 4.125,
-             "loihi": 16, "loihiDelayed": 12}
+             "loihi": 16, "loihiDelayed": 12, "corrSpikeGrad": 12}
 
 
 def main(argv=None):
@@ -113,6 +113,10 @@ def main(argv=None):
     elif args.op == "spikeGrad":
         g = torch.randn(shape, device=dev, generator=gen)
         fn = lambda: sc.spikeGrad(g, a, 10.0, 10.0, 1.0)
+    elif args.op == "corrSpikeGrad":
+        g = torch.randn(shape, device=dev, generator=gen)
+        fn = lambda: sc.corrSpikeGrad(g, filt, a, 10.0, 10.0, 1.0, 1.0)
+        extra["taps"] = int(filt.numel())
     elif args.op == "spikeGradShift":
         g = torch.randn(shape, device=dev, generator=gen)
         d = -(torch.rand(neurons, device=dev, generator=gen) * 5)

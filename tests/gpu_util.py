@@ -84,6 +84,14 @@ def c_delay_grad(g, out, Ts):
     return res[:nn]
 
 
+def c_corr_spike_grad(g, f, u, theta, tau, scale, Ts):
+    out = torch.full_like(g, float("nan"))
+    rows, T = rows_T(g)
+    capi.call("slayer_b200_corr_spike_grad", ptr(out), ptr(g), ptr(f), ptr(u), rows, T, f.numel(), float(Ts),
+              float(theta), float(tau), float(scale), stream())
+    return out
+
+
 def c_spike_grad_shift(g, u, lut, theta, tau, scale, Ts, scalar=None):
     out = torch.empty_like(g)
     nb, T = g.shape[0], g.shape[-1]

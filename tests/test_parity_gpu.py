@@ -579,6 +579,41 @@ def test_srm_delayed_sizes_outside_the_fused_path(T):
         G.c_srm_delayed(G.dev(u0), G.dev(nu), G.dev(lut), 10.0, 1.0, scratch=False)
 
 
+# ----------------------------------------------------------------------- corr_spike_grad
+@pytest.mark.parametrize("shape,K,Ts", [((1, 1, 1, 1, 1), 1, 1.0), ((2, 3, 1, 1, 7), 3, 1.0), ((5, 10, 4, 3, 500), 77, 0.1),
+                                        ((3, 16, 1, 1, 300), 77, 1.0), ((4, 8, 2, 1, 301), 12, 0.5), ((2, 6, 1, 1, 1450), 110, 1.0),
+                                        ((3, 5, 1, 1, 33), 40, 2.0), ((70, 37, 1, 1, 302), 77, 1.0), ((1, 3, 1, 1, 5001), 2, 1.0),
+                                        ((2, 2, 1, 1, 2500), 2300, 1.0), ((2, 2, 1, 1, 64), 0, 1.0)])
+def test_corr_spike_grad_equals_corr_then_spike_grad(shape, K, Ts):
+    """The backward step of "spike, then psp" in one launch: corr of the gradient times the
+    surrogate gradient at the potential.  Equal to the two operators it replaces (the product is
+    taken of the filtered value rounded to fp32 either way; only denormal intermediates of the
+    surrogate differ: 1e-37 absolute) and to the oracle within 1e-5."""
+    rng = np.random.RandomState(sum(shape) + K)
+    g = rng.randn(*shape).astype(np.float32)
+    u = (rng.randn(*shape) * 30).astype(np.float32)
+    f = rng.randn(K).astype(np.float32)
+    gd, ud, fd = G.dev(g), G.dev(u), G.dev(f)
+    for theta, tau, scale in ((10.0, 10.0, 1.0), (5120.0, 5120.0, 1 / 195.0)):
+        got = G.host(G.c_corr_spike_grad(gd, fd, ud, theta, tau, scale, Ts))
+        two = G.host(G.c_spike_grad(G.c_conv(gd, fd, Ts, corr=True), ud, theta, tau, scale))
+        np.testing.assert_allclose(got, two, rtol=0, atol=1e-37)
+        want = co.spike_grad(co.corr(g, f, Ts), u, theta, tau, scale)
+        np.testing.assert_allclose(got, want, rtol=REL, atol=1e-37)
+
+
+def test_corr_spike_grad_unaligned_buffers_and_many_rows():
+    rng = np.random.RandomState(78)
+    f = rng.randn(77).astype(np.float32)
+    for rows, T, off in ((9, 300, 1), (70, 302, 2), (1000, 300, 0), (33, 2000, 3)):
+        n = rows * T
+        g, u = rng.randn(n + 3).astype(np.float32), (rng.randn(n + 3) * 20).astype(np.float32)
+        gd, ud = G.dev(g)[off:off + n].view(rows, T), G.dev(u)[off:off + n].view(rows, T)
+        got = G.host(G.c_corr_spike_grad(gd, G.dev(f), ud, 10.0, 10.0, 1.0, 1.0))
+        two = G.host(G.c_spike_grad(G.c_conv(gd, G.dev(f), 1.0, corr=True), ud, 10.0, 10.0, 1.0))
+        np.testing.assert_allclose(got, two, rtol=0, atol=1e-37)
+
+
 # ----------------------------------------------------------------------- spike_grad_shift
 @pytest.mark.parametrize("shape,Ts", [((1, 1, 1, 1, 1), 1.0), ((2, 3, 1, 1, 7), 1.0), ((5, 10, 4, 3, 500), 0.1),
                                       ((3, 16, 1, 1, 300), 1.0), ((4, 8, 2, 1, 301), 0.5), ((2, 6, 1, 1, 1450), 1.0),
