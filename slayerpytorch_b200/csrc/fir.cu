@@ -799,7 +799,32 @@ __device__ __forceinline__ bool fir_wait(uint64_t *bar, unsigned parity, int lim
 struct FirRho {
     const float *u;
     float theta, tau, c;
+    float tau_inv;          // 1 / tau, correctly rounded (computed once on the host)
 };
+
+// a / b rounded to nearest for a divisor that is the same for the whole launch, from its
+// correctly rounded reciprocal y: q0 = a y, then two residual corrections with fused
+// multiply-adds (r = a - b q exactly; q + r y rounds to the quotient - Markstein's theorem; the
+// second step is a safety margin).  The hardware division costs one pass through the
+// special-function unit per element, which this epilogue cannot hide behind memory time as the
+// separate surrogate-gradient pass does.  Infinite or NaN a, and quotients that overflow, return
+// q0, which then already is the quotient's value.
+__device__ __forceinline__ float div_by_launch_constant(float a, float b, float y)
+{
+    const float q0 = a * y;
+    const float r0 = fmaf(-b, q0, a);
+    const float q1 = fmaf(r0, y, q0);
+    const float r1 = fmaf(-b, q1, a);
+    const float q2 = fmaf(r1, y, q1);
+    return fabsf(q0) <= FLT_MAX ? q2 : q0;
+}
+
+// rho_times (common.cuh) with the division above: g * (c * exp(-|u - theta| / tau))
+__device__ __forceinline__ float rho_times_fir(float g, float u, const FirRho &rho)
+{
+    const float e = expf(div_by_launch_constant(-fabsf(u - rho.theta), rho.tau, rho.tau_inv));
+    return g * (rho.c * e);
+}
 
 template <int DIR, int V, int MINB, bool PK = false, bool RHO = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
@@ -975,6 +1000,30 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
 #pragma unroll
                 for (int m = 0; m < kFirSeg; ++m) acc[m] = 0.0f;
 
+                // RHO: the potentials of this thread's 16 outputs are requested now and used after
+                // the arithmetic, a few microseconds later
+                float uv[RHO ? kFirSeg : 1];
+                if constexpr (RHO) {
+                    const int left = T - (t0 + tb);
+                    const float *up = rho.u + (row < rows ? row : 0) * (int64_t)T + t0 + tb;
+                    if (V == 4) {
+#pragma unroll
+                        for (int q = 0; q < kFirSeg / 4; ++q) {
+                            float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (4 * q < left)
+                                asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(t4.x), "=f"(t4.y), "=f"(t4.z), "=f"(t4.w) : "l"(up + 4 * q));
+                            uv[4 * q] = t4.x; uv[4 * q + 1] = t4.y; uv[4 * q + 2] = t4.z; uv[4 * q + 3] = t4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < kFirSeg; ++q) {
+                            uv[q] = 0.0f;
+                            if (q < left) asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(uv[q]) : "l"(up + q));
+                        }
+                    }
+                }
+
                 // initial window (phase 0): conv x[tb-4 .. tb+16), corr x[tb .. tb+20)
                 float w[kFirRing];
                 const unsigned x0 = xrow + 4u * (unsigned)tb - (DIR < 0 ? 16u : 0u);
@@ -1001,21 +1050,8 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
                     float *dst = out + row * (int64_t)T + t0 + tb;
                     const int left = T - (t0 + tb);          // > 0, multiple of V
                     if constexpr (RHO) {
-                        const float *up = rho.u + row * (int64_t)T + t0 + tb;
-                        float uv[kFirSeg];
-                        if (V == 4) {
 #pragma unroll
-                            for (int q = 0; q < kFirSeg / 4; ++q) {
-                                float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (4 * q < left) t4 = __ldg(reinterpret_cast<const float4 *>(up + 4 * q));
-                                uv[4 * q] = t4.x; uv[4 * q + 1] = t4.y; uv[4 * q + 2] = t4.z; uv[4 * q + 3] = t4.w;
-                            }
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < kFirSeg; ++q) uv[q] = q < left ? __ldg(up + q) : 0.0f;
-                        }
-#pragma unroll
-                        for (int q = 0; q < kFirSeg; ++q) acc[q] = rho_times(acc[q] * Ts, uv[q], rho.theta, rho.tau, rho.c);
+                        for (int q = 0; q < kFirSeg; ++q) acc[q] = rho_times_fir(acc[q] * Ts, uv[q], rho);
                     } else {
 #pragma unroll
                         for (int q = 0; q < kFirSeg; ++q) acc[q] *= Ts;
@@ -1213,7 +1249,7 @@ static int launch_fir2(float *out, const float *in, const float *filt,
 template <int DIR, bool PK, bool RHO = false>
 static int launch_fir_tiled(float *out, const float *in, const float *filt, int64_t rows, int64_t T, int64_t Keff,
                             float Ts, cudaStream_t stream, const int *skip_flag, float spike_value, bool &taken,
-                            FirRho rho = FirRho{nullptr, 0.0f, 1.0f, 0.0f})
+                            FirRho rho = FirRho{nullptr, 0.0f, 1.0f, 0.0f, 1.0f})
 {
     constexpr bool kFlowOnly = PK || RHO;           // forms that only the flow kernel has
     taken = true;
@@ -1407,10 +1443,12 @@ extern "C" int slayer_b200_corr_spike_grad(float *out, const float *in, const fl
     SB200_REQUIRE(rows == 0 || T == 0 || u != nullptr, "corr_spike_grad: null pointer");
     SB200_REQUIRE(out != u || rows == 0 || T == 0, "corr_spike_grad: out must not alias u");
     if (rows == 0 || T == 0) return SLAYER_B200_OK;
-    if (K > 0) {
+    // (the epilogue divides by tau through its reciprocal, which wants a tau well inside the
+    // normal range; any other tau takes the two passes)
+    if (K > 0 && tau >= 0x1p-60f && tau <= 0x1p60f) {
         bool taken = false;
         rc = launch_fir_tiled<1, false, true>(out, in, filter, rows, T, K < T ? K : T, Ts, (cudaStream_t)stream, nullptr, 0.0f,
-                                              taken, FirRho{u, theta, tau, scale / tau});
+                                              taken, FirRho{u, theta, tau, scale / tau, 1.0f / tau});
         if (taken) return rc;
     }
     // shapes the tiled kernel does not take (and the empty filter): the two passes, the second in place

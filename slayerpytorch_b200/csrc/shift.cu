@@ -334,7 +334,7 @@ static int launch_shift(float *out, const float *in, const float *lut, float shi
         else shift_vec4_kernel<false, RHO><<<g, threads, 0, stream>>>((float4 *)out, (const float4 *)in, nullptr, shift, Ts, rows, (int)(T / 4), nn, lpr_log2, ra);
     } else if (flat && RHO && T < (1 << 20)) {
         const int unit = (T & 1) ? 4 : 2;               // rows per quad-aligned unit (T % 4 != 0 here)
-        int rpb = (int)((4096 + T - 1) / T);            // about four quads per thread and block of rows
+        int rpb = (int)((16384 + T - 1) / T);           // about sixteen quads per thread and block of rows: few barriers
         rpb = ((rpb + unit - 1) / unit) * unit;
         if (rpb > kRhoRowsMax) rpb = kRhoRowsMax;       // kRhoRowsMax is a multiple of 4
         int64_t nb = ceil_div(rows, rpb);

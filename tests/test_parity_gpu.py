@@ -602,6 +602,27 @@ def test_corr_spike_grad_equals_corr_then_spike_grad(shape, K, Ts):
         np.testing.assert_allclose(got, want, rtol=REL, atol=1e-37)
 
 
+def test_corr_spike_grad_divides_like_the_separate_pass_for_any_tau():
+    """The epilogue divides by tau through its reciprocal and two fused corrections; the quotient
+    must be the correctly rounded one for every tau it accepts (a significand of all ones, thirds,
+    tiny and huge values), and tau outside its range takes the two passes."""
+    rng = np.random.RandomState(5)
+    g = rng.randn(64, 300).astype(np.float32)
+    u = (rng.randn(64, 300) * np.logspace(-3, 3, 300, dtype=np.float32)).astype(np.float32)
+    u[3, 7], u[4, 8], u[5, 9] = np.inf, -np.inf, np.nan
+    f = rng.randn(20).astype(np.float32)
+    gd, ud, fd = G.dev(g), G.dev(u), G.dev(f)
+    c = G.c_conv(gd, fd, 1.0, corr=True)
+    taus = [np.nextafter(np.float32(2), np.float32(1)), np.nextafter(np.float32(1), np.float32(2)), np.float32(1 / 3), np.float32(0.1),
+            np.float32(7.3), np.float32(1e-3), np.float32(123456.7), np.float32(2.0 ** -60), np.float32(2.0 ** 60),
+            np.float32(1e-30), np.float32(1e30)] + list(rng.uniform(0.5, 64, 8).astype(np.float32))
+    for tau in taus:
+        for theta in (0.0, 10.0):
+            got = G.host(G.c_corr_spike_grad(gd, fd, ud, theta, float(tau), 1.0, 1.0))
+            two = G.host(G.c_spike_grad(c, ud, theta, float(tau), 1.0))
+            np.testing.assert_allclose(got, two, rtol=0, atol=1e-37, err_msg="tau = %r" % tau)
+
+
 def test_corr_spike_grad_unaligned_buffers_and_many_rows():
     rng = np.random.RandomState(78)
     f = rng.randn(77).astype(np.float32)
