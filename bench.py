@@ -66,7 +66,7 @@ ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12,
              "getSpikesPacked": 8.125, "convPacked": 4.125, "corrSpikeGrad": 12}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count) on launches too large for L2; see the summaries under profiles/.
-NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
+NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "fir_flow_kernel<surrogate-gradient epilogue>": 11.6, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
                            "spike_grad_shift_rows_kernel": 11.6, "loihi_get_spikes_wide_kernel": 11.9,
                            "delay_grad_kernel": 8.0}
 
@@ -85,7 +85,8 @@ def kernel_of(op, T):
     """Name of the kernel an operator launches for 16-byte aligned fp32 tensors of row length T
     (conv on a mostly-zero input: fir_sparse_kernel instead, see conv_is_probed)."""
     quad = T % 4 == 0
-    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "convPacked": "fir_flow_kernel", "corrSpikeGrad": "fir_flow_kernel",
+    return {"conv": "fir_flow_kernel", "corr": "fir_flow_kernel", "convPacked": "fir_flow_kernel<packed input>",
+            "corrSpikeGrad": "fir_flow_kernel<surrogate-gradient epilogue>",
             "getSpikes": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "getSpikesPacked": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
             "getSpikesDelayed": "srm_get_spikes_tma_kernel" if quad else "srm_get_spikes_wide_kernel",
@@ -804,7 +805,25 @@ def op_table_of(wl, per_op):
     return table
 
 
-def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
+def time_plain_corr(wl, ops, layer, flush):
+    """The corr launch that a corrSpikeGrad launch contains, on the same operand (average ms)."""
+    L = wl.layers[layer]
+    srm = wl.kernels[0]
+    ev = []
+    for _ in range(5):
+        flush_l2(flush)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = ops.corr(L["g_p"], srm, wl.Ts)
+        e1.record()
+        ev.append((e0, e1))
+        del out
+    torch.cuda.synchronize()
+    t = sorted(a.elapsed_time(b) for a, b in ev)[1:]          # the first call may set the kernel up
+    return sum(t) / len(t)
+
+
+def roofline_of(wl, per_op, peak, peak_kind, sm_mhz, ops=None, flush=None):
     """The kernel with the largest share of the step, described on its largest launch."""
     sparse = wl.sparse_convs(True)
 
@@ -841,6 +860,14 @@ def roofline_of(wl, per_op, peak, peak_kind, sm_mhz):
                     "peak_how": "148 SMs x 128 fp32 lanes x 2 flop x the SM clock sampled during the run"})
     else:
         out.update({"bound": "hbm", **hbm})
+    if op == "corrSpikeGrad":
+        out["note"] = ("the launch also evaluates the surrogate gradient of its 16 outputs per thread (one exp, one division by "
+                       "reciprocal + 4 FMAs each) and reads the potential; the 2K flop per element counted here leave that out")
+        if ops is not None and flush is not None:
+            ms = time_plain_corr(wl, ops, layer, flush)
+            tfl = 2.0 * taps * el / (ms * 1e-3) / 1e12
+            out["same_launch_without_epilogue"] = {"op": "corr", "avg_launch_us": round(ms * 1e3, 2), "achieved": round(tfl, 2),
+                                                   "frac": round(tfl / fma_peak, 4)}
     return out
 
 
@@ -915,7 +942,7 @@ def time_ours(args, rank, world, device):
                   "how": "sum over the step's launches of max(algorithmic bytes / measured HBM peak, 2K flop / fp32 FMA peak at the "
                          "sampled clock); a conv that the event-driven kernel takes owes 2K flop x input density",
                   "event_driven_conv_layers": {("L%d" % k): round(v, 4) for k, v in wl.sparse_convs(fused).items()}},
-        "roofline": roofline_of(wl, per_op, peak, peak_kind, sm_mhz),
+        "roofline": roofline_of(wl, per_op, peak, peak_kind, sm_mhz, ops, flush),
         "per_op": op_table_of(wl, per_op),
     }
     if allreduce:
