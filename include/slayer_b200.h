@@ -59,9 +59,9 @@ int slayer_b200_corr(float *out, const float *in, const float *filter,
  * src/slayer.py:892) and then spikeFunction.backward (the tensor expression at src/slayer.py:862)
  * of the layer that produced the spikes, without the intermediate gradient tensor (12 instead of
  * 20 bytes per element).  The filtered value is rounded to fp32 before it is multiplied, so the
- * result equals the two calls', except that intermediate values of the surrogate below 1.2e-38
- * are flushed to zero (the filter's translation unit flushes denormals, the separate pass does
- * not).  `out` must alias neither `in` nor `u`.  It has no counterpart in the reference.
+ * result equals the two calls', except that an exponential below 1.2e-38 is flushed to zero
+ * (the filter's translation unit flushes denormals, the separate pass does not): a difference of
+ * at most 1.2e-38 * scale/tau * |filtered value|.  `out` must alias neither `in` nor `u`.  It has no counterpart in the reference.
  */
 int slayer_b200_corr_spike_grad(float *out, const float *in, const float *filter, const float *u,
                                 int64_t rows, int64_t T, int64_t K, float Ts,
