@@ -455,28 +455,24 @@ struct DrainLane {
 };
 
 // Potentials of an unskewed wide tile starting at time t0 (T % 4 == 0).
+// `changed`: bit r set = row r of the tile differs from what was loaded; the other rows are in
+// global memory already (the potential is updated in place) and are not written again.
 __device__ __forceinline__ void wide_store(const float *tile, float *g, int64_t row0, int64_t rows,
-                                           int t0, int T, int lane)
+                                           int t0, int T, int lane, unsigned changed)
 {
     const DrainLane dl(lane);
     const int t = t0 + dl.c16 * 4;
     if (t >= T) return;
     const int64_t nrow = rows - row0;
+    if (nrow < kTile) changed &= (1u << (int)nrow) - 1u;         // rows past the end of the array
+    changed >>= dl.rsub;
     float *dst = g + (row0 + dl.rsub) * (int64_t)T + t;
     const int64_t pitch = 2 * (int64_t)T;
-    if (nrow >= kTile) {
 #pragma unroll
-        for (int i = 0; i < kTile / 2; ++i) {
+    for (int i = 0; i < kTile / 2; ++i) {
+        if ((changed >> (2 * i)) & 1u)
             *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(tile + dl.word(i));
-            dst += pitch;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < kTile / 2; ++i) {
-            if (i * 2 + dl.rsub < nrow)
-                *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(tile + dl.word(i));
-            dst += pitch;
-        }
+        dst += pitch;
     }
 }
 
@@ -604,6 +600,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
     int sg_next = 0;                // stage the next load goes to
     int inflight = 0;               // lane 0: loads issued and not yet waited for
     int delay_steps = 0;            // DELAYED: the delay of this lane's row, in steps
+    unsigned long long prev_bits = 0ull;    // spike bits of the previous tile of this lane's row
     auto issue_load = [&]() {       // lane 0 only
         const bool two = kWide * j_next + kBoxT < T;           // the second box starts inside the rows
         float *dst = u_tiles + sg_next * kWideWords;
@@ -652,6 +649,7 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
         if (lane == 0) --inflight;
 
         const bool two = kWide * j + kBoxT < T;
+        if (j == 0) prev_bits = 0ull;
         unsigned m[2] = {0u, 0u};
 #pragma unroll 1
         for (int h = 0; h < (two ? 2 : 1); ++h) {
@@ -684,7 +682,15 @@ srm_get_spikes_tma_kernel(const __grid_constant__ CUtensorMap map_u, float *__re
             masks[kTile + lane] = m[1];
         }
         __syncwarp();
-        wide_store(tile, u, rb * kTile, rows, kWide * j, T, lane);
+        // A row's potentials change in this tile only if it spikes here or a spike of the last
+        // nuEff - 1 steps before the tile still reaches into it (spikes further back than the
+        // previous tile: assume they do).
+        const unsigned long long cur_bits = ((unsigned long long)m[1] << 32) | m[0];
+        const int reach = nuEff - 1;
+        const bool row_changed = cur_bits != 0ull || reach > kWide ||
+                                 (reach > 0 && (prev_bits >> (kWide - reach)) != 0ull);
+        prev_bits = cur_bits;
+        wide_store(tile, u, rb * kTile, rows, kWide * j, T, lane, __ballot_sync(0xffffffffu, row_changed));
         if (!DELAYED && !PACKED) wide_store_spikes(masks, s, rb * kTile, rows, kWide * j, T, lane, spikeVal);
         if (DELAYED && j == ntiles - 1)
             store_delayed_spikes(masks, 2 * ntiles, da.out, rb * kTile, rows, T, lane, delay_steps, spikeVal);
