@@ -66,7 +66,7 @@ ALG_BYTES = {"conv": 8, "corr": 8, "getSpikes": 12, "shift": 8, "spikeGrad": 12,
              "getSpikesPacked": 8.125, "convPacked": 4.125, "corrSpikeGrad": 12}
 # DRAM bytes per element measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch over its element count) on launches too large for L2; see the summaries under profiles/.
-NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "fir_flow_kernel<surrogate-gradient epilogue>": 11.6, "srm_get_spikes_tma_kernel": 11.62, "shift_vec4_kernel": 7.4,
+NCU_TRAFFIC_PER_ELEMENT = {"fir_flow_kernel": 7.36, "fir_flow_kernel<surrogate-gradient epilogue>": 11.6, "srm_get_spikes_tma_kernel": 9.85, "shift_vec4_kernel": 7.4,
                            "spike_grad_shift_rows_kernel": 11.6, "loihi_get_spikes_wide_kernel": 11.9,
                            "delay_grad_kernel": 8.0}
 
