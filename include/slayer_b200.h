@@ -334,8 +334,10 @@ int slayer_b200_set_fir_packed(int enable);
  * take the 16-sample segments of a CTA's tiles round robin across tile boundaries and hand tiles
  * over through split-phase shared-memory barriers (bounded waits; a wait that runs out records
  * 0x5102 in the device status word); 2 (the default): the same with a larger register budget
- * where two CTAs per SM still fit; 0: one CTA-wide barrier per tile.  All compute the same bits.
- * It has no counterpart in the reference.
+ * where two CTAs per SM still fit, and with per-row offsets inside the tiles when the arrays are
+ * 16-byte aligned but T is odd, so that copies and stores are 16 instead of 4 bytes wide; 3: as 2
+ * without the row offsets (4-byte accesses for such rows); 0: one
+ * CTA-wide barrier per tile.  All compute the same bits.  It has no counterpart in the reference.
  */
 int slayer_b200_set_fir_flow(int mode);
 

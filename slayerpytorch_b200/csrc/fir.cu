@@ -826,7 +826,13 @@ __device__ __forceinline__ float rho_times_fir(float g, float u, const FirRho &r
     return g * (rho.c * e);
 }
 
-template <int DIR, int V, int MINB, bool PK = false, bool RHO = false>
+// SH (with V = 4): rows that do not start on 16-byte boundaries although the arrays do (used for odd T).
+// Row R starts s = (R T) mod 4 samples past a boundary; its shared-memory row is filled from that
+// boundary on, so position p holds sample g0 + p - s, every copy is a 16-byte copy again, and the
+// lane of the row produces the outputs of the samples s earlier than its neighbours' - which puts
+// its 16-byte stores on boundaries too.  Only the quads that contain a row's first or last
+// sample are handled element by element.
+template <int DIR, int V, int MINB, bool PK = false, bool RHO = false, bool SH = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
                 int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status, const int *skip_flag,
@@ -914,7 +920,37 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
             mbar_arrive(bars + buf);         // (release) this thread's part of the tile is in place
             return;
         }
-        if constexpr (V == 4) {
+        if constexpr (SH) {
+            constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
+            for (int r = warp; r < kFirRows; r += nwarps) {
+                const bool row_ok = r < nrow;
+                const int64_t R = row0 + (row_ok ? r : 0);
+                const int srow = (int)((R * (int64_t)T) & 3);       // samples the row starts past a 16-byte boundary
+                const float *src = in + R * (int64_t)T;
+                float *drow = xs + r * sh.SX;
+#pragma unroll
+                for (int k = 0; k < kChunks; ++k) {
+                    const int pcol = lane * 4 + 128 * k;
+                    if (pcol >= WX) continue;
+                    const int gt = g0 + pcol - srow;                // sample of the chunk's first element
+                    const unsigned dst = xbuf_saddr + 4u * (unsigned)(buf * tile_words + r * sh.SX + pcol);
+                    if (!row_ok || gt >= T || gt + 4 <= 0) {
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, 0;\n" ::"r"(dst), "l"(in) : "memory");
+                    } else if (gt >= 0) {
+                        // whole chunk, or the row's last samples and zeros behind them
+                        const int bytes = gt + 4 <= T ? 16 : 4 * (T - gt);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src + gt), "r"(bytes) : "memory");
+                    } else {
+                        // the row's first samples with zeros in front: element by element
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const bool ok = gt + j >= 0 && gt + j < T;
+                            cp_async<4>(drow + pcol + j, ok ? src + gt + j : in, ok);
+                        }
+                    }
+                }
+            }
+        } else if constexpr (V == 4) {
             constexpr int kChunks = (kFirTileWordsPerRow + 127) / 128;     // 4
             int goff[kChunks], nbytes[kChunks];          // source offset in the row; 16, 0 (zero fill) or -1 (no chunk)
 #pragma unroll
@@ -995,7 +1031,9 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
         int seg = unit0;
         for (; seg < sh.nseg && !gave_up; seg += nwarps) {
             const int tb = seg * kFirSeg;
-            if (t0 + tb < T) {          // else: whole segment beyond the row end (warp-uniform)
+            if (t0 + tb < T + (SH ? 3 : 0)) {          // else: whole segment beyond the row end (warp-uniform)
+                // SH: this lane's outputs are those of the samples srow earlier
+                const int srow = SH ? (int)(((row < rows ? row : 0) * (int64_t)T) & 3) : 0;
                 float acc[kFirSeg];
 #pragma unroll
                 for (int m = 0; m < kFirSeg; ++m) acc[m] = 0.0f;
@@ -1005,8 +1043,25 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
                 float uv[RHO ? kFirSeg : 1];
                 if constexpr (RHO) {
                     const int left = T - (t0 + tb);
-                    const float *up = rho.u + (row < rows ? row : 0) * (int64_t)T + t0 + tb;
-                    if (V == 4) {
+                    const float *up = rho.u + (row < rows ? row : 0) * (int64_t)T + t0 + tb - srow;
+                    if (SH) {
+                        const int tf = t0 + tb - srow;              // sample of this lane's first output
+#pragma unroll
+                        for (int q = 0; q < kFirSeg / 4; ++q) {
+                            float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            const int tq = tf + 4 * q;
+                            if (tq >= 0 && tq + 4 <= T) {
+                                asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(t4.x), "=f"(t4.y), "=f"(t4.z), "=f"(t4.w) : "l"(up + 4 * q));
+                            } else {
+                                if (tq >= 0 && tq < T) t4.x = __ldg(up + 4 * q);
+                                if (tq + 1 >= 0 && tq + 1 < T) t4.y = __ldg(up + 4 * q + 1);
+                                if (tq + 2 >= 0 && tq + 2 < T) t4.z = __ldg(up + 4 * q + 2);
+                                if (tq + 3 >= 0 && tq + 3 < T) t4.w = __ldg(up + 4 * q + 3);
+                            }
+                            uv[4 * q] = t4.x; uv[4 * q + 1] = t4.y; uv[4 * q + 2] = t4.z; uv[4 * q + 3] = t4.w;
+                        }
+                    } else if (V == 4) {
 #pragma unroll
                         for (int q = 0; q < kFirSeg / 4; ++q) {
                             float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1056,7 +1111,22 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
 #pragma unroll
                         for (int q = 0; q < kFirSeg; ++q) acc[q] *= Ts;
                     }
-                    if (V == 4) {
+                    if (SH) {
+                        const int tf = t0 + tb - srow;              // sample of this lane's first output
+                        float *d = dst - srow;
+#pragma unroll
+                        for (int q = 0; q < kFirSeg / 4; ++q) {
+                            const int tq = tf + 4 * q;
+                            if (tq >= 0 && tq + 4 <= T) {
+                                *reinterpret_cast<float4 *>(d + 4 * q) = make_float4(
+                                    acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    if (tq + j >= 0 && tq + j < T) d[4 * q + j] = acc[4 * q + j];
+                            }
+                        }
+                    } else if (V == 4) {
 #pragma unroll
                         for (int q = 0; q < kFirSeg / 4; ++q)
                             if (4 * q < left)
@@ -1267,9 +1337,37 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
         fir_long_kernel<DIR><<<(unsigned)g, 256, 0, stream>>>(out, in, filt, rows, T, Keff, Ts, skip_flag);
         return check_launch("fir (long filter) kernel launch");
     }
+    const int vw = PK ? tile_vec_width(T, {out}) : (RHO ? tile_vec_width(T, {out, in, rho.u}) : tile_vec_width(T, {out, in}));
+    // Rows off the 8-byte grid although the arrays are on the 16-byte one (odd T): the flow kernel
+    // with a per-row offset, so that copies and stores are 16 bytes wide instead of 4.  Its tiles
+    // have to cover up to three samples more.  (Measured: 1.16 against 1.82 ms per 917504 x 301,
+    // 1.28 against 1.54 ms per 131072 x 1449 with 110 taps; for T % 4 == 2 the 8-byte form is the
+    // faster one, 1.14 against 1.28 ms per 131072 x 1450, and stays.)
+    if constexpr (!PK) {
+        const int fmode = g_fir_flow.load();
+        if (vw == 1 && T >= 8 && (fmode == 2 || (kFlowOnly && fmode != 3)) && aligned16(out) && aligned16(in) &&
+            (!RHO || aligned16(rho.u))) {
+            FirShape sh2;
+            int *status2 = device_status_word();
+            if (status2 && fir_shape(rows, T + 3, Keff, sh2)) {
+                const int64_t ntiles2 = ceil_div(rows, kFirRows) * sh2.ttiles;
+                const size_t smem2 = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh2.SX);
+                int64_t per_sm = (int64_t)(220 * 1024 / (smem2 + 1024));
+                if (per_sm > 8) per_sm = 8;
+                if (per_sm < 1) per_sm = 1;
+                int64_t grid2 = per_sm * (int64_t)sm_count();
+                if (grid2 > ntiles2) grid2 = ntiles2;
+                auto kern2 = sh2.nwarps <= 8 ? fir_flow_kernel<DIR, 4, 1, false, RHO, true> : fir_flow_kernel<DIR, 4, 2, false, RHO, true>;
+                int rc2 = reserve_dynamic_smem((const void *)kern2, smem2);
+                if (rc2) return rc2;
+                kern2<<<(unsigned)grid2, sh2.nwarps * 32, smem2, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh2, ntiles2,
+                                                                           status2, skip_flag, spike_value, rho);
+                return check_launch("fir (flow, row offsets) kernel launch");
+            }
+        }
+    }
     const size_t smem = sizeof(float) * (8 + (size_t)((Keff + 3) & ~3LL) + 4 + 2 * (size_t)kFirRows * sh.SX +
                                          (PK ? 2 * (size_t)kFirRows * kFirStageWords : 0));
-    const int vw = PK ? tile_vec_width(T, {out}) : (RHO ? tile_vec_width(T, {out, in, rho.u}) : tile_vec_width(T, {out, in}));
     int64_t ctas_per_sm = (int64_t)(220 * 1024 / (smem + 1024));      // 2 for full-size tiles
     if (ctas_per_sm > 8) ctas_per_sm = 8;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -1277,7 +1375,7 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
     if (grid > ntiles) grid = ntiles;
     int *status = (kFlowOnly || g_fir_flow.load() != 0) ? device_status_word() : nullptr;
     if (status) {
-        const bool roomy = (kFlowOnly || g_fir_flow.load() == 2) && sh.nwarps <= 8;
+        const bool roomy = (kFlowOnly || g_fir_flow.load() >= 2) && sh.nwarps <= 8;
         auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1, PK, RHO> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1, PK, RHO> : fir_flow_kernel<DIR, 1, 1, PK, RHO>))
                           : (vw == 4 ? fir_flow_kernel<DIR, 4, 2, PK, RHO> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2, PK, RHO> : fir_flow_kernel<DIR, 1, 2, PK, RHO>));
         int rc = reserve_dynamic_smem((const void *)kern, smem);
@@ -1354,7 +1452,7 @@ extern "C" int slayer_b200_set_fir_packed(int enable)
 
 extern "C" int slayer_b200_set_fir_flow(int mode)
 {
-    return sb200::g_fir_flow.exchange(mode < 0 || mode > 2 ? 1 : mode);
+    return sb200::g_fir_flow.exchange(mode < 0 || mode > 3 ? 1 : mode);
 }
 
 extern "C" int slayer_b200_set_fir_skip_zeros(int mode)

@@ -36,7 +36,7 @@ def main(argv=None):
     ap.add_argument("--packed-fir", type=int, default=None, metavar="MODE",
                     help="conv/corr: kernel selection as slayer_b200_set_fir_packed takes it (0 scalar, 1 packed, 2 / 3 tile size)")
     ap.add_argument("--fir-flow", type=int, default=None, metavar="MODE",
-                    help="conv/corr: form of the scalar kernel as slayer_b200_set_fir_flow takes it (0, 1, 2)")
+                    help="conv/corr: form of the scalar kernel as slayer_b200_set_fir_flow takes it (0, 1, 2, 3)")
     ap.add_argument("--srm-stages", type=int, default=None, metavar="N",
                     help="getSpikes*: stages per warp as slayer_b200_set_srm_stages takes it (2 .. 8)")
     ap.add_argument("--no-skip-zeros", action="store_true", help="conv/corr: no zero skipping (the dense kernels only)")
