@@ -364,6 +364,11 @@ int slayer_b200_set_srm_stages(int stages);
  *      two-row kernel (slayer_b200_set_fir_packed) also skips sample positions that are zero in
  *      all 64 rows of a tile.
  *   2: the event-driven kernel for every input it can take, whatever the density (testing).
+ * The decision of a probed call lives in one of 64 slots of a per-device ring (1 KB, allocated by
+ * the first probed call on the device: make that call outside stream capture).  Calls on one
+ * stream never share a live slot; calls on different streams, or replays of graphs captured from
+ * them, do once more than 64 probed calls lie between them - keep concurrent streams closer than
+ * that, or switch the probe off (mode 0 or 2) for them.
  * It has no counterpart in the reference.
  */
 int slayer_b200_set_fir_skip_zeros(int mode);
