@@ -28,6 +28,7 @@
 // The row stride of the tile is = 4 (mod 8) words, which makes the per-row 128-bit loads of a
 // warp conflict free.
 #include <atomic>
+#include <type_traits>
 #include <cfloat>
 
 #include "common.cuh"
@@ -142,6 +143,13 @@ __device__ __forceinline__ void fir_rest(float (&acc)[kFirSeg], float (&w)[kFirR
     }
     fir_step<DIR, PH>(acc, w, f, fp, xp);
     if constexpr (PH + 1 < kFirPhases) fir_rest<DIR, PH + 1>(acc, w, f, fp, xp, left - 1, tail);
+}
+
+// The partial group of `tail` taps when the groups end in front of phase PH.
+template <int DIR, int PH>
+__device__ __forceinline__ void fir_tail(float (&acc)[kFirSeg], float (&w)[kFirRing], float4 (&f)[2], int tail)
+{
+    if (tail) fir_group_n<DIR, PH>(acc, w, f[PH & 1], tail);
 }
 
 struct FirShape {
@@ -832,7 +840,12 @@ __device__ __forceinline__ float rho_times_fir(float g, float u, const FirRho &r
 // lane of the row produces the outputs of the samples s earlier than its neighbours' - which puts
 // its 16-byte stores on boundaries too.  Only the quads that contain a row's first or last
 // sample are handled element by element.
-template <int DIR, int V, int MINB, bool PK = false, bool RHO = false, bool SH = false>
+// RX: how the groups of four taps that do not fill a run of six are handled.  false: behind the
+// loop over whole runs (up to five more group bodies); true: the loop is left where the groups
+// end, so that no group body exists twice - the code a segment walks through then fits the
+// instruction cache whatever K is (110 taps, 4 runs + 3 groups: 1.02 -> 0.83 ms per 131072 x
+// 1448), at the price of a compare and branch per group (77 taps, 3 runs + 1: 3 % slower).
+template <int DIR, int V, int MINB, bool PK = false, bool RHO = false, bool SH = false, bool RX = false>
 __global__ void __launch_bounds__(kFirMaxWarps * 32, MINB)
 fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const float *__restrict__ filt,
                 int64_t rows, int T, int K, float Ts, FirShape sh, int64_t ntiles, int *status, const int *skip_flag,
@@ -1088,18 +1101,43 @@ fir_flow_kernel(float *__restrict__ out, const float *__restrict__ in, const flo
                 unsigned fp = fs_addr;
                 float4 f[2];
                 f[0] = ld4(fp);
-                int g = 0;
-                for (; g + kFirPhases <= groups; g += kFirPhases) {
-                    fir_step<DIR, 0>(acc, w, f, fp, xp);
-                    fir_step<DIR, 1>(acc, w, f, fp, xp);
-                    fir_step<DIR, 2>(acc, w, f, fp, xp);
-                    fir_step<DIR, 3>(acc, w, f, fp, xp);
-                    fir_step<DIR, 4>(acc, w, f, fp, xp);
-                    fir_step<DIR, 5>(acc, w, f, fp, xp);
-                    xp += kFirPhases * step;
-                    fp += 16 * kFirPhases;
+                if constexpr (!RX) {
+                    int g = 0;
+                    for (; g + kFirPhases <= groups; g += kFirPhases) {
+                        fir_step<DIR, 0>(acc, w, f, fp, xp);
+                        fir_step<DIR, 1>(acc, w, f, fp, xp);
+                        fir_step<DIR, 2>(acc, w, f, fp, xp);
+                        fir_step<DIR, 3>(acc, w, f, fp, xp);
+                        fir_step<DIR, 4>(acc, w, f, fp, xp);
+                        fir_step<DIR, 5>(acc, w, f, fp, xp);
+                        xp += kFirPhases * step;
+                        fp += 16 * kFirPhases;
+                    }
+                    fir_rest<DIR, 0>(acc, w, f, fp, xp, groups - g, tail);
+                } else {
+                    // Several groups left over after the runs of six: leave the run where the
+                    // groups end instead of repeating up to five group bodies behind the loop -
+                    // the code a segment walks through stays small enough for the instruction
+                    // cache (110 taps: 27 groups = 4 runs + 3).
+                    int n = groups;
+                    for (;;) {
+                        if (n == 0) { fir_tail<DIR, 0>(acc, w, f, tail); break; }
+                        fir_step<DIR, 0>(acc, w, f, fp, xp);
+                        if (n == 1) { fir_tail<DIR, 1>(acc, w, f, tail); break; }
+                        fir_step<DIR, 1>(acc, w, f, fp, xp);
+                        if (n == 2) { fir_tail<DIR, 2>(acc, w, f, tail); break; }
+                        fir_step<DIR, 2>(acc, w, f, fp, xp);
+                        if (n == 3) { fir_tail<DIR, 3>(acc, w, f, tail); break; }
+                        fir_step<DIR, 3>(acc, w, f, fp, xp);
+                        if (n == 4) { fir_tail<DIR, 4>(acc, w, f, tail); break; }
+                        fir_step<DIR, 4>(acc, w, f, fp, xp);
+                        if (n == 5) { fir_tail<DIR, 5>(acc, w, f, tail); break; }
+                        fir_step<DIR, 5>(acc, w, f, fp, xp);
+                        n -= kFirPhases;
+                        xp += kFirPhases * step;
+                        fp += 16 * kFirPhases;
+                    }
                 }
-                fir_rest<DIR, 0>(acc, w, f, fp, xp, groups - g, tail);
 
                 if (row < rows) {
                     float *dst = out + row * (int64_t)T + t0 + tb;
@@ -1338,6 +1376,11 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
         return check_launch("fir (long filter) kernel launch");
     }
     const int vw = PK ? tile_vec_width(T, {out}) : (RHO ? tile_vec_width(T, {out, in, rho.u}) : tile_vec_width(T, {out, in}));
+    // groups of four taps left over after the runs of six: two or more take the form of the
+    // kernel that leaves the run where the groups end, and so do the forms with more code around
+    // the arithmetic (packed input, surrogate epilogue), which measure 2-3 % faster that way
+    // even with one group left over (mode 4 of slayer_b200_set_fir_flow: always)
+    const bool rx = ((Keff >> 2) % kFirPhases) >= 2 || kFlowOnly || g_fir_flow.load() == 4;
     // Rows off the 8-byte grid although the arrays are on the 16-byte one (odd T): the flow kernel
     // with a per-row offset, so that copies and stores are 16 bytes wide instead of 4.  Its tiles
     // have to cover up to three samples more.  (Measured: 1.16 against 1.82 ms per 917504 x 301,
@@ -1345,7 +1388,7 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
     // faster one, 1.14 against 1.28 ms per 131072 x 1450, and stays.)
     if constexpr (!PK) {
         const int fmode = g_fir_flow.load();
-        if (vw == 1 && T >= 8 && (fmode == 2 || (kFlowOnly && fmode != 3)) && aligned16(out) && aligned16(in) &&
+        if (vw == 1 && T >= 8 && (fmode == 2 || fmode == 4 || (kFlowOnly && fmode != 3)) && aligned16(out) && aligned16(in) &&
             (!RHO || aligned16(rho.u))) {
             FirShape sh2;
             int *status2 = device_status_word();
@@ -1357,7 +1400,8 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
                 if (per_sm < 1) per_sm = 1;
                 int64_t grid2 = per_sm * (int64_t)sm_count();
                 if (grid2 > ntiles2) grid2 = ntiles2;
-                auto kern2 = sh2.nwarps <= 8 ? fir_flow_kernel<DIR, 4, 1, false, RHO, true> : fir_flow_kernel<DIR, 4, 2, false, RHO, true>;
+                auto kern2 = sh2.nwarps <= 8 ? (rx ? fir_flow_kernel<DIR, 4, 1, false, RHO, true, true> : fir_flow_kernel<DIR, 4, 1, false, RHO, true, false>)
+                                             : (rx ? fir_flow_kernel<DIR, 4, 2, false, RHO, true, true> : fir_flow_kernel<DIR, 4, 2, false, RHO, true, false>);
                 int rc2 = reserve_dynamic_smem((const void *)kern2, smem2);
                 if (rc2) return rc2;
                 kern2<<<(unsigned)grid2, sh2.nwarps * 32, smem2, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh2, ntiles2,
@@ -1376,8 +1420,14 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
     int *status = (kFlowOnly || g_fir_flow.load() != 0) ? device_status_word() : nullptr;
     if (status) {
         const bool roomy = (kFlowOnly || g_fir_flow.load() >= 2) && sh.nwarps <= 8;
-        auto kern = roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1, PK, RHO> : (vw == 2 ? fir_flow_kernel<DIR, 2, 1, PK, RHO> : fir_flow_kernel<DIR, 1, 1, PK, RHO>))
-                          : (vw == 4 ? fir_flow_kernel<DIR, 4, 2, PK, RHO> : (vw == 2 ? fir_flow_kernel<DIR, 2, 2, PK, RHO> : fir_flow_kernel<DIR, 1, 2, PK, RHO>));
+        auto pick = [&](auto rxc) {
+            constexpr bool RXV = decltype(rxc)::value;
+            return roomy ? (vw == 4 ? fir_flow_kernel<DIR, 4, 1, PK, RHO, false, RXV>
+                                    : (vw == 2 ? fir_flow_kernel<DIR, 2, 1, PK, RHO, false, RXV> : fir_flow_kernel<DIR, 1, 1, PK, RHO, false, RXV>))
+                         : (vw == 4 ? fir_flow_kernel<DIR, 4, 2, PK, RHO, false, RXV>
+                                    : (vw == 2 ? fir_flow_kernel<DIR, 2, 2, PK, RHO, false, RXV> : fir_flow_kernel<DIR, 1, 2, PK, RHO, false, RXV>));
+        };
+        auto kern = rx ? pick(std::true_type{}) : pick(std::false_type{});
         int rc = reserve_dynamic_smem((const void *)kern, smem);
         if (rc) return rc;
         kern<<<(unsigned)grid, sh.nwarps * 32, smem, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh, ntiles, status, skip_flag,
@@ -1452,7 +1502,7 @@ extern "C" int slayer_b200_set_fir_packed(int enable)
 
 extern "C" int slayer_b200_set_fir_flow(int mode)
 {
-    return sb200::g_fir_flow.exchange(mode < 0 || mode > 3 ? 1 : mode);
+    return sb200::g_fir_flow.exchange(mode < 0 || mode > 4 ? 1 : mode);
 }
 
 extern "C" int slayer_b200_set_fir_skip_zeros(int mode)

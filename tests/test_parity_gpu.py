@@ -78,18 +78,20 @@ def test_shift_unaligned_buffers_take_the_scalar_path():
 
 
 # --------------------------------------------------------------------------- conv / corr
-@pytest.fixture(params=["scalar-lean", "scalar", "scalar-no-row-offsets", "scalar-tile-barrier", "packed", "packed-half-tiles",
-                        "packed-full-tiles", "event-driven"])
+@pytest.fixture(params=["scalar-lean", "scalar", "scalar-no-row-offsets", "scalar-run-exit", "scalar-tile-barrier", "packed",
+                        "packed-half-tiles", "packed-full-tiles", "event-driven"])
 def fir_variant(request):
     """conv / corr have several kernels that must give the same bits: the scalar one in its three
     forms (segments dealt out across tiles with split-phase barriers, the same with more
     registers - the default, which also keeps 16-byte accesses for rows that are off the 16-byte
-    grid by giving each row an offset inside the tile -, that without the row offsets, one CTA-wide
-    barrier per tile), the packed one (two rows per lane,
+    grid by giving each row an offset inside the tile -, that without the row offsets, that with
+    the loop over the tap groups always left where the groups end, one CTA-wide barrier per tile),
+    the packed one (two rows per lane,
     two-wide FMAs) with either of its tile sizes, and the event-driven one (a list of non-zero
     samples per row; here forced on whatever the input holds)."""
     from slayerpytorch_b200 import capi
     packed, flow, zeros = {"scalar-lean": (0, 1, 1), "scalar": (0, 2, 1), "scalar-no-row-offsets": (0, 3, 1),
+                           "scalar-run-exit": (0, 4, 1),
                            "scalar-tile-barrier": (0, 0, 1), "packed": (1, 2, 1),
                            "packed-half-tiles": (2, 2, 1), "packed-full-tiles": (3, 2, 1),
                            "event-driven": (0, 2, 2)}[request.param]
