@@ -335,8 +335,8 @@ int slayer_b200_set_fir_packed(int enable);
  * over through split-phase shared-memory barriers (bounded waits; a wait that runs out records
  * 0x5102 in the device status word); 2 (the default): the same with a larger register budget
  * where two CTAs per SM still fit, and with per-row offsets inside the tiles when the arrays are
- * 16-byte aligned but T is odd, so that copies and stores are 16 instead of 4 bytes wide; 3: as 2
- * without the row offsets (4-byte accesses for such rows); 4: as 2 with the loop over the groups
+ * 16-byte aligned but their rows are not (T % 4 != 0), so that copies and stores are 16 instead
+ * of 8 or 4 bytes wide; 3: as 2 without the row offsets; 4: as 2 with the loop over the groups
  * of four taps always in the form that is left where the groups end (by default only where that
  * form measured faster); 0: one
  * CTA-wide barrier per tile.  All compute the same bits.  It has no counterpart in the reference.

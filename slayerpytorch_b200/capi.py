@@ -103,7 +103,7 @@ def set_fir_packed(mode):
 
 def set_fir_flow(mode):
     """Form of the scalar conv / corr kernel: 1 = no per-tile barrier, 2 = the same with more
-    registers and 16-byte accesses for rows of odd length (default), 3 = as 2 without the
+    registers and 16-byte accesses for rows off the 16-byte grid (default), 3 = as 2 without the
     latter, 0 = one barrier per tile.  Returns the previous setting."""
     return int(load().slayer_b200_set_fir_flow(int(mode)))
 

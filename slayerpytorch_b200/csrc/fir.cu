@@ -834,7 +834,7 @@ __device__ __forceinline__ float rho_times_fir(float g, float u, const FirRho &r
     return g * (rho.c * e);
 }
 
-// SH (with V = 4): rows that do not start on 16-byte boundaries although the arrays do (used for odd T).
+// SH (with V = 4): rows that do not start on 16-byte boundaries although the arrays do (T % 4 != 0).
 // Row R starts s = (R T) mod 4 samples past a boundary; its shared-memory row is filled from that
 // boundary on, so position p holds sample g0 + p - s, every copy is a 16-byte copy again, and the
 // lane of the row produces the outputs of the samples s earlier than its neighbours' - which puts
@@ -1381,14 +1381,15 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
     // the arithmetic (packed input, surrogate epilogue), which measure 2-3 % faster that way
     // even with one group left over (mode 4 of slayer_b200_set_fir_flow: always)
     const bool rx = ((Keff >> 2) % kFirPhases) >= 2 || kFlowOnly || g_fir_flow.load() == 4;
-    // Rows off the 8-byte grid although the arrays are on the 16-byte one (odd T): the flow kernel
-    // with a per-row offset, so that copies and stores are 16 bytes wide instead of 4.  Its tiles
-    // have to cover up to three samples more.  (Measured: 1.16 against 1.82 ms per 917504 x 301,
-    // 1.28 against 1.54 ms per 131072 x 1449 with 110 taps; for T % 4 == 2 the 8-byte form is the
-    // faster one, 1.14 against 1.28 ms per 131072 x 1450, and stays.)
+    // Rows off the 16-byte grid although the arrays are on it (T % 4 != 0): the flow kernel with a
+    // per-row offset, so that copies and stores are 16 bytes wide instead of 8 or 4.  Its tiles
+    // have to cover up to three samples more, and it always takes the form of the tap loop with the
+    // smaller instruction footprint (its fill and store code is the longest).  Measured, 110 taps
+    // on 131072 rows: T = 1449 0.93 ms (4-byte accesses: 1.37 ms), against T = 1450 with 8-byte
+    // accesses 0.97 ms and T = 1448 0.84 ms; 77 taps on 917504 x 301: 1.09 against 1.82 ms.
     if constexpr (!PK) {
         const int fmode = g_fir_flow.load();
-        if (vw == 1 && T >= 8 && (fmode == 2 || fmode == 4 || (kFlowOnly && fmode != 3)) && aligned16(out) && aligned16(in) &&
+        if (vw < 4 && T >= 8 && (fmode == 2 || fmode == 4 || (kFlowOnly && fmode != 3)) && aligned16(out) && aligned16(in) &&
             (!RHO || aligned16(rho.u))) {
             FirShape sh2;
             int *status2 = device_status_word();
@@ -1400,8 +1401,7 @@ static int launch_fir_tiled(float *out, const float *in, const float *filt, int6
                 if (per_sm < 1) per_sm = 1;
                 int64_t grid2 = per_sm * (int64_t)sm_count();
                 if (grid2 > ntiles2) grid2 = ntiles2;
-                auto kern2 = sh2.nwarps <= 8 ? (rx ? fir_flow_kernel<DIR, 4, 1, false, RHO, true, true> : fir_flow_kernel<DIR, 4, 1, false, RHO, true, false>)
-                                             : (rx ? fir_flow_kernel<DIR, 4, 2, false, RHO, true, true> : fir_flow_kernel<DIR, 4, 2, false, RHO, true, false>);
+                auto kern2 = sh2.nwarps <= 8 ? fir_flow_kernel<DIR, 4, 1, false, RHO, true, true> : fir_flow_kernel<DIR, 4, 2, false, RHO, true, true>;
                 int rc2 = reserve_dynamic_smem((const void *)kern2, smem2);
                 if (rc2) return rc2;
                 kern2<<<(unsigned)grid2, sh2.nwarps * 32, smem2, stream>>>(out, in, filt, rows, (int)T, (int)Keff, Ts, sh2, ntiles2,
